@@ -1,0 +1,424 @@
+#!/usr/bin/env python
+"""LoRA-delta throughput benchmark (one JSON line on stdout).
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--config 2..5]
+
+A step is one pass of the hot path over one batch: for every transformer layer, the q/k/v LoRA deltas
+(shrink + expand) and the o LoRA delta of all tokens of the batch.  The default workload is the S1-shaped decode
+batch (configuration 2: hidden 4096, 32 layers, 1000 rank-8 adapters paged randomly into a [262144, 4096] fp16
+pool, 256 tokens with Zipf(1.0) adapter ids), drawn from seeded generators.
+
+* ``value``: tokens/s with every input resident in HBM, the step replayed from a CUDA graph, CUDA-event timed.
+* ``e2e``: the same metric through the public Python API (LoraBatchOps) with activations starting in pinned host
+  memory and the deltas read back to the host inside the timed region.
+* ``roofline``: the dominant kernel's algorithmic bytes per launch over its CUDA-event time, against the measured
+  HBM copy bandwidth.
+* ``cpu_baseline`` / ``--impl reference``: the reference's torch per-token formula on the host cores.
+
+Multi-GPU: configurations 2 and 3 (7B-shaped, one GPU holds everything) run as independent replicas, one batch per
+GPU ("weak"); configurations 4 and 5 run under S-LoRA tensor parallelism ("strong").
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+import torch  # noqa: E402
+
+
+def parse_args():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--config", type=int, default=2)
+    ap.add_argument("--phys-layers", type=int, default=8,
+                    help="distinct layers held in HBM and cycled over the model's layer count")
+    ap.add_argument("--mode", default="auto", choices=["auto", "dp", "tp"])
+    ap.add_argument("--no-graph", action="store_true")
+    ap.add_argument("--no-pdl", action="store_true")
+    ap.add_argument("--no-plan", action="store_true")
+    ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-cpu", action="store_true")
+    ap.add_argument("--cpu-seconds", type=float, default=10.0)
+    ap.add_argument("--pool-rows", type=int, default=None)
+    return ap.parse_args()
+
+
+def load_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        d = json.load(open(path))
+        return float(d["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons through NVML (read-only) while the timed region runs."""
+
+    def __init__(self, index):
+        self.samples, self.reasons, self.max_mhz = [], set(), None
+        self._stop = threading.Event()
+        self._thread = None
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self.nv = pynvml
+            self.h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM)
+        except Exception:
+            self.nv = None
+
+    def _run(self):
+        nv = self.nv
+        names = {"hw_slowdown": 0x8, "sw_power_cap": 0x4, "hw_thermal_slowdown": 0x40, "sw_thermal_slowdown": 0x20,
+                 "hw_power_brake": 0x80}
+        while not self._stop.is_set():
+            try:
+                self.samples.append(nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM))
+                try:
+                    r = nv.nvmlDeviceGetCurrentClocksEventReasons(self.h)
+                except Exception:
+                    r = nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.h)
+                for k, bit in names.items():
+                    if r & bit:
+                        self.reasons.add(k)
+            except Exception:
+                pass
+            time.sleep(0.02)
+
+    def __enter__(self):
+        if self.nv is not None:
+            self._thread = threading.Thread(target=self._run, daemon=True)
+            self._thread.start()
+        return self
+
+    def __exit__(self, *exc):
+        self._stop.set()
+        if self._thread is not None:
+            self._thread.join()
+        return False
+
+    def summary(self):
+        return {"sm_mhz": statistics.median(self.samples) if self.samples else None, "sm_max_mhz": self.max_mhz,
+                "reasons": sorted(self.reasons), "samples": len(self.samples)}
+
+
+def physical_gpu_index(local_rank):
+    vis = os.environ.get("CUDA_VISIBLE_DEVICES")
+    if vis:
+        try:
+            return int(vis.split(",")[local_rank])
+        except Exception:
+            return local_rank
+    return local_rank
+
+
+# ------------------------------------------------------------------------------------------------------------------
+# the reference arm: the reference's CPU formulation of the path on the host cores
+# ------------------------------------------------------------------------------------------------------------------
+def cpu_workload(cfg, pool_rows):
+    from slora_b200.workloads import build_workload
+    return build_workload(cfg, device="cpu", phys_layers=1, pool_rows=pool_rows)
+
+
+def run_cpu_baseline(cfg, pool_rows, seconds):
+    from oracle import cpu_baseline as cb
+    wl = cpu_workload(cfg, pool_rows)
+    sec_per_layer, reps = cb.time_layer(wl, min_seconds=seconds)
+    L = wl.spec.layers
+    return {"value": wl.T / (sec_per_layer * L), "unit": "tokens/s", "cores": torch.get_num_threads(),
+            "kind": "port",
+            "sample": f"1 of {L} layers (q,k,v,o over the whole {wl.T}-token batch) x {reps} repetitions, "
+                      f"{sec_per_layer:.3f} s per layer, extrapolated x{L}; torch per-token formula, fp32, "
+                      f"{torch.get_num_threads()} threads of {os.cpu_count()} cpus"}, wl
+
+
+def reference_arm(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    from oracle import cpu_baseline as cb
+    from slora_b200.workloads import SPECS
+    pool_rows = args.pool_rows or min(SPECS[args.config].pool_rows, 65536 if args.config != 4 else 327680)
+    wl = cpu_workload(args.config, pool_rows)
+    L = wl.spec.layers
+    call = (wl.x_qkv[0], wl.x_o[0], wl.pools_a[0], wl.pools_b[0], wl.a_start, wl.a_len, wl.a_loc, wl.ids,
+            wl.a_scaling, wl.proj_dims())
+    for _ in range(max(1, min(args.warmup, 3))):
+        cb.per_token_layer(*call)
+    times = []
+    for _ in range(args.steps):
+        t0 = time.perf_counter()
+        cb.per_token_layer(*call)
+        times.append(time.perf_counter() - t0)
+    sec_per_layer = sum(times) / len(times)
+    value = wl.T / (sec_per_layer * L)
+    sample = (f"each step = 1 of {L} layers (q,k,v,o over the whole {wl.T}-token batch), extrapolated x{L}; "
+              f"torch per-token formula, fp32, {torch.get_num_threads()} threads")
+    line = {"impl": "reference", "metric": "lora_delta_tokens_per_s", "value": value, "unit": "tokens/s",
+            "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": sec_per_layer * L * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "f32", "data": "synthetic",
+            "config": {"workload": wl.spec.name, "tokens": wl.T, "layers": L, "hidden": wl.spec.hidden,
+                       "adapters": wl.spec.n_adapters, "pool_rows": pool_rows},
+            "cpu_baseline": {"value": value, "unit": "tokens/s", "cores": torch.get_num_threads(), "kind": "port",
+                             "sample": sample},
+            "e2e": {"value": value, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+            "gpu_launches": 0}
+    print(json.dumps(line), flush=True)
+
+
+# ------------------------------------------------------------------------------------------------------------------
+# our arm
+# ------------------------------------------------------------------------------------------------------------------
+class Runner:
+    """Holds one GPU's resident workload and issues steps through the public API."""
+
+    def __init__(self, args, cfg, device, seed_shift=0):
+        import slora_b200 as sl
+        from slora_b200.workloads import build_workload
+        self.sl = sl
+        self.args = args
+        wl = build_workload(cfg, device=device, phys_layers=args.phys_layers, pool_rows=args.pool_rows)
+        if seed_shift:
+            # replicas serve different batches: redraw the per-token adapter ids
+            from slora_b200.workloads import build_batch
+            g = torch.Generator().manual_seed(3000 + cfg + 7919 * seed_shift)
+            ids, seg = build_batch(wl.spec, g)
+            wl.ids, wl.segments = ids.to(device), seg
+        self.wl = wl
+        self.L = wl.spec.layers
+        self.P = args.phys_layers
+        H, K = wl.spec.hidden, wl.spec.h_kv
+        dt = wl.dtype
+        self.q = [torch.zeros((wl.T, H), dtype=dt, device=device) for _ in range(self.P)]
+        self.k = [torch.zeros((wl.T, K), dtype=dt, device=device) for _ in range(self.P)]
+        self.v = [torch.zeros((wl.T, K), dtype=dt, device=device) for _ in range(self.P)]
+        self.o = [torch.zeros((wl.T, H), dtype=dt, device=device) for _ in range(self.P)]
+        self.ops = sl.LoraBatchOps(wl.a_start, wl.a_len, wl.a_loc, wl.a_scaling, wl.pools_a, wl.pools_b, wl.max_rank,
+                                   use_pdl=not args.no_pdl)
+        self.ops.prepare(wl.ids, use_plan=not args.no_plan)
+        self.launches_per_step = 4 * self.L
+        self.graph = None
+
+    def zero_outputs(self):
+        for bufs in (self.q, self.k, self.v, self.o):
+            for b in bufs:
+                b.zero_()
+
+    def step_eager(self):
+        ops, wl = self.ops, self.wl
+        for l in range(self.L):
+            p = l % self.P
+            ops.lora_get_qkv(p, wl.x_qkv[p], self.q[p], self.k[p], self.v[p])
+            ops.lora_get_o(p, wl.x_o[p], self.o[p])
+
+    def capture(self):
+        s = torch.cuda.Stream()
+        s.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(s):
+            self.step_eager()
+        torch.cuda.current_stream().wait_stream(s)
+        torch.cuda.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, stream=s):
+            self.step_eager()
+        self.graph = g
+
+    def step(self):
+        if self.graph is not None:
+            self.graph.replay()
+        else:
+            self.step_eager()
+
+
+def kernel_roofline(run, peak_gbs, peak_kind, reps=3):
+    """Per-launch CUDA-event timing of the q/k/v expand launch (the largest kernel of the step) and of the q/k/v
+    shrink launch, issued one at a time (no overlap with neighbours) over all layers."""
+    from slora_b200 import batch_infer
+    wl, ops = run.wl, run.ops
+    dims = wl.proj_dims()
+    distinct = torch.unique(wl.ids).tolist()
+    es = 2
+    b_bytes = sum(wl.ranks[a] * dims[p][1] * es for a in distinct for p in range(3))
+    y_bytes = wl.T * sum(2 * dims[p][1] * es for p in range(3))
+    a_bytes = sum(wl.ranks[a] * dims[p][0] * es for a in distinct for p in range(3))
+    x_bytes = wl.T * dims[0][0] * es
+    ev = [[torch.cuda.Event(enable_timing=True) for _ in range(3)] for _ in range(run.L * reps)]
+    i = 0
+    for _ in range(reps):
+        for l in range(run.L):
+            p = l % run.P
+            ev[i][0].record()
+            batch_infer.shrink_multi(ops.plan, wl.ids, [0, 1, 2], ops.delta, wl.x_qkv[p], wl.pools_a[p], wl.a_start,
+                                     wl.a_len, wl.a_loc)
+            ev[i][1].record()
+            batch_infer.expand_multi(ops.plan, wl.ids, [0, 1, 2], [run.q[p], run.k[p], run.v[p]], ops.delta,
+                                     wl.pools_b[p], wl.a_start, wl.a_len, wl.a_loc, wl.a_scaling,
+                                     ops.delta[0].stride(0), wl.max_rank)
+            ev[i][2].record()
+            i += 1
+    torch.cuda.synchronize()
+    t_shrink = statistics.mean(e[0].elapsed_time(e[1]) for e in ev) * 1e-3
+    t_expand = statistics.mean(e[1].elapsed_time(e[2]) for e in ev) * 1e-3
+    out = {}
+    for name, t, nbytes in (("lora_expand_kernel(qkv)", t_expand, b_bytes + y_bytes),
+                            ("lora_shrink_kernel(qkv)", t_shrink, a_bytes + x_bytes)):
+        out[name] = {"bound": "hbm", "achieved": nbytes / t / 1e9, "peak": peak_gbs, "unit": "GB/s",
+                     "frac": nbytes / t / 1e9 / peak_gbs, "traffic": None, "kernel": name,
+                     "us_per_launch": t * 1e6, "algorithmic_bytes_per_launch": nbytes, "peak_kind": peak_kind}
+    return out
+
+
+def e2e_measure(run, steps, warmup):
+    """Steps through LoraBatchOps with activations in pinned host memory and results copied back to the host."""
+    sl, wl = run.sl, run.wl
+    L, T, H, K = run.L, wl.T, wl.spec.hidden, wl.spec.h_kv
+    dt = wl.dtype
+    dev = wl.ids.device
+    g = torch.Generator().manual_seed(77)
+    x_host = torch.randn((L, 2, T, H), generator=g, dtype=torch.float32).to(dt).pin_memory()
+    ids_host = wl.ids.cpu().pin_memory()
+    x_dev = torch.empty((L, 2, T, H), dtype=dt, device=dev)
+    ids_dev = torch.empty_like(wl.ids)
+    y_dev = torch.zeros((L, T, 2 * H + 2 * K), dtype=dt, device=dev)
+    y_host = torch.empty((L, T, 2 * H + 2 * K), dtype=dt).pin_memory()
+    ops = sl.LoraBatchOps(wl.a_start, wl.a_len, wl.a_loc, wl.a_scaling, wl.pools_a, wl.pools_b, wl.max_rank,
+                          use_pdl=not run.args.no_pdl)
+    h2d = x_host.numel() * x_host.element_size() + ids_host.numel() * 8
+    d2h = y_host.numel() * y_host.element_size()
+    times = []
+    for it in range(warmup + steps):
+        y_dev.zero_()
+        torch.cuda.synchronize()
+        t0 = torch.cuda.Event(enable_timing=True)
+        t1 = torch.cuda.Event(enable_timing=True)
+        t0.record()
+        x_dev.copy_(x_host, non_blocking=True)
+        ids_dev.copy_(ids_host, non_blocking=True)
+        ops.prepare(ids_dev, use_plan=not run.args.no_plan)
+        for l in range(L):
+            p = l % run.P
+            yl = y_dev[l]
+            ops.lora_get_qkv(p, x_dev[l, 0], yl[:, :H], yl[:, H:H + K], yl[:, H + K:H + 2 * K])
+            ops.lora_get_o(p, x_dev[l, 1], yl[:, H + 2 * K:])
+        y_host.copy_(y_dev, non_blocking=True)
+        t1.record()
+        torch.cuda.synchronize()
+        if it >= warmup:
+            times.append(t0.elapsed_time(t1) * 1e-3)
+    return sum(times), h2d, d2h
+
+
+def main():
+    args = parse_args()
+    if args.impl == "reference":
+        reference_arm(args)
+        return
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device (there is no CPU path); use --impl reference for the CPU arm")
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=device)
+    mode = args.mode
+    if mode == "auto":
+        mode = "tp" if (args.config in (4, 5) and world > 1) else "dp"
+    if mode == "tp" and world > 1:
+        from slora_b200 import tp_bench
+        tp_bench.run(args, dist, rank, world, device)
+        return
+
+    peak_gbs, peak_kind = load_peaks()
+    run = Runner(args, args.config, device, seed_shift=rank)
+    wl = run.wl
+    run.step_eager()
+    torch.cuda.synchronize()
+    run.ops.plan and run.ops.plan.check()
+    if not args.no_graph:
+        run.capture()
+    for _ in range(max(args.warmup, 3)):
+        run.step()
+    torch.cuda.synchronize()
+    if dist is not None:
+        dist.barrier()
+    torch.cuda.synchronize()
+    with ClockSampler(physical_gpu_index(local_rank)) as clocks:
+        t0 = torch.cuda.Event(enable_timing=True)
+        t1 = torch.cuda.Event(enable_timing=True)
+        t0.record()
+        for _ in range(args.steps):
+            run.step()
+        t1.record()
+        torch.cuda.synchronize()
+    elapsed = t0.elapsed_time(t1) * 1e-3
+    if dist is not None:
+        dist.barrier()
+        t = torch.tensor([elapsed], dtype=torch.float64, device=device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        elapsed = float(t.item())
+    tokens = wl.T * args.steps * world
+    value = tokens / elapsed
+    ms_per_step = elapsed / args.steps * 1e3
+    bytes_layer = wl.algorithmic_bytes_per_layer()
+    step_gbs = bytes_layer * run.L / (elapsed / args.steps) / 1e9
+
+    roof = kernel_roofline(run, peak_gbs, peak_kind)
+    e2e = None
+    if not args.no_e2e:
+        e_time, h2d, d2h = e2e_measure(run, max(3, min(args.steps, 10)), 3)
+        e_steps = max(3, min(args.steps, 10))
+        if dist is not None:
+            t = torch.tensor([e_time], dtype=torch.float64, device=device)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            e_time = float(t.item())
+        e2e = {"value": wl.T * e_steps * world / e_time, "unit": "tokens/s", "h2d_bytes_per_step": h2d,
+               "d2h_bytes_per_step": d2h, "steps": e_steps, "ms_per_step": e_time / e_steps * 1e3}
+    cpu = None
+    if rank == 0 and world == 1 and not args.no_cpu:
+        cpu, _ = run_cpu_baseline(args.config, min(wl.spec.pool_rows, 65536 if args.config != 4 else 327680),
+                                  args.cpu_seconds)
+    if rank == 0:
+        main_roof = roof["lora_expand_kernel(qkv)"]
+        line = {
+            "metric": "lora_delta_tokens_per_s", "value": value, "unit": "tokens/s", "n_gpus": world,
+            "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "f16 in, f32 accumulate", "data": "synthetic",
+            "config": {"workload": wl.spec.name, "tokens_per_gpu": wl.T, "layers": run.L, "hidden": wl.spec.hidden,
+                       "kv_width": wl.spec.h_kv, "adapters": wl.spec.n_adapters, "max_rank": wl.max_rank,
+                       "distinct_adapters_in_batch": len(torch.unique(wl.ids)), "pool_rows": wl.spec.pool_rows,
+                       "phys_layers": run.P, "parallelism": f"replicas x{world}" if world > 1 else "1 gpu",
+                       "l2": "inputs larger than L2: %d MiB of adapter rows and activations touched per step, no "
+                             "reuse between layers" % (bytes_layer * min(run.P, run.L) // 2 ** 20),
+                       "graph": not args.no_graph, "pdl": not args.no_pdl, "plan": not args.no_plan},
+            "roofline": main_roof,
+            "roofline_shrink": roof["lora_shrink_kernel(qkv)"],
+            "step_hbm": {"algorithmic_bytes_per_step": bytes_layer * run.L, "achieved": step_gbs, "peak": peak_gbs,
+                         "frac": step_gbs / peak_gbs, "unit": "GB/s", "peak_kind": peak_kind,
+                         "frac_of_nominal_8TBs": step_gbs / 8000.0},
+            "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": run.launches_per_step * args.steps,
+            "clocks": clocks.summary(),
+        }
+        print(json.dumps(line), flush=True)
+    if dist is not None:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

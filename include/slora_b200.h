@@ -1,0 +1,182 @@
+/*
+ * slora_b200 -- C ABI of the B200 (sm_100a) multi-adapter LoRA shrink/expand library.
+ *
+ * Every pointer named "device" is a CUDA device pointer borrowed for the duration of the call; the library
+ * never takes ownership and never allocates.  All calls are asynchronous on the given stream (a cudaStream_t
+ * passed as void*; NULL is the legacy default stream) and return an int status: 0 on success, a negative
+ * SLORA_ERR_* code otherwise, with a human-readable message available from slora_last_error().
+ * No call aborts, traps or synchronises the device, except where stated.
+ *
+ * Table vocabulary (the reference's InferAdapter tables, slora/server/router/model_infer/infer_adapter.py:11-39):
+ *   start[a]   offset of adapter a's first entry in loc            (a_start, int64)
+ *   ranks4[a]  4 * slot_rows of adapter a                          (a_len,   int64; slot_rows == LoRA rank r)
+ *   loc[i]     pool row index                                      (a_loc,   int64)
+ *   ids[t]     adapter slot of token t                             (req_bins / batch_req_bins, int64)
+ *   scales[a]  alpha / r, same dtype as the activations            (a_scaling)
+ * Projection p in {0,1,2,3} = {q,k,v,o} owns the slot  loc[start[a] + slot_rows*p .. + slot_rows).
+ * Pool buffers are [pool_rows, pool_stride] elements (key_buffer[l] holds A rows, value_buffer[l] holds B rows,
+ * slora/common/mem_allocator.py:229-234).
+ *
+ * Layout inside a slot: the slot's rows concatenated form a flat array; A is [slot_rows, h_in] row-major in it
+ * and B is [h_out, slot_rows*rank_mult] row-major in it.  With pool_stride == h_in (A) / == h_out (B) and
+ * rank_mult == 1 this is bit-for-bit the layout the reference kernels read
+ * (slora/csrc/bgmv/bgmv_impl.cuh:34-38 and :174-179,191); other strides serve GQA and tensor-parallel shards.
+ */
+#ifndef SLORA_B200_H_
+#define SLORA_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define SLORA_OK 0
+#define SLORA_ERR_NULL (-1)      /* required pointer is NULL */
+#define SLORA_ERR_ALIGN (-2)     /* pointer or stride not 16-byte aligned where vector access needs it */
+#define SLORA_ERR_DTYPE (-3)     /* dtype is neither SLORA_F16 nor SLORA_BF16 */
+#define SLORA_ERR_SHAPE (-4)     /* a feature size is not a positive multiple of 8, or a size is out of range */
+#define SLORA_ERR_QKVO (-5)      /* projection index outside 0..3 */
+#define SLORA_ERR_WORKSPACE (-6) /* plan workspace too small or not a plan */
+#define SLORA_ERR_LAUNCH (-7)    /* CUDA reported an error at launch; message holds cudaGetErrorString */
+#define SLORA_ERR_RANK (-8)      /* rank not supported by the expand path (needs 8,16,32,64 or 128) */
+#define SLORA_ERR_TABLE (-9)     /* slora_validate_tables found an out-of-range entry */
+
+#define SLORA_F16 0
+#define SLORA_BF16 1
+
+/* flags */
+#define SLORA_FLAG_PDL 1u /* launch with programmatic dependent launch: the kernel may start while the previous
+                             kernel on the stream drains, and prefetches adapter rows before it waits for that
+                             kernel.  Safe whenever the previous kernels on the stream do not write the pool
+                             buffers or the tables that this call reads. */
+
+/* Bits of the device status word (plan header / status argument). */
+#define SLORA_STATUS_BAD_ID 1      /* a token's adapter id was outside [0, n_adapters) - token skipped   */
+#define SLORA_STATUS_BAD_TABLE 2   /* start/ranks4/loc entry out of range - work item skipped            */
+#define SLORA_STATUS_BAD_RANK 4    /* expand met a rank outside {8,16,32,64,128} - work item skipped      */
+#define SLORA_STATUS_TIMEOUT 8     /* a bounded wait for a bulk copy ran out - work item skipped          */
+
+int slora_version(void);
+const char* slora_last_error(void); /* thread-local, valid until the next failing call on this thread */
+
+/*
+ * Drop-in for the reference's one native entry point,
+ *   dispatch_bgmv(y, x, w, start_indicies, lora_ranks, loc_indicies, indicies, qkvo, lora_scales)
+ *   (slora/csrc/lora_ops.cc:76-126).
+ * Direction is chosen as the reference does (slora/csrc/bgmv/bgmv_impl.cuh:221,232): h_in < h_out => expand
+ * (y[t,:] += scale * x[t,:r] . B), else shrink (y[t,:r] = x[t,:] . A^T, columns >= r untouched).
+ * T tokens; x is [T, h_in] and y is [T, h_out], both contiguous as in the reference.
+ */
+int slora_dispatch_bgmv(void* y, const void* x, const void* w, const int64_t* start, const int64_t* ranks4,
+                        const int64_t* loc, const int64_t* ids, int qkvo, const void* scales, int64_t T,
+                        int h_in, int h_out, int64_t pool_rows, int64_t pool_stride, int64_t n_adapters,
+                        int64_t loc_len, int dtype, void* stream);
+
+/*
+ * The two halves of dispatch_bgmv with explicit strides (replace bgmv_multi_lora_rank_shrink_kernel /
+ * bgmv_multi_lora_rank_expand_kernel, slora/csrc/bgmv/bgmv_impl.cuh:15-149 and :153-208).
+ * delta_width = number of columns of delta (the batch's maximum rank).
+ */
+int slora_bgmv_shrink(void* delta, const void* x, const void* w, const int64_t* start, const int64_t* ranks4,
+                      const int64_t* loc, const int64_t* ids, int qkvo, int64_t T, int h_in, int64_t x_stride,
+                      int64_t delta_stride, int delta_width, int64_t pool_rows, int64_t pool_stride,
+                      int64_t n_adapters, int64_t loc_len, int dtype, void* stream);
+int slora_bgmv_expand(void* y, const void* delta, const void* w, const int64_t* start, const int64_t* ranks4,
+                      const int64_t* loc, const int64_t* ids, const void* scales, int qkvo, int64_t T,
+                      int h_out, int64_t delta_stride, int delta_width, int64_t y_stride, int64_t pool_rows,
+                      int64_t pool_stride, int64_t n_adapters, int64_t loc_len, int dtype, void* stream);
+
+/*
+ * Segment (prefill) variants: request i covers tokens [seg_start[i], seg_start[i]+seg_len[i]) and uses adapter
+ * seg_adapter[i].  Replace lora_get_qkvo_fwd_shrink / lora_get_qkvo_fwd_expand
+ * (slora/models/peft/triton_kernel/lora/lora_prefill.py:139-164 and :105-136).  seg_start/seg_len are int32
+ * (the reference's b_start_loc / b_seq_len), seg_adapter int64 (req_bins).  max_seg_len bounds the grid exactly as
+ * the reference's max_input_len does.
+ */
+int slora_sgmv_shrink(void* delta, const void* x, const void* w, const int64_t* start, const int64_t* ranks4,
+                      const int64_t* loc, const int32_t* seg_start, const int32_t* seg_len,
+                      const int64_t* seg_adapter, int n_seg, int max_seg_len, int qkvo, int64_t T, int h_in,
+                      int64_t x_stride, int64_t delta_stride, int delta_width, int64_t pool_rows,
+                      int64_t pool_stride, int64_t n_adapters, int64_t loc_len, int dtype, void* stream);
+int slora_sgmv_expand(void* y, const void* delta, const void* w, const int64_t* start, const int64_t* ranks4,
+                      const int64_t* loc, const int32_t* seg_start, const int32_t* seg_len,
+                      const int64_t* seg_adapter, const void* scales, int n_seg, int max_seg_len, int qkvo,
+                      int64_t T, int h_out, int64_t delta_stride, int delta_width, int64_t y_stride,
+                      int64_t pool_rows, int64_t pool_stride, int64_t n_adapters, int64_t loc_len, int dtype,
+                      void* stream);
+
+/*
+ * Batch plan: groups the tokens of one batch by adapter once, so that every later call of the batch (all layers,
+ * all projections) reads each adapter row once per group instead of once per token.  The reference has no
+ * counterpart (it re-derives everything per token in every launch, bgmv_impl.cuh:34-38); the plan plays the role
+ * of req_bins / batch_req_bins built in LoraUnorderedBatchInfer.__init__ / forward
+ * (slora/models/peft/lora_unordered_batch_infer.py:24-38,66).
+ * The workspace is caller-owned device memory of slora_plan_workspace_bytes(T, n_adapters) bytes, 16-byte aligned.
+ * slora_plan_build launches one small kernel on the stream; the plan is valid for later calls on that stream.
+ * slora_plan_status copies the plan's status word back (synchronises the stream).
+ */
+size_t slora_plan_workspace_bytes(int64_t T, int64_t n_adapters);
+int slora_plan_build(void* workspace, size_t workspace_bytes, const int64_t* ids, int64_t T, int64_t n_adapters,
+                     void* stream);
+int slora_plan_status(const void* workspace, int* status_out, int* n_tiles_out, void* stream);
+
+/*
+ * Planned multi-projection calls.  nproj in 1..3 projections share the activations x (shrink) and the tables.
+ * plan may be NULL, in which case ids (per-token adapter ids) must be given and every token is its own group.
+ *   slora_lora_shrink_multi: delta[p][t, :r] = x[t, :] . A_{p}^T for p < nproj
+ *   slora_lora_expand_multi: y[p][t, :] += scale * delta[p][t, :r_b] . B_{p}^T
+ * delta element (t, k) of projection p is read at
+ *   delta[p] + (k / (r_b / delta_parts)) * delta_part_stride + t * delta_stride + k % (r_b / delta_parts)
+ * (delta_parts == 1: a plain [T, delta_stride] matrix; delta_parts == N: the all-gathered [N, T, r/N] buffer of an
+ * N-way tensor-parallel shrink).  rank_mult: B rank = slot_rows * rank_mult (1 except under tensor parallelism).
+ * These mirror _batch_lora_get_qkv / _batch_lora_get_o and _lora_get_qkv / _lora_get_o
+ * (slora/models/peft/lora_unordered_batch_infer.py:254-318,428-448,321-424,451-483).
+ */
+int slora_lora_shrink_multi(const void* plan, const int64_t* ids, int nproj, const int* qkvo, void* const* delta,
+                            int64_t delta_stride, int delta_width, const void* x, int64_t x_stride, int h_in,
+                            const void* pool_a, int64_t pool_rows, int64_t pool_stride, const int64_t* start,
+                            const int64_t* ranks4, const int64_t* loc, int64_t n_adapters, int64_t loc_len,
+                            int64_t T, int dtype, unsigned flags, void* stream);
+int slora_lora_expand_multi(const void* plan, const int64_t* ids, int nproj, const int* qkvo, void* const* y,
+                            const int64_t* y_stride, const int* h_out, const void* const* delta,
+                            int64_t delta_stride, int delta_width, int delta_parts, int64_t delta_part_stride,
+                            int rank_mult, const void* pool_b, int64_t pool_rows, int64_t pool_stride,
+                            const int64_t* start, const int64_t* ranks4, const int64_t* loc, const void* scales,
+                            int64_t n_adapters, int64_t loc_len, int64_t T, int dtype, unsigned flags,
+                            void* stream);
+
+/*
+ * One layer's q/k/v LoRA deltas (shrink for q,k,v then expand for q,k,v: two launches) and the o delta.
+ * Counterparts of _batch_lora_get_qkv (lora_unordered_batch_infer.py:254-318) and _batch_lora_get_o (:428-448)
+ * without the base torch.mm and rotary calls.  delta_* are caller scratch [T, delta_stride] like self.delta[0..2]
+ * (:68-69,75-76); they need not be zeroed (only columns < r are written and read).
+ */
+int slora_batch_lora_qkv(const void* plan, const int64_t* ids, void* q, void* k, void* v, int64_t q_stride,
+                         int64_t k_stride, int64_t v_stride, int h_out_q, int h_out_kv, const void* x,
+                         int64_t x_stride, int h_in, const void* pool_a, const void* pool_b, int64_t pool_rows,
+                         int64_t pool_stride, const int64_t* start, const int64_t* ranks4, const int64_t* loc,
+                         const void* scales, int64_t n_adapters, int64_t loc_len, void* delta_q, void* delta_k,
+                         void* delta_v, int64_t delta_stride, int delta_width, int64_t T, int dtype,
+                         unsigned flags, void* stream);
+int slora_batch_lora_o(const void* plan, const int64_t* ids, void* o, int64_t o_stride, int h_out, const void* x,
+                       int64_t x_stride, int h_in, const void* pool_a, const void* pool_b, int64_t pool_rows,
+                       int64_t pool_stride, const int64_t* start, const int64_t* ranks4, const int64_t* loc,
+                       const void* scales, int64_t n_adapters, int64_t loc_len, void* delta, int64_t delta_stride,
+                       int delta_width, int64_t T, int dtype, unsigned flags, void* stream);
+
+/*
+ * Debug check of the tables (the reference has none; its kernels read whatever the tables say).
+ * Launches one kernel that range-checks start/ranks4/loc/ids and writes report[0] = number of bad entries,
+ * report[1] = kind of the first one found (1 ids, 2 start/ranks4, 3 loc), report[2] = its index.
+ * report is device memory (4 x int32).  Asynchronous; the caller reads report after synchronising.
+ */
+int slora_validate_tables(const int64_t* start, const int64_t* ranks4, const int64_t* loc, const int64_t* ids,
+                          int64_t n_adapters, int64_t loc_len, int64_t T, int64_t pool_rows, int32_t* report,
+                          void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* SLORA_B200_H_ */

@@ -1,0 +1,160 @@
+"""The LoRA half of the reference's batch-infer layer, as two fused calls per transformer layer.
+
+``LoraUnorderedBatchInfer`` (``slora/models/peft/lora_unordered_batch_infer.py:16-483``) issues, per layer,
+``torch.mm`` + shrink + expand for q, k and v and later for o: eight ``dispatch_bgmv`` launches per layer.
+:class:`LoraBatchOps` keeps that call structure (``lora_get_qkv`` where the reference has
+``_batch_lora_get_qkv`` / ``_lora_get_qkv``, ``lora_get_o`` for ``_batch_lora_get_o`` / ``_lora_get_o``) but each
+call is one q/k/v-fused shrink launch plus one fused expand launch, working from a :class:`BatchPlan` that groups
+the batch's tokens by adapter once per forward instead of per launch.  The base ``torch.mm`` and the rotary
+embedding stay with the caller, exactly where the reference has them.
+"""
+from __future__ import annotations
+
+import ctypes
+
+import torch
+
+from . import _lib
+
+
+class BatchPlan:
+    """Tokens of one batch grouped by adapter (device-resident; built by one small kernel).
+
+    Plays the role of ``req_bins`` / ``batch_req_bins`` (``lora_unordered_batch_infer.py:24-38,66``): it is
+    derived from the per-token adapter ids once per forward and shared by every layer and projection.
+    """
+
+    def __init__(self, token_adapter_ids: torch.Tensor, n_adapters: int, workspace: torch.Tensor | None = None):
+        _lib.require_cuda(token_adapter_ids)
+        if token_adapter_ids.dtype != torch.int64 or token_adapter_ids.dim() != 1:
+            raise RuntimeError("token_adapter_ids must be a 1-D int64 tensor")
+        self.ids = token_adapter_ids.contiguous()
+        self.T = self.ids.numel()
+        self.n_adapters = int(n_adapters)
+        need = _lib.lib.slora_plan_workspace_bytes(self.T, self.n_adapters)
+        if workspace is None:
+            workspace = torch.empty((need + 3) // 4, dtype=torch.int32, device=self.ids.device)
+        elif workspace.numel() * workspace.element_size() < need:
+            raise RuntimeError(f"plan workspace too small: {workspace.numel() * workspace.element_size()} < {need}")
+        self.workspace = workspace
+        _lib.check(_lib.lib.slora_plan_build(workspace.data_ptr(), workspace.numel() * workspace.element_size(),
+                                             self.ids.data_ptr(), self.T, self.n_adapters,
+                                             _lib.current_stream_ptr()))
+
+    @property
+    def ptr(self) -> int:
+        return self.workspace.data_ptr()
+
+    def status(self):
+        """``(status_bits, n_tiles)`` -- synchronises the current stream."""
+        st, nt = ctypes.c_int(0), ctypes.c_int(0)
+        _lib.check(_lib.lib.slora_plan_status(self.ptr, ctypes.byref(st), ctypes.byref(nt),
+                                              _lib.current_stream_ptr()))
+        return st.value, nt.value
+
+    def check(self):
+        st, _ = self.status()
+        if st:
+            what = ", ".join(v for k, v in _lib.STATUS_BITS.items() if st & k)
+            raise RuntimeError(f"slora_b200: device reported: {what} (status {st})")
+
+
+class LoraBatchOps:
+    """Per-forward LoRA operator: shrink+expand for q/k/v and for o of one layer, in place on the base outputs.
+
+    Parameters mirror what ``LoraUnorderedBatchInfer.__init__`` reads from ``infer_adapter``
+    (``lora_unordered_batch_infer.py:26-38``): the four tables and the per-layer pool buffers.
+    ``max_lora_dim`` is the width of the delta buffers (``self.max_lora_dim`` there).
+    """
+
+    def __init__(self, a_start, a_len, a_loc, a_scaling, key_buffer, value_buffer, max_lora_dim, use_pdl=True):
+        _lib.require_cuda(a_start, a_len, a_loc, a_scaling)
+        self.a_start, self.a_len, self.a_loc, self.a_scaling = a_start, a_len, a_loc, a_scaling
+        self.key_buffer, self.value_buffer = key_buffer, value_buffer
+        self.max_lora_dim = int(max_lora_dim)
+        self.flags = _lib.FLAG_PDL if use_pdl else 0
+        self.plan = None
+        self.delta = None
+
+    @classmethod
+    def from_infer_adapter(cls, infer_adapter, max_lora_dim, use_pdl=True):
+        mm = infer_adapter.mem_manager
+        return cls(infer_adapter.a_start, infer_adapter.a_len, infer_adapter.a_loc, infer_adapter.a_scaling,
+                   mm.key_buffer, mm.value_buffer, max_lora_dim, use_pdl)
+
+    def prepare(self, token_adapter_ids, use_plan=True):
+        """Start a forward: ``token_adapter_ids`` is ``req_bins`` (decode) or ``batch_req_bins`` (prefill).
+
+        Allocates the three delta buffers the reference allocates in ``forward`` (``:68-69,75-76``) and builds the
+        plan.  ``use_plan=False`` keeps every token its own group (the reference's behaviour).
+        """
+        self.ids = token_adapter_ids.contiguous()
+        T = self.ids.numel()
+        dtype = self.key_buffer[0].dtype
+        self.delta = [torch.zeros((T, self.max_lora_dim), dtype=dtype, device=self.ids.device) for _ in range(3)]
+        self.plan = BatchPlan(self.ids, self.a_start.numel()) if use_plan else None
+        return self
+
+    def _common(self, layer_id):
+        kb, vb = self.key_buffer[layer_id], self.value_buffer[layer_id]
+        if kb.stride(0) != vb.stride(0):
+            raise RuntimeError("A and B pools must share one row stride")
+        return kb, vb, kb.size(0), kb.stride(0)
+
+    def lora_get_qkv(self, layer_id, x, q, k, v):
+        """``q += lora_q(x)``, ``k += lora_k(x)``, ``v += lora_v(x)`` (2-D views ``[T, h]``), in place."""
+        kb, vb, rows, stride = self._common(layer_id)
+        _lib.require_cuda(x, q, k, v)
+        if k.size(1) != v.size(1):
+            raise RuntimeError("k and v must have the same width")
+        d = self.delta
+        _lib.check(_lib.lib.slora_batch_lora_qkv(
+            0 if self.plan is None else self.plan.ptr, self.ids.data_ptr(), q.data_ptr(), k.data_ptr(), v.data_ptr(),
+            q.stride(0), k.stride(0), v.stride(0), q.size(1), k.size(1), x.data_ptr(), x.stride(0), x.size(1),
+            kb.data_ptr(), vb.data_ptr(), rows, stride, self.a_start.data_ptr(), self.a_len.data_ptr(),
+            self.a_loc.data_ptr(), self.a_scaling.data_ptr(), self.a_start.numel(), self.a_loc.numel(),
+            d[0].data_ptr(), d[1].data_ptr(), d[2].data_ptr(), d[0].stride(0), self.max_lora_dim, x.size(0),
+            _lib.dtype_code(x.dtype), self.flags, _lib.current_stream_ptr()))
+        return q
+
+    def lora_get_o(self, layer_id, x, o):
+        """``o += lora_o(x)`` in place (``x`` is the attention output, ``[T, H]``)."""
+        kb, vb, rows, stride = self._common(layer_id)
+        _lib.require_cuda(x, o)
+        d = self.delta[0]  # the reference reuses delta[0] for o (:438)
+        _lib.check(_lib.lib.slora_batch_lora_o(
+            0 if self.plan is None else self.plan.ptr, self.ids.data_ptr(), o.data_ptr(), o.stride(0), o.size(1),
+            x.data_ptr(), x.stride(0), x.size(1), kb.data_ptr(), vb.data_ptr(), rows, stride,
+            self.a_start.data_ptr(), self.a_len.data_ptr(), self.a_loc.data_ptr(), self.a_scaling.data_ptr(),
+            self.a_start.numel(), self.a_loc.numel(), d.data_ptr(), d.stride(0), self.max_lora_dim, x.size(0),
+            _lib.dtype_code(x.dtype), self.flags, _lib.current_stream_ptr()))
+        return o
+
+
+def shrink_multi(plan, ids, qkvo, deltas, x, pool_a, a_start, a_len, a_loc, flags=0):
+    """Planned shrink of up to three projections that share ``x`` (C entry ``slora_lora_shrink_multi``)."""
+    n = len(qkvo)
+    q_arr = (ctypes.c_int * n)(*qkvo)
+    d_arr = (ctypes.c_void_p * n)(*[d.data_ptr() for d in deltas])
+    _lib.check(_lib.lib.slora_lora_shrink_multi(
+        0 if plan is None else plan.ptr, _lib.ptr(ids), n, q_arr, d_arr, deltas[0].stride(0), deltas[0].size(1),
+        x.data_ptr(), x.stride(0), x.size(1), pool_a.data_ptr(), pool_a.size(0), pool_a.stride(0),
+        a_start.data_ptr(), a_len.data_ptr(), a_loc.data_ptr(), a_start.numel(), a_loc.numel(), x.size(0),
+        _lib.dtype_code(x.dtype), flags, _lib.current_stream_ptr()))
+
+
+def expand_multi(plan, ids, qkvo, ys, deltas, pool_b, a_start, a_len, a_loc, a_scaling, delta_stride, delta_width,
+                 delta_parts=1, delta_part_stride=0, rank_mult=1, flags=0):
+    """Planned expand of up to three projections (C entry ``slora_lora_expand_multi``)."""
+    n = len(qkvo)
+    q_arr = (ctypes.c_int * n)(*qkvo)
+    y_arr = (ctypes.c_void_p * n)(*[y.data_ptr() for y in ys])
+    ys_arr = (ctypes.c_int64 * n)(*[y.stride(0) for y in ys])
+    ho_arr = (ctypes.c_int * n)(*[y.size(1) for y in ys])
+    d_arr = (ctypes.c_void_p * n)(*[d.data_ptr() for d in deltas])
+    T = ys[0].size(0)
+    _lib.check(_lib.lib.slora_lora_expand_multi(
+        0 if plan is None else plan.ptr, _lib.ptr(ids), n, q_arr, y_arr, ys_arr, ho_arr, d_arr, delta_stride,
+        delta_width, delta_parts, delta_part_stride, rank_mult, pool_b.data_ptr(), pool_b.size(0), pool_b.stride(0),
+        a_start.data_ptr(), a_len.data_ptr(), a_loc.data_ptr(), a_scaling.data_ptr(), a_start.numel(),
+        a_loc.numel(), T, _lib.dtype_code(ys[0].dtype), flags, _lib.current_stream_ptr()))

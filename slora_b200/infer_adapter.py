@@ -1,0 +1,160 @@
+"""Adapter index tables over the Unified-Paging pool.
+
+Same role and public fields as the reference's ``InferAdapter``
+(``slora/server/router/model_infer/infer_adapter.py:11-250``): ``a_loc`` lists the pool rows of every loaded
+adapter, ``a_start[i]`` / ``a_len[i]`` (= ``4 * r``) delimit adapter ``i``'s run in it, ``a_scaling[i]`` is
+``alpha / r``; within a run the rows of projection ``p`` (q, k, v, o) are ``a_loc[a_start + p*r : a_start + (p+1)*r]``.
+``load_adapters`` allocates rows and copies each layer's ``w_combined[0]`` (A rows) into ``key_buffer[l]`` and
+``w_combined[1]`` (B rows) into ``value_buffer[l]``; ``offload_adapters`` frees rows and compacts the tables.
+
+Mechanism differs from the reference: table entries are assembled on the host and uploaded in one copy per table
+(the reference writes them element by element from Python), and compaction is a single gather with an index vector
+(the reference launches a Triton variable-length copy).  An adapter object needs ``lora_dir``, ``r``, ``scaling``
+and ``layers[l]`` with ``w_combined`` (``[2, 4r, heads, head_dim]``) plus optional ``load_to_gpu`` /
+``offload_from_gpu`` (``slora/models/peft/layer_weights/lora_layer_weight.py:230-261``).
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Any, Dict, List
+
+import torch
+
+
+@dataclass
+class InferAdapter:
+    adapter_dirs: List[str]
+    a_loc: torch.Tensor
+    a_start: torch.Tensor
+    a_len: torch.Tensor
+    a_scaling: torch.Tensor
+    mem_manager: Any
+    idx_map: Dict[str, int]
+    prefetch_tag: Dict[str, int]
+    cur_tag: int
+    prefetch_stream: Any
+
+    @classmethod
+    def init(cls, mem_manager, prefetch_stream=None):
+        dev = mem_manager.mem_state.device
+        return cls(
+            adapter_dirs=[],
+            a_loc=torch.empty(0, dtype=torch.long, device=dev),
+            a_start=torch.empty(0, dtype=torch.long, device=dev),
+            a_len=torch.empty(0, dtype=torch.long, device=dev),
+            a_scaling=torch.empty(0, dtype=mem_manager.dtype, device=dev),
+            mem_manager=mem_manager,
+            idx_map={},
+            prefetch_tag={},
+            cur_tag=0,
+            prefetch_stream=prefetch_stream,
+        )
+
+    # -- copy one adapter's rows into the pool ----------------------------------------------------------
+    def _copy_rows(self, adapter, loc, prefetch):
+        mm = self.mem_manager
+        for layer_id, layer in enumerate(adapter.layers):
+            if hasattr(layer, "load_to_gpu"):
+                layer.load_to_gpu(prefetch=prefetch)
+            w = layer.w_combined
+            if w.device != loc.device:
+                w = w.to(loc.device, non_blocking=True)
+            mm.key_buffer[layer_id][loc] = w[0].reshape(len(loc), mm.head_num, mm.head_dim)
+            mm.value_buffer[layer_id][loc] = w[1].reshape(len(loc), mm.head_num, mm.head_dim)
+            if hasattr(layer, "offload_from_gpu"):
+                layer.offload_from_gpu()
+
+    def load_adapters(self, adapters, prefetch=False):
+        """Make every adapter in ``adapters`` resident (``infer_adapter.py:92-171``).
+
+        With ``prefetch=True`` adapters are tagged as wanted by the next batch and loading stops when the pool is
+        full instead of raising.
+        """
+        if len(adapters) == 0:
+            return
+        new_adapters, tot_size = [], 0
+        if prefetch:
+            self.cur_tag ^= 1
+            capacity = self.mem_manager.can_use_mem_size
+        for adapter in adapters:
+            if adapter is None:
+                continue
+            if prefetch:
+                self.prefetch_tag[adapter.lora_dir] = self.cur_tag
+            if adapter.lora_dir in self.idx_map or any(adapter.lora_dir == a.lora_dir for a in new_adapters):
+                continue
+            if prefetch and tot_size + adapter.r * 4 > capacity:
+                break
+            new_adapters.append(adapter)
+            tot_size += adapter.r * 4
+        if not new_adapters:
+            return
+        new_loc = self.mem_manager.alloc(tot_size)
+        dev = new_loc.device
+        loc_offset = self.a_loc.numel()
+        starts, lens, cum = [], [], 0
+        for adapter in new_adapters:
+            self.idx_map[adapter.lora_dir] = len(self.adapter_dirs)
+            self.adapter_dirs.append(adapter.lora_dir)
+            starts.append(loc_offset + cum)
+            lens.append(adapter.r * 4)
+            cum += adapter.r * 4
+        self.a_start = torch.cat((self.a_start, torch.tensor(starts, dtype=torch.long, device=dev)))
+        self.a_len = torch.cat((self.a_len, torch.tensor(lens, dtype=torch.long, device=dev)))
+        self.a_loc = torch.cat((self.a_loc, new_loc.to(torch.long)))
+        self.a_scaling = torch.cat((self.a_scaling, torch.tensor([a.scaling for a in new_adapters],
+                                                                 dtype=self.a_scaling.dtype, device=dev)))
+        use_stream = prefetch and self.prefetch_stream is not None and dev.type == "cuda"
+        ctx = torch.cuda.stream(self.prefetch_stream) if use_stream else _NullCtx()
+        with ctx:
+            rows = new_loc.clone() if use_stream else new_loc
+            for adapter, s, n in zip(new_adapters, starts, lens):
+                self._copy_rows(adapter, rows[s - loc_offset: s - loc_offset + n], prefetch)
+
+    def offload_adapters(self, reserve_adapter_dirs):
+        """Drop every adapter not in ``reserve_adapter_dirs`` (and not tagged by the latest prefetch), free its rows
+        and compact the tables (``infer_adapter.py:186-250``)."""
+        if len(reserve_adapter_dirs) == len(self.adapter_dirs):
+            return
+        dev = self.a_loc.device
+        if len(reserve_adapter_dirs) == 0:
+            self.mem_manager.free(self.a_loc)
+            self.adapter_dirs = []
+            self.a_loc = torch.empty(0, dtype=torch.long, device=dev)
+            self.a_start = torch.empty(0, dtype=torch.long, device=dev)
+            self.a_len = torch.empty(0, dtype=torch.long, device=dev)
+            self.a_scaling = torch.empty(0, dtype=self.a_scaling.dtype, device=dev)
+            self.idx_map = {}
+            return
+        reserve = set(reserve_adapter_dirs)
+        keep = [i for i, d in enumerate(self.adapter_dirs)
+                if d in reserve or self.prefetch_tag.get(d, None) == self.cur_tag]
+        if len(keep) == len(self.adapter_dirs):
+            return
+        starts = self.a_start.tolist()
+        lens = self.a_len.tolist()
+        keep_set = set(keep)
+        drop_rows = [torch.arange(starts[i], starts[i] + lens[i]) for i in range(len(starts)) if i not in keep_set]
+        keep_rows = [torch.arange(starts[i], starts[i] + lens[i]) for i in keep]
+        self.mem_manager.free(self.a_loc[torch.cat(drop_rows).to(dev)])
+        gather = torch.cat(keep_rows).to(dev) if keep_rows else torch.empty(0, dtype=torch.long, device=dev)
+        new_lens = [lens[i] for i in keep]
+        new_starts, cum = [], 0
+        for n in new_lens:
+            new_starts.append(cum)
+            cum += n
+        keep_t = torch.tensor(keep, dtype=torch.long, device=dev)
+        self.a_loc = self.a_loc[gather]
+        self.a_scaling = self.a_scaling[keep_t]
+        self.a_len = torch.tensor(new_lens, dtype=torch.long, device=dev)
+        self.a_start = torch.tensor(new_starts, dtype=torch.long, device=dev)
+        self.adapter_dirs = [self.adapter_dirs[i] for i in keep]
+        self.idx_map = {d: i for i, d in enumerate(self.adapter_dirs)}
+
+
+class _NullCtx:
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *exc):
+        return False

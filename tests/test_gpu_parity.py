@@ -1,0 +1,258 @@
+"""Parity of the CUDA path (through the C ABI) with the CPU oracle on identical seeded inputs.  Needs a B200."""
+import numpy as np
+import pytest
+import torch
+
+import slora_b200 as sl
+from slora_b200 import batch_infer
+from slora_b200.workloads import build_workload, make_tables
+from tests.helpers import assert_parity, oracle_layer, orc
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+def _dispatch_layer(w, layer=0, y_init=None):
+    """q,k,v,o deltas with eight dispatch_bgmv calls, the reference's call pattern
+    (lora_unordered_batch_infer.py:254-318,428-448)."""
+    outs, deltas = [], []
+    R = w.max_rank
+    for p, (h_in, h_out) in enumerate(w.proj_dims()):
+        x = w.x_o[layer] if p == 3 else w.x_qkv[layer]
+        delta = torch.zeros((w.T, R), dtype=w.dtype, device=DEV)
+        y = torch.zeros((w.T, h_out), dtype=w.dtype, device=DEV) if y_init is None else y_init[p].clone()
+        ka = w.pools_a[layer].view(w.pools_a[layer].shape[0], 1, -1)
+        vb = w.pools_b[layer].view(w.pools_b[layer].shape[0], 1, -1)
+        sl.dispatch_bgmv(delta, x, ka, w.a_start, w.a_len, w.a_loc, w.ids, p, w.a_scaling)
+        sl.dispatch_bgmv(y, delta, vb, w.a_start, w.a_len, w.a_loc, w.ids, p, w.a_scaling)
+        outs.append(y)
+        deltas.append(delta)
+    torch.cuda.synchronize()
+    return outs, deltas
+
+
+def _fused_layer(w, layer=0, use_plan=True, use_pdl=True):
+    ops = sl.LoraBatchOps(w.a_start, w.a_len, w.a_loc, w.a_scaling, w.pools_a, w.pools_b, w.max_rank, use_pdl)
+    ops.prepare(w.ids, use_plan=use_plan)
+    H, K = w.spec.hidden, w.spec.h_kv
+    q = torch.zeros((w.T, H), dtype=w.dtype, device=DEV)
+    k = torch.zeros((w.T, K), dtype=w.dtype, device=DEV)
+    v = torch.zeros((w.T, K), dtype=w.dtype, device=DEV)
+    o = torch.zeros((w.T, H), dtype=w.dtype, device=DEV)
+    ops.lora_get_qkv(layer, w.x_qkv[layer], q, k, v)
+    ops.lora_get_o(layer, w.x_o[layer], o)
+    torch.cuda.synchronize()
+    if ops.plan is not None:
+        ops.plan.check()
+    return [q, k, v, o]
+
+
+def test_config1_dispatch_bgmv():
+    wl = build_workload(1)
+    ref = oracle_layer(wl)
+    outs, deltas = _dispatch_layer(wl.to(DEV))
+    for p in range(4):
+        assert_parity(outs[p], ref[p], what=f"cfg1 proj {p}")
+        x = wl.x_o[0] if p == 3 else wl.x_qkv[0]
+        dref = orc.lora_shrink_ref(x, wl.pools_a[0], wl.a_start, wl.a_len, wl.a_loc, wl.ids, p)
+        assert_parity(deltas[p], dref, what=f"cfg1 shrink {p}")
+
+
+def test_config1_against_committed_golden_vectors():
+    import json, os
+    from tests.helpers import ROOT
+    g = np.load(os.path.join(ROOT, "tests", "golden", "cfg1_oracle.npz"))
+    cols = json.load(open(os.path.join(ROOT, "tests", "golden", "cfg1_oracle.json")))["columns"]
+    outs = _fused_layer(build_workload(1).to(DEV))
+    for p in range(4):
+        assert_parity(outs[p][:, cols], g[f"delta_p{p}"], what=f"golden proj {p}")
+
+
+@pytest.mark.parametrize("rank", [8, 16, 32, 64, 128])
+@pytest.mark.parametrize("hidden", [1024, 5120])
+def test_uniform_rank_dispatch(rank, hidden):
+    wl = build_workload(2, pool_rows=4096, n_adapters=6, decode_tokens=37, hidden=hidden, rank_choices=(rank,))
+    ref = oracle_layer(wl)
+    outs, _ = _dispatch_layer(wl.to(DEV))
+    for p in range(4):
+        assert_parity(outs[p], ref[p], what=f"r={rank} H={hidden} proj {p}")
+
+
+@pytest.mark.parametrize("use_plan,use_pdl", [(True, True), (True, False), (False, True)])
+def test_mixed_ranks_fused(use_plan, use_pdl):
+    wl = build_workload(3, pool_rows=8192, n_adapters=40, decode_tokens=60, prefill=("seqs", 3, 5, 40), hidden=2048)
+    ref = oracle_layer(wl)
+    outs = _fused_layer(wl.to(DEV), use_plan=use_plan, use_pdl=use_pdl)
+    for p in range(4):
+        assert_parity(outs[p], ref[p], what=f"mixed proj {p}")
+
+
+def test_config2_shape_small_pool():
+    """S1-shaped decode batch (1000 rank-8 adapters, 256 Zipf tokens, hidden 4096) over a 65536-row pool."""
+    wl = build_workload(2, pool_rows=65536)
+    ref = oracle_layer(wl)
+    w = wl.to(DEV)
+    outs = _fused_layer(w)
+    for p in range(4):
+        assert_parity(outs[p], ref[p], what=f"cfg2 proj {p}")
+    outs2, _ = _dispatch_layer(w)
+    for p in range(4):
+        # planned and per-token paths do the same arithmetic per token: bit-identical results
+        assert torch.equal(outs[p], outs2[p])
+
+
+def test_bf16():
+    wl = build_workload(3, dtype=torch.bfloat16, pool_rows=8192, n_adapters=30, decode_tokens=50,
+                        prefill=("seqs", 2, 5, 30), hidden=1024)
+    ref = oracle_layer(wl)
+    outs = _fused_layer(wl.to(DEV))
+    for p in range(4):
+        assert_parity(outs[p], ref[p], dtype=torch.bfloat16, what=f"bf16 proj {p}")
+
+
+def test_expand_accumulates_into_y_and_leaves_other_columns():
+    wl = build_workload(2, pool_rows=4096, n_adapters=8, decode_tokens=20, hidden=1024, rank_choices=(8, 16))
+    w = wl.to(DEV)
+    g = torch.Generator().manual_seed(5)
+    y0 = [torch.randn((wl.T, ho), generator=g).to(wl.dtype) for _, ho in wl.proj_dims()]
+    outs, _ = _dispatch_layer(w, y_init=[y.to(DEV) for y in y0])
+    ref = oracle_layer(wl)
+    for p in range(4):
+        got_delta = outs[p].float().cpu() - y0[p].float()
+        # the sum is rounded to fp16 at |y| ~ 1, i.e. absolute error up to 2^-11 per element
+        assert (got_delta - torch.from_numpy(ref[p])).abs().max() < 2e-3
+    # shrink writes only columns < r of each token's row
+    sentinel = torch.full((wl.T, wl.max_rank), 7.0, dtype=wl.dtype, device=DEV)
+    ka = w.pools_a[0].view(-1, 1, 1024)
+    sl.dispatch_bgmv(sentinel, w.x_qkv[0], ka, w.a_start, w.a_len, w.a_loc, w.ids, 0, w.a_scaling)
+    torch.cuda.synchronize()
+    for t in range(wl.T):
+        r = wl.ranks[int(wl.ids[t])]
+        assert (sentinel[t, r:] == 7.0).all()
+        assert not (sentinel[t, :r] == 7.0).all()
+
+
+def test_segment_entry_points():
+    """lora_get_qkvo_fwd_shrink / expand (the reference's Triton prefill API) over request segments."""
+    wl = build_workload(3, pool_rows=8192, n_adapters=20, decode_tokens=0, prefill=("seqs", 5, 3, 70), hidden=1024)
+    w = wl.to(DEV)
+    seg = wl.segments
+    b_start = torch.tensor([s for s, _, _ in seg], dtype=torch.int32, device=DEV)
+    b_len = torch.tensor([n for _, n, _ in seg], dtype=torch.int32, device=DEV)
+    req_bins = torch.tensor([a for _, _, a in seg], dtype=torch.int64, device=DEV)
+    max_len = max(n for _, n, _ in seg)
+    ref = oracle_layer(wl)
+    for p in range(4):
+        x = w.x_o[0] if p == 3 else w.x_qkv[0]
+        delta = torch.zeros((wl.T, wl.max_rank), dtype=wl.dtype, device=DEV)
+        y = torch.zeros((wl.T, 1024), dtype=wl.dtype, device=DEV)
+        sl.lora_get_qkvo_fwd_shrink(x, w.pools_a[0], delta, w.a_loc, w.a_start, w.a_len, b_start, b_len, req_bins,
+                                    1024, p, wl.max_rank, max_len)
+        sl.lora_get_qkvo_fwd_expand(delta, w.pools_b[0], y, w.a_scaling, w.a_loc, w.a_start, w.a_len, b_start, b_len,
+                                    req_bins, 1024, p, wl.max_rank, max_len)
+        torch.cuda.synchronize()
+        assert_parity(y, ref[p], what=f"segments proj {p}")
+
+
+def test_gqa_narrow_kv_over_wide_pool_rows():
+    """k/v output width 256 with pool rows of 1024 elements (the GQA case the reference cannot express)."""
+    wl = build_workload(5, pool_rows=4096, n_adapters=5, decode_tokens=40, hidden=1024, h_kv=256, rank_choices=(16, 64))
+    ref = oracle_layer(wl)
+    outs = _fused_layer(wl.to(DEV))
+    for p in range(4):
+        assert outs[p].shape[1] == (256 if p in (1, 2) else 1024)
+        assert_parity(outs[p], ref[p], what=f"gqa proj {p}")
+
+
+def test_expand_reads_all_gathered_delta_parts():
+    """Expand with the delta laid out as the all-gather of an N-way rank-sharded shrink: [N, T, r/N]."""
+    wl = build_workload(2, pool_rows=4096, n_adapters=6, decode_tokens=30, hidden=1024, rank_choices=(16, 32))
+    w = wl.to(DEV)
+    N, R = 4, wl.max_rank
+    p = 0
+    dref = orc.lora_shrink_ref(wl.x_qkv[0], wl.pools_a[0], wl.a_start, wl.a_len, wl.a_loc, wl.ids, p)
+    parts = torch.zeros((N, wl.T, R // N), dtype=wl.dtype)
+    for t in range(wl.T):
+        r = wl.ranks[int(wl.ids[t])]
+        rs = r // N
+        for g in range(N):
+            parts[g, t, :rs] = torch.from_numpy(dref[t, g * rs:(g + 1) * rs]).to(wl.dtype)
+    parts = parts.to(DEV)
+    y = torch.zeros((wl.T, 1024), dtype=wl.dtype, device=DEV)
+    plan = batch_infer.BatchPlan(w.ids, w.a_start.numel())
+    batch_infer.expand_multi(plan, w.ids, [p], [y], [parts], w.pools_b[0], w.a_start, w.a_len, w.a_loc, w.a_scaling,
+                             delta_stride=R // N, delta_width=R // N, delta_parts=N, delta_part_stride=wl.T * (R // N))
+    torch.cuda.synchronize()
+    plan.check()
+    assert_parity(y, oracle_layer(wl)[p], what="gathered delta")
+
+
+def test_empty_batch_and_bad_ids():
+    wl = build_workload(2, pool_rows=4096, n_adapters=6, decode_tokens=16, hidden=1024)
+    w = wl.to(DEV)
+    # empty batch: every entry point returns without launching
+    e_ids = torch.empty(0, dtype=torch.int64, device=DEV)
+    e_x = torch.empty((0, 1024), dtype=wl.dtype, device=DEV)
+    e_d = torch.empty((0, 8), dtype=wl.dtype, device=DEV)
+    sl.dispatch_bgmv(e_d, e_x, w.pools_a[0].view(-1, 1, 1024), w.a_start, w.a_len, w.a_loc, e_ids, 0, w.a_scaling)
+    # a token with an adapter id outside the tables is skipped and reported, the others are computed
+    ids = w.ids.clone()
+    ids[3] = 99
+    ids[7] = -1
+    ops = sl.LoraBatchOps(w.a_start, w.a_len, w.a_loc, w.a_scaling, w.pools_a, w.pools_b, wl.max_rank)
+    ops.prepare(ids)
+    o = torch.zeros((wl.T, 1024), dtype=wl.dtype, device=DEV)
+    ops.lora_get_o(0, w.x_o[0], o)
+    torch.cuda.synchronize()
+    st, n_tiles = ops.plan.status()
+    assert st & 1 and n_tiles > 0
+    with pytest.raises(RuntimeError):
+        ops.plan.check()
+    ref = oracle_layer(wl)[3]
+    keep = [t for t in range(wl.T) if t not in (3, 7)]
+    assert_parity(o[keep], ref[keep], what="valid tokens")
+    assert (o[3] == 0).all() and (o[7] == 0).all()
+    assert sl.validate_tables(w.a_start, w.a_len, w.a_loc, ids, 4096)[0] == 2
+    assert sl.validate_tables(w.a_start, w.a_len, w.a_loc, w.ids, 4096) == (0, 0, 0)
+    bad_loc = w.a_loc.clone()
+    bad_loc[5] = 4096
+    n_bad, kind, index = sl.validate_tables(w.a_start, w.a_len, bad_loc, w.ids, 4096)
+    assert (n_bad, kind, index) == (1, 3, 5)
+
+
+def test_out_of_range_pool_row_is_skipped_not_read():
+    wl = build_workload(2, pool_rows=4096, n_adapters=4, decode_tokens=12, hidden=1024)
+    w = wl.to(DEV)
+    bad_loc = w.a_loc.clone()
+    a = int(wl.ids[0])
+    bad_loc[int(wl.a_start[a])] = 1 << 40  # first q row of that adapter
+    ops = sl.LoraBatchOps(w.a_start, w.a_len, bad_loc, w.a_scaling, w.pools_a, w.pools_b, wl.max_rank)
+    ops.prepare(w.ids)
+    o = torch.zeros((wl.T, 1024), dtype=wl.dtype, device=DEV)
+    q = torch.zeros((wl.T, 1024), dtype=wl.dtype, device=DEV)
+    k, v = torch.zeros_like(q), torch.zeros_like(q)
+    ops.lora_get_qkv(0, w.x_qkv[0], q, k, v)
+    torch.cuda.synchronize()
+    assert ops.plan.status()[0] & 2
+    ref = oracle_layer(wl)
+    other = [t for t in range(wl.T) if int(wl.ids[t]) != a]
+    assert_parity(k[other], ref[1][other], what="unaffected tokens")
+
+
+def test_unsupported_inputs_raise():
+    wl = build_workload(2, pool_rows=4096, n_adapters=4, decode_tokens=8, hidden=1024)
+    w = wl.to(DEV)
+    ka = w.pools_a[0].view(-1, 1, 1024)
+    d = torch.zeros((wl.T, 8), dtype=wl.dtype, device=DEV)
+    with pytest.raises(RuntimeError, match="No suitable kernel"):
+        sl.dispatch_bgmv(d.float(), w.x_qkv[0].float(), ka.float(), w.a_start, w.a_len, w.a_loc, w.ids, 0,
+                         w.a_scaling.float())
+    with pytest.raises(RuntimeError, match="contiguous"):
+        sl.dispatch_bgmv(d, w.x_qkv[0][:, ::2], ka, w.a_start, w.a_len, w.a_loc, w.ids, 0, w.a_scaling)
+    with pytest.raises(RuntimeError, match="CUDA"):
+        sl.dispatch_bgmv(d.cpu(), w.x_qkv[0], ka, w.a_start, w.a_len, w.a_loc, w.ids, 0, w.a_scaling)
+    with pytest.raises(RuntimeError):
+        sl.dispatch_bgmv(d, w.x_qkv[0], ka, w.a_start, w.a_len, w.a_loc, w.ids, 4, w.a_scaling)
+    x_odd = torch.zeros((wl.T, 1020), dtype=wl.dtype, device=DEV)
+    with pytest.raises(RuntimeError, match="No suitable kernel"):
+        sl.dispatch_bgmv(d, x_odd, ka, w.a_start, w.a_len, w.a_loc, w.ids, 0, w.a_scaling)
