@@ -1048,6 +1048,7 @@ int slora_dispatch_bgmv(void* y, const void* x, const void* w, const int64_t* st
                         const int64_t* loc, const int64_t* ids, int qkvo, const void* scales, int64_t T, int h_in,
                         int h_out, int64_t pool_rows, int64_t pool_stride, int64_t n_adapters, int64_t loc_len,
                         int dtype, void* stream) {
+  if (T == 0) return SLORA_OK;
   if (!y || !x) return fail(SLORA_ERR_NULL, "x or y is null");
   if (h_in < h_out) {
     return slora_bgmv_expand(y, x, w, start, ranks4, loc, ids, scales, qkvo, T, h_out, h_in, h_in, h_out,
