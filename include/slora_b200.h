@@ -118,8 +118,8 @@ int slora_sgmv_expand(void* y, const void* delta, const void* w, const int64_t* 
  * slora_plan_status copies the plan's status word back (synchronises the stream).
  */
 size_t slora_plan_workspace_bytes(int64_t T, int64_t n_adapters);
-int slora_plan_build(void* workspace, size_t workspace_bytes, const int64_t* ids, int64_t T, int64_t n_adapters,
-                     void* stream);
+int slora_plan_build(void* workspace, size_t workspace_bytes, const int64_t* ids, int64_t T, const int64_t* start,
+                     const int64_t* ranks4, int64_t n_adapters, int64_t loc_len, void* stream);
 int slora_plan_status(const void* workspace, int* status_out, int* n_tiles_out, void* stream);
 
 /*

@@ -46,7 +46,7 @@ _SIGS = {
     "slora_sgmv_expand": (c_int, [_P, _P, _P, _P, _P, _P, _P, _P, _P, _P, c_int, c_int, c_int, c_int64, c_int,
                                   c_int64, c_int, c_int64, c_int64, c_int64, c_int64, c_int64, c_int, _P]),
     "slora_plan_workspace_bytes": (c_size_t, [c_int64, c_int64]),
-    "slora_plan_build": (c_int, [_P, c_size_t, _P, c_int64, c_int64, _P]),
+    "slora_plan_build": (c_int, [_P, c_size_t, _P, c_int64, _P, _P, c_int64, c_int64, _P]),
     "slora_plan_status": (c_int, [_P, POINTER(c_int), POINTER(c_int), _P]),
     "slora_lora_shrink_multi": (c_int, [_P, _P, c_int, POINTER(c_int), POINTER(c_void_p), c_int64, c_int, _P,
                                         c_int64, c_int, _P, c_int64, c_int64, _P, _P, _P, c_int64, c_int64, c_int64,

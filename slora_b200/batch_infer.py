@@ -24,13 +24,14 @@ class BatchPlan:
     derived from the per-token adapter ids once per forward and shared by every layer and projection.
     """
 
-    def __init__(self, token_adapter_ids: torch.Tensor, n_adapters: int, workspace: torch.Tensor | None = None):
-        _lib.require_cuda(token_adapter_ids)
+    def __init__(self, token_adapter_ids: torch.Tensor, a_start: torch.Tensor, a_len: torch.Tensor, loc_len: int,
+                 workspace: torch.Tensor | None = None):
+        _lib.require_cuda(token_adapter_ids, a_start, a_len)
         if token_adapter_ids.dtype != torch.int64 or token_adapter_ids.dim() != 1:
             raise RuntimeError("token_adapter_ids must be a 1-D int64 tensor")
         self.ids = token_adapter_ids.contiguous()
         self.T = self.ids.numel()
-        self.n_adapters = int(n_adapters)
+        self.n_adapters = a_start.numel()
         need = _lib.lib.slora_plan_workspace_bytes(self.T, self.n_adapters)
         if workspace is None:
             workspace = torch.empty((need + 3) // 4, dtype=torch.int32, device=self.ids.device)
@@ -38,8 +39,8 @@ class BatchPlan:
             raise RuntimeError(f"plan workspace too small: {workspace.numel() * workspace.element_size()} < {need}")
         self.workspace = workspace
         _lib.check(_lib.lib.slora_plan_build(workspace.data_ptr(), workspace.numel() * workspace.element_size(),
-                                             self.ids.data_ptr(), self.T, self.n_adapters,
-                                             _lib.current_stream_ptr()))
+                                             self.ids.data_ptr(), self.T, a_start.data_ptr(), a_len.data_ptr(),
+                                             self.n_adapters, int(loc_len), _lib.current_stream_ptr()))
 
     @property
     def ptr(self) -> int:
@@ -92,7 +93,7 @@ class LoraBatchOps:
         T = self.ids.numel()
         dtype = self.key_buffer[0].dtype
         self.delta = [torch.zeros((T, self.max_lora_dim), dtype=dtype, device=self.ids.device) for _ in range(3)]
-        self.plan = BatchPlan(self.ids, self.a_start.numel()) if use_plan else None
+        self.plan = BatchPlan(self.ids, self.a_start, self.a_len, self.a_loc.numel()) if use_plan else None
         return self
 
     def _common(self, layer_id):

@@ -8,7 +8,8 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 ROOT = os.path.dirname(HERE)
 SOURCES = [os.path.join(HERE, "csrc", "lora_kernels.cu")]
-HEADERS = [os.path.join(ROOT, "include", "slora_b200.h")]
+HEADERS = [os.path.join(ROOT, "include", "slora_b200.h")] + sorted(
+    os.path.join(HERE, "csrc", f) for f in os.listdir(os.path.join(HERE, "csrc")) if f.endswith(".cuh"))
 OUT = os.path.join(HERE, "libslora_b200.so")
 
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "-shared",

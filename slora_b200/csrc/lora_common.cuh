@@ -1,0 +1,302 @@
+// Shared definitions of the LoRA shrink / expand kernels: argument blocks, the batch-plan layout, tile lookup
+// and the PTX wrappers (mbarrier, bulk asynchronous copy, programmatic dependent launch).
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+
+#include <cstdint>
+
+#include "slora_b200.h"
+
+namespace slora {
+
+constexpr int kTileTokens = 8;  // tokens per tile (plan granularity)
+constexpr int kMaxRows = 4;     // adapter rows per shrink work item
+constexpr int kChunk = 8192;    // flat B elements per expand work item (16 KB)
+constexpr uint32_t kSpinLimit = 1u << 18;
+
+// ---- batch plan workspace (int32 words) --------------------------------------------------------------------
+//   [header PH_WORDS][tile records 8 * max_tiles][perm T][pos T][cnt n_adapters]
+// tile record: {adapter, first slot in perm, tokens (0 = skip), slot_rows r, first loc entry, 0, 0, 0}
+constexpr int PH_MAGIC = 0, PH_NTILES = 1, PH_STATUS = 2, PH_MAXTILES = 3, PH_T = 4, PH_NADAPTERS = 5;
+constexpr int PH_WORDS = 16;
+constexpr int kTileWords = 8;
+constexpr int32_t kPlanMagic = 0x534c5032;  // "SLP2"
+
+enum TileMode { MODE_TOKEN = 0, MODE_PLAN = 1, MODE_SEGMENT = 2 };
+
+struct TileSrc {
+  const int32_t* plan;
+  const int64_t* ids;  // TOKEN: adapter per token; SEGMENT: adapter per segment
+  const int32_t* seg_start;
+  const int32_t* seg_len;
+  int mode;
+  int n_seg;
+  int tiles_per_seg;
+  int slots;  // tile slots the launch enumerates (upper bound of the number of tiles)
+  int64_t T;
+};
+
+struct Tables {
+  const int64_t* start;
+  const int64_t* ranks4;
+  const int64_t* loc;
+  int64_t n_adapters;
+  int64_t loc_len;
+  int64_t pool_rows;
+  int64_t pool_stride;
+};
+
+// One tile as the kernels see it.
+struct TileInfo {
+  int adapter;
+  int first;  // PLAN: first slot in perm; otherwise first token
+  int n;      // tokens, 1..kTileTokens
+  int r;      // slot rows (= LoRA rank of the adapter as stored in the tables)
+  int64_t loc_base;
+  const int32_t* perm;  // PLAN only
+};
+
+struct ShrinkArgs {
+  TileSrc src;
+  Tables tb;
+  const void* w;
+  const void* x;
+  int64_t x_stride;
+  int h_in;
+  void* delta[3];
+  int qkvo[3];
+  int nproj;
+  int64_t delta_stride;
+  int delta_width;
+  int max_rb;        // row blocks enumerated per (tile, projection)
+  int rows_per_cta;  // <= kMaxRows
+  int tok_pass;      // simple kernel: tokens staged per pass
+  int piece;         // simple kernel: elements per bulk copy
+  int32_t* status;
+};
+
+struct ExpandArgs {
+  TileSrc src;
+  Tables tb;
+  const void* w;
+  const void* scales;
+  void* y[3];
+  int64_t y_stride[3];
+  int h_out[3];
+  const void* delta[3];
+  int qkvo[3];
+  int chunk_begin[4];  // prefix sums of chunks per projection
+  int nproj;
+  int64_t delta_stride;
+  int delta_parts;
+  int64_t delta_part_stride;
+  int rank_mult;
+  int piece;  // elements per bulk copy (power of two dividing pool_stride, <= kChunk)
+  int32_t* status;
+};
+
+// ---- PTX wrappers ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+  return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
+}
+__device__ __forceinline__ void fence_barrier_init() { asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory"); }
+__device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+      "selp.u32 %0, 1, 0, p;\n"
+      "}\n"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+// Bounded wait: true when the phase completed within the limit.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
+  for (uint32_t i = 0; i < kSpinLimit; ++i) {
+    if (mbar_try_wait(bar, parity)) return true;
+  }
+  return false;
+}
+// Bulk asynchronous copy global -> this CTA's shared memory; both addresses 16-byte aligned, bytes % 16 == 0.
+__device__ __forceinline__ void bulk_g2s(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                   smem_u32(dst)),
+               "l"(src), "r"(bytes), "r"(smem_u32(bar))
+               : "memory");
+}
+
+// ---- element conversion ---------------------------------------------------------------------------------------
+template <typename T>
+__device__ __forceinline__ void cvt8(const uint4& v, float (&f)[8]);
+template <>
+__device__ __forceinline__ void cvt8<__half>(const uint4& v, float (&f)[8]) {
+  const __half2* h = reinterpret_cast<const __half2*>(&v);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float2 t = __half22float2(h[i]);
+    f[2 * i] = t.x;
+    f[2 * i + 1] = t.y;
+  }
+}
+template <>
+__device__ __forceinline__ void cvt8<__nv_bfloat16>(const uint4& v, float (&f)[8]) {
+  const uint32_t* u = reinterpret_cast<const uint32_t*>(&v);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    f[2 * i] = __uint_as_float(u[i] << 16);
+    f[2 * i + 1] = __uint_as_float(u[i] & 0xffff0000u);
+  }
+}
+template <typename T>
+__device__ __forceinline__ float to_f32(T v);
+template <>
+__device__ __forceinline__ float to_f32<__half>(__half v) { return __half2float(v); }
+template <>
+__device__ __forceinline__ float to_f32<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
+template <typename T>
+__device__ __forceinline__ T from_f32(float v);
+template <>
+__device__ __forceinline__ __half from_f32<__half>(float v) { return __float2half_rn(v); }
+template <>
+__device__ __forceinline__ __nv_bfloat16 from_f32<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
+
+__device__ __forceinline__ void set_status(int32_t* status, int bit) {
+  if (status != nullptr) atomicOr(status, bit);
+}
+
+// Number of tiles the launch has to visit (exact for a plan, the slot count otherwise).
+__device__ __forceinline__ int tile_count(const TileSrc& s) {
+  return s.mode == MODE_PLAN ? min(s.plan[PH_NTILES], s.slots) : s.slots;
+}
+
+// Which tokens / adapter does tile `tile_idx` cover?  False when the slot holds no work (or fails a range check,
+// in which case the status word records why).
+__device__ __forceinline__ bool lookup_tile(const TileSrc& s, const Tables& tb, int tile_idx, TileInfo& t,
+                                            int32_t* status) {
+  if (s.mode == MODE_PLAN) {
+    const int32_t* hdr = s.plan;
+    if (tile_idx >= hdr[PH_NTILES]) return false;
+    const int4* rec = reinterpret_cast<const int4*>(s.plan + PH_WORDS + kTileWords * tile_idx);
+    const int4 r0 = rec[0];
+    const int4 r1 = rec[1];
+    t.adapter = r0.x;
+    t.first = r0.y;
+    t.n = r0.z;
+    t.r = r0.w;
+    t.loc_base = r1.x;
+    t.perm = s.plan + PH_WORDS + kTileWords * hdr[PH_MAXTILES];
+    return t.n > 0 && t.r > 0;
+  }
+  int64_t adapter;
+  t.perm = nullptr;
+  if (s.mode == MODE_TOKEN) {
+    if (tile_idx >= s.T) return false;
+    adapter = s.ids[tile_idx];
+    t.first = tile_idx;
+    t.n = 1;
+  } else {
+    const int seg = tile_idx / s.tiles_per_seg;
+    const int sub = tile_idx - seg * s.tiles_per_seg;
+    if (seg >= s.n_seg) return false;
+    const int64_t len = s.seg_len[seg];
+    const int64_t off = static_cast<int64_t>(sub) * kTileTokens;
+    if (off >= len) return false;
+    const int64_t first = static_cast<int64_t>(s.seg_start[seg]) + off;
+    if (first < 0 || first >= s.T) return false;
+    int64_t n = len - off;
+    if (n > kTileTokens) n = kTileTokens;
+    if (first + n > s.T) n = s.T - first;
+    adapter = s.ids[seg];
+    t.first = static_cast<int>(first);
+    t.n = static_cast<int>(n);
+  }
+  if (adapter < 0 || adapter >= tb.n_adapters) {
+    set_status(status, SLORA_STATUS_BAD_ID);
+    return false;
+  }
+  const int64_t r4 = tb.ranks4[adapter];
+  const int64_t st = tb.start[adapter];
+  if (r4 < 0 || st < 0 || st + r4 > tb.loc_len || r4 > (int64_t(1) << 20)) {
+    set_status(status, SLORA_STATUS_BAD_TABLE);
+    return false;
+  }
+  t.adapter = static_cast<int>(adapter);
+  t.r = static_cast<int>(r4 >> 2);
+  t.loc_base = st;
+  return t.r > 0;
+}
+
+__device__ __forceinline__ int tile_token(const TileInfo& t, int i) {
+  return t.perm ? t.perm[t.first + i] : t.first + i;
+}
+
+// Sum V per-lane values across the warp; lane l returns the total of logical index (l >> (5 - log2 V)).
+template <int V>
+__device__ __forceinline__ float warp_reduce_scatter(float (&v)[V], int lane) {
+  int mask = 16;
+#pragma unroll
+  for (int half = V / 2; half >= 1; half >>= 1) {
+    const bool up = (lane & mask) != 0;
+#pragma unroll
+    for (int i = 0; i < half; ++i) {
+      const float keep = up ? v[i + half] : v[i];
+      const float send = up ? v[i] : v[i + half];
+      v[i] = keep + __shfl_xor_sync(0xffffffffu, send, mask);
+    }
+    mask >>= 1;
+  }
+#pragma unroll
+  for (; mask >= 1; mask >>= 1) v[0] += __shfl_xor_sync(0xffffffffu, v[0], mask);
+  return v[0];
+}
+
+// Exchange step of the expand butterfly over 8 per-lane partial sums (see expand_finish).
+template <int HALF>
+__device__ __forceinline__ void exch(float (&v)[8], int lane, int mask) {
+  const bool up = (lane & mask) != 0;
+#pragma unroll
+  for (int i = 0; i < HALF; ++i) {
+    const float keep = up ? v[i + HALF] : v[i];
+    const float send = up ? v[i] : v[i + HALF];
+    v[i] = keep + __shfl_xor_sync(0xffffffffu, send, mask);
+  }
+}
+
+// LPO lanes (= r / 8) share one output, each holding the partial dot product over its 8 values of k, for the 8
+// loads m = 0..7 of the warp.  After the butterfly lane l owns NV = max(1, 8 / LPO) complete outputs, those of
+// loads m_base(l) + i, i < NV, where m_base takes 4, 2, 1 from lane bits 0, 1, 2 (as far as LPO uses them).
+template <int LPO>
+__device__ __forceinline__ void expand_butterfly(float (&v)[8], int lane) {
+  if (LPO >= 2) exch<4>(v, lane, 1);
+  if (LPO >= 4) exch<2>(v, lane, 2);
+  if (LPO >= 8) exch<1>(v, lane, 4);
+  if (LPO >= 16) v[0] += __shfl_xor_sync(0xffffffffu, v[0], 8);
+}
+template <int LPO>
+__device__ __forceinline__ int expand_m_base(int lane) {
+  int m = 0;
+  if (LPO >= 2) m += (lane & 1) ? 4 : 0;
+  if (LPO >= 4) m += (lane & 2) ? 2 : 0;
+  if (LPO >= 8) m += (lane & 4) ? 1 : 0;
+  return m;
+}
+
+}  // namespace slora

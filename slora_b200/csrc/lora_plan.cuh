@@ -1,0 +1,120 @@
+// Batch plan: group the tokens of one batch by adapter (one CTA; T and n_adapters are a few thousand at most).
+#pragma once
+
+#include "lora_common.cuh"
+
+namespace slora {
+
+// workspace words: [header PH_WORDS][tile records kTileWords * max_tiles][perm T][pos T][cnt n_adapters]
+// Counting sort by adapter id: histogram, exclusive scan over adapters (tokens and tiles at once), scatter.
+// Tokens whose id is outside [0, n_adapters) are left out and SLORA_STATUS_BAD_ID is recorded; adapters whose
+// table entries are out of range get tiles of zero tokens and SLORA_STATUS_BAD_TABLE.
+__global__ void __launch_bounds__(1024) plan_build_kernel(int32_t* ws, const int64_t* __restrict__ ids,
+                                                          const int64_t* __restrict__ start,
+                                                          const int64_t* __restrict__ ranks4, int64_t loc_len, int T,
+                                                          int n_adapters, int max_tiles) {
+  int32_t* hdr = ws;
+  int32_t* tiles = ws + PH_WORDS;
+  int32_t* perm = tiles + kTileWords * max_tiles;
+  int32_t* pos = perm + T;
+  int32_t* cnt = pos + T;
+  __shared__ int s_tok[32], s_tile[32];
+  __shared__ int s_status;
+  const int tid = threadIdx.x, nthr = blockDim.x, lane = tid & 31, warp = tid >> 5;
+
+  for (int i = tid; i < n_adapters; i += nthr) cnt[i] = 0;
+  if (tid == 0) s_status = 0;
+  __syncthreads();
+  for (int t = tid; t < T; t += nthr) {
+    const int64_t a = ids[t];
+    if (a < 0 || a >= n_adapters) {
+      pos[t] = -1;
+      atomicOr(&s_status, SLORA_STATUS_BAD_ID);
+    } else {
+      pos[t] = atomicAdd(&cnt[a], 1);
+    }
+  }
+  __syncthreads();
+  // exclusive scan over adapters of (tokens, tiles); each thread owns a contiguous run of adapters
+  const int per = (n_adapters + nthr - 1) / nthr;
+  const int lo = min(tid * per, n_adapters), hi = min(lo + per, n_adapters);
+  int tok_sum = 0, tile_sum = 0;
+  for (int a = lo; a < hi; ++a) {
+    const int c = cnt[a];
+    tok_sum += c;
+    tile_sum += (c + kTileTokens - 1) / kTileTokens;
+  }
+  int tok_inc = tok_sum, tile_inc = tile_sum;
+#pragma unroll
+  for (int off = 1; off < 32; off <<= 1) {
+    const int a = __shfl_up_sync(0xffffffffu, tok_inc, off);
+    const int b = __shfl_up_sync(0xffffffffu, tile_inc, off);
+    if (lane >= off) {
+      tok_inc += a;
+      tile_inc += b;
+    }
+  }
+  if (lane == 31) {
+    s_tok[warp] = tok_inc;
+    s_tile[warp] = tile_inc;
+  }
+  __syncthreads();
+  if (warp == 0) {
+    const int nw = nthr >> 5;
+    const int a = lane < nw ? s_tok[lane] : 0, b = lane < nw ? s_tile[lane] : 0;
+    int ai = a, bi = b;
+#pragma unroll
+    for (int off = 1; off < 32; off <<= 1) {
+      const int a2 = __shfl_up_sync(0xffffffffu, ai, off);
+      const int b2 = __shfl_up_sync(0xffffffffu, bi, off);
+      if (lane >= off) {
+        ai += a2;
+        bi += b2;
+      }
+    }
+    s_tok[lane] = ai - a;  // exclusive
+    s_tile[lane] = bi - b;
+    if (lane == 31) hdr[PH_NTILES] = min(bi, max_tiles);
+  }
+  __syncthreads();
+  int tok_off = s_tok[warp] + tok_inc - tok_sum;
+  int tile_off = s_tile[warp] + tile_inc - tile_sum;
+  for (int a = lo; a < hi; ++a) {
+    const int c = cnt[a];
+    cnt[a] = tok_off;  // becomes the group's first slot in perm
+    if (c > 0) {
+      const int64_t r4 = ranks4[a], st = start[a];
+      const bool good = r4 >= 0 && st >= 0 && st + r4 <= loc_len && r4 <= (int64_t(1) << 20) && st < 0x7fffffffLL;
+      if (!good) atomicOr(&s_status, SLORA_STATUS_BAD_TABLE);
+      for (int i = 0; i * kTileTokens < c; ++i) {
+        if (tile_off < max_tiles) {
+          int4* rec = reinterpret_cast<int4*>(tiles + kTileWords * tile_off);
+          rec[0] = make_int4(a, tok_off + i * kTileTokens, good ? min(kTileTokens, c - i * kTileTokens) : 0,
+                             good ? static_cast<int>(r4 >> 2) : 0);
+          rec[1] = make_int4(good ? static_cast<int>(st) : 0, 0, 0, 0);
+        }
+        ++tile_off;
+      }
+    }
+    tok_off += c;
+  }
+  __syncthreads();
+  for (int t = tid; t < T; t += nthr) {
+    const int p = pos[t];
+    if (p >= 0) perm[cnt[ids[t]] + p] = t;
+  }
+  if (tid == 0) {
+    hdr[PH_MAGIC] = kPlanMagic;
+    hdr[PH_STATUS] = s_status;
+    hdr[PH_MAXTILES] = max_tiles;
+    hdr[PH_T] = T;
+    hdr[PH_NADAPTERS] = n_adapters;
+  }
+}
+
+// Empty kernel launched (without programmatic serialization) right after plan_build_kernel: later kernels that
+// start early under programmatic dependent launch read the plan before their grid-dependency wait, and this
+// fully serialised launch in between guarantees the plan's writes are complete and visible by then.
+__global__ void plan_fence_kernel() {}
+
+}  // namespace slora

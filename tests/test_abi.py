@@ -38,7 +38,7 @@ def test_version_and_workspace_size():
     big = _lib.lib.slora_plan_workspace_bytes(4096, 2000)
     assert 0 < small < big
     # header + tiles + perm + pos + counters
-    assert small >= 4 * (16 + 4 * (32 + 256) + 2 * 256 + 1000)
+    assert small >= 4 * (16 + 8 * (32 + 256) + 2 * 256 + 1000)
     assert _lib.lib.slora_plan_workspace_bytes(-1, 5) == 0
 
 
@@ -65,7 +65,7 @@ def test_argument_validation_needs_no_device():
                              64, 0, 0)
     assert rc == -8
     # plan workspace too small
-    rc = L.slora_plan_build(fake, 16, fake, 256, 1000, 0)
+    rc = L.slora_plan_build(fake, 16, fake, 256, fake, fake, 1000, 64, 0)
     assert rc == -6
     # an empty batch is a no-op, not an error
     rc = L.slora_bgmv_shrink(fake, fake, fake, fake, fake, fake, fake, 0, 0, 1024, 1024, 8, 8, 64, 1024, 2, 64, 0, 0)

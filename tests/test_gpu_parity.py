@@ -179,7 +179,7 @@ def test_expand_reads_all_gathered_delta_parts():
             parts[g, t, :rs] = torch.from_numpy(dref[t, g * rs:(g + 1) * rs]).to(wl.dtype)
     parts = parts.to(DEV)
     y = torch.zeros((wl.T, 1024), dtype=wl.dtype, device=DEV)
-    plan = batch_infer.BatchPlan(w.ids, w.a_start.numel())
+    plan = batch_infer.BatchPlan(w.ids, w.a_start, w.a_len, w.a_loc.numel())
     batch_infer.expand_multi(plan, w.ids, [p], [y], [parts], w.pools_b[0], w.a_start, w.a_len, w.a_loc, w.a_scaling,
                              delta_stride=R // N, delta_width=R // N, delta_parts=N, delta_part_stride=wl.T * (R // N))
     torch.cuda.synchronize()
