@@ -115,12 +115,18 @@ __device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
 __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
+// One non-blocking probe of a barrier phase.  (mbarrier.try_wait may suspend the thread for a system-dependent time;
+// the pipelines here poll with test_wait instead so that a waiting warp resumes as soon as the phase flips.)
 __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
   uint32_t ok;
   asm volatile(
       "{\n"
       ".reg .pred p;\n"
+#ifdef SLORA_WAIT_SUSPEND
       "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+#else
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+#endif
       "selp.u32 %0, 1, 0, p;\n"
       "}\n"
       : "=r"(ok)
@@ -165,6 +171,43 @@ __device__ __forceinline__ void cvt8<__nv_bfloat16>(const uint4& v, float (&f)[8
     f[2 * i + 1] = __uint_as_float(u[i] & 0xffff0000u);
   }
 }
+// acc += a.lo * b.lo + a.hi * b.hi for a packed pair of 16-bit floats, with the mixed-precision FMA of sm_100
+// (f16/bf16 operands, f32 accumulator: the products are exact in f32, so this equals converting first).
+template <typename T>
+__device__ __forceinline__ void fma_pair(float& acc, uint32_t a, uint32_t b);
+template <>
+__device__ __forceinline__ void fma_pair<__half>(float& acc, uint32_t a, uint32_t b) {
+  asm("{\n"
+      ".reg .b16 al, ah, bl, bh;\n"
+      "mov.b32 {al, ah}, %1;\n"
+      "mov.b32 {bl, bh}, %2;\n"
+      "fma.rn.f32.f16 %0, al, bl, %0;\n"
+      "fma.rn.f32.f16 %0, ah, bh, %0;\n"
+      "}\n"
+      : "+f"(acc)
+      : "r"(a), "r"(b));
+}
+template <>
+__device__ __forceinline__ void fma_pair<__nv_bfloat16>(float& acc, uint32_t a, uint32_t b) {
+  asm("{\n"
+      ".reg .b16 al, ah, bl, bh;\n"
+      "mov.b32 {al, ah}, %1;\n"
+      "mov.b32 {bl, bh}, %2;\n"
+      "fma.rn.f32.bf16 %0, al, bl, %0;\n"
+      "fma.rn.f32.bf16 %0, ah, bh, %0;\n"
+      "}\n"
+      : "+f"(acc)
+      : "r"(a), "r"(b));
+}
+// acc += dot of two vectors of eight 16-bit floats
+template <typename T>
+__device__ __forceinline__ void dot8(float& acc, const uint4& a, const uint4& b) {
+  fma_pair<T>(acc, a.x, b.x);
+  fma_pair<T>(acc, a.y, b.y);
+  fma_pair<T>(acc, a.z, b.z);
+  fma_pair<T>(acc, a.w, b.w);
+}
+
 template <typename T>
 __device__ __forceinline__ float to_f32(T v);
 template <>

@@ -229,7 +229,7 @@ int run_shrink(const TileSrc& src, const Tables& tb, const void* w, const void* 
     a.max_rb = (delta_width + kMaxRows - 1) / kMaxRows;
     const int64_t items = static_cast<int64_t>(src.slots) * nproj * a.max_rb;
     const int64_t grid = items < sm_count() ? items : sm_count();
-    const size_t smem = static_cast<size_t>(kPipeStages) * kShrinkStageBytes;
+    const size_t smem = kRingBytes;
     if (dtype == SLORA_F16) {
       auto k = lora_shrink_pipe_kernel<__half>;
       rc = ensure_dyn_smem(k, 2, smem);
@@ -313,9 +313,9 @@ int run_expand(const TileSrc& src, const Tables& tb, const void* w, const void* 
   if (choice == CHOOSE_PIPELINED && !can_pipe)
     return fail(SLORA_ERR_ALIGN, "pipelined expand needs 16-byte aligned y and delta rows and a plain delta layout");
   if (can_pipe && choice != CHOOSE_SIMPLE) {
-    const int64_t items = static_cast<int64_t>(src.slots) * 2 * a.chunk_begin[nproj];
+    const int64_t items = static_cast<int64_t>(src.slots) * a.chunk_begin[nproj];
     const int64_t grid = items < sm_count() ? items : sm_count();
-    const size_t smem = static_cast<size_t>(kPipeStages) * kExpandStageBytes;
+    const size_t smem = kRingBytes;
     if (dtype == SLORA_F16) {
       auto k = lora_expand_pipe_kernel<__half>;
       rc = ensure_dyn_smem(k, 2, smem);

@@ -2,60 +2,183 @@
 //
 // One CTA per SM walks its share of the work items (item i belongs to CTA i mod gridDim.x).  Warp 0 is the
 // producer: its 32 lanes resolve 32 upcoming items in parallel (tile record -> table entries -> row addresses and
-// token ids), then feed a ring of kPipeStages shared-memory stages with bulk asynchronous copies
-// (cp.async.bulk + mbarrier complete_tx), one lane per copy.  Warps 1..4 are consumers: they wait on a stage's
-// "full" barrier, do the arithmetic and release the stage through its "empty" barrier.  Consumer warps never
-// synchronise with each other (shrink: one adapter row per warp; expand: one 2048-element span of the B chunk per
-// warp), so every wait in the kernel is an mbarrier wait with a time limit.
+// token ids), then feed a ring of shared-memory stages with bulk asynchronous copies (cp.async.bulk + mbarrier
+// complete_tx).  Warps 1..8 are consumers: they wait on a stage's "full" barrier, do the arithmetic and release the
+// stage through its "empty" barrier.  Consumer warps never wait for each other (shrink: each warp owns a K-slice and
+// the last warp to finish an item, elected by an atomic counter, adds the partial sums; expand: each warp owns a
+// 1024-element span of the B chunk), so every wait in the kernel is an mbarrier wait with a time limit.
 //
-// Programmatic dependent launch: the producer fills the first stages with adapter rows (which no kernel on the
-// stream writes) before it executes griddepcontrol.wait, and only then requests activations (x, y, delta).  With a
-// ring of ~100 KB two kernels fit on an SM, so the next kernel's prologue overlaps this kernel's tail.
+// What shapes the ring (measured on B200): a cp.async.bulk warp-instruction costs the issuing warp 400-600 cycles
+// whatever its size and however many lanes take part, and ~1 us passes before the bytes land.  So a stage is filled
+// by ONE bulk instruction in which every participating lane carries one copy (adapter rows and activation rows
+// alike), stages are made as large as the work item allows (tens of KB), and they are packed back to back in a
+// byte ring of kRingBytes so that several are in flight whatever their size.
 //
-// Shrink stage  = K-chunk of 1024 elements: [4 adapter rows][8 token rows] (24 KB); an item is (tile, projection,
-//                 block of 4 rows) and spans ceil(h_in / 1024) consecutive stages; accumulators stay in registers.
-// Expand stage  = one item (tile half of <= 4 tokens, projection, 8192-element chunk of B): [B chunk 16 KB]
-//                 [y segments 4 x 2 KB][delta rows 4 x 256 B] (25 KB).  y is read through the stage and written
-//                 back with plain coalesced stores.
+// Programmatic dependent launch: the producer issues the adapter-row copies of the first stages (rows that no kernel
+// on the stream writes) before it executes griddepcontrol.wait and stashes the activation copies (x, y, delta) of
+// those stages; they go out right after the wait.  With a ring of 96 KB two kernels fit on an SM, so the next
+// kernel's prologue overlaps this kernel's tail.
+//
+// Shrink stage  = K-chunk of up to kKC elements of one item (tile, projection, block of <= 4 rows):
+//                 [nrows adapter-row chunks][n token-row chunks]; accumulators stay in registers across the chunks.
+// Expand stage  = one item (tile, projection, 8192-element chunk of B): [B chunk][n y segments][n delta rows].
+//                 y is read through the stage and written back with plain coalesced stores.
 #pragma once
 
 #include "lora_common.cuh"
 
 namespace slora {
 
-constexpr int kPipeStages = 4;
-constexpr int kConsumerWarps = 4;
+constexpr int kSlots = 8;  // stage descriptors (barrier pairs) in flight
+constexpr int kRingBytes = 96 * 1024;
+constexpr int kConsumerWarps = 8;
 constexpr int kPipeThreads = 32 * (1 + kConsumerWarps);
-constexpr int kKC = 1024;  // K elements per shrink stage
-constexpr int kShrinkStageBytes = (kMaxRows + kTileTokens) * kKC * 2;
-constexpr int kHalfTokens = 4;  // tokens per expand item
-constexpr int kYSlot = kChunk / 8;  // outputs per token in a stage (r = 8 gives the most)
-constexpr int kExpandYBytes = kHalfTokens * kYSlot * 2;
-constexpr int kExpandDBytes = kHalfTokens * 128 * 2;
-constexpr int kExpandStageBytes = kChunk * 2 + kExpandYBytes + kExpandDBytes;
-constexpr int kMaxPieces = 8;  // B copies per expand stage (lanes 0..7); y copies use lanes 8..11, delta 12..15
+constexpr int kKC = 2048;  // K elements per shrink stage
+constexpr int kMaxPieces = 8;  // B copies per expand stage (lanes 0..7); y copies use lanes 8..15, delta 16..23
 constexpr int kSpanRows = 4;   // pool rows a B chunk may touch
 
 constexpr int FLAG_FIRST = 1, FLAG_LAST = 2, FLAG_END = 4;
 constexpr uint32_t FULL_MASK = 0xffffffffu;
-constexpr uint64_t kWaitNs = 1000000000ull;  // one second
+constexpr long long kWaitCycles = 4000000000ll;  // about two seconds of SM clock
 
-__device__ __forceinline__ uint64_t gtime_ns() {
-  uint64_t t;
-  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-  return t;
-}
-// Wait for a barrier phase for at most kWaitNs; false on timeout.
+// Wait for a barrier phase for a bounded time (SM cycle counter); false on timeout.
 __device__ __forceinline__ bool mbar_wait_timed(uint64_t* bar, uint32_t parity) {
   if (mbar_try_wait(bar, parity)) return true;
-  const uint64_t t0 = gtime_ns();
+  const long long t0 = clock64();
   for (;;) {
 #pragma unroll 1
-    for (int i = 0; i < 64; ++i) {
+    for (int i = 0; i < 1024; ++i) {
       if (mbar_try_wait(bar, parity)) return true;
     }
-    if (gtime_ns() - t0 > kWaitNs) return false;
+    if (clock64() - t0 > kWaitCycles) return false;
   }
+}
+
+// Shared-memory control block of one pipeline.
+struct PipeCtl {
+  uint64_t full[kSlots];
+  uint64_t empty[kSlots];
+  int meta[kSlots][16];
+  uint32_t off[kSlots];          // producer only: byte offset of the stage in the ring
+  // activation copies of the stages issued before the grid-dependency wait (producer only, one entry per lane)
+  uint64_t pend_src[kSlots][32];
+  uint32_t pend_dst[kSlots][32];
+  uint32_t pend_bytes[kSlots][32];
+  // shrink only: per-item partial sums of the consumer warps and the arrival counter that elects the last warp
+  float red[kSlots][kConsumerWarps][32];
+  int red_cnt[kSlots];
+};
+
+// Producer-side ring state (identical in all 32 lanes).
+struct Ring {
+  uint32_t g = 0;     // next stage index
+  uint32_t tail = 0;  // oldest stage not yet known to be released
+  uint32_t head = 0;  // next free byte
+  bool pre = true;    // still before the grid-dependency wait
+  int npend = 0;      // stages with stashed activation copies
+  bool dead = false;  // a bounded wait ran out
+};
+
+__device__ __forceinline__ void ring_flush(Ring& r, PipeCtl& c, int lane) {
+  pdl_wait();
+  for (int i = 0; i < r.npend; ++i) {
+    const uint32_t slot = (r.g - r.npend + i) % kSlots;
+    if (c.pend_bytes[slot][lane] != 0) {
+      asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                       c.pend_dst[slot][lane]),
+                   "l"(c.pend_src[slot][lane]), "r"(c.pend_bytes[slot][lane]), "r"(smem_u32(&c.full[slot]))
+                   : "memory");
+    }
+  }
+  r.npend = 0;
+  r.pre = false;
+}
+
+// Reserve `sz` bytes (a multiple of 128) and a descriptor for stage r.g; returns the byte offset, or 0xffffffff when
+// a wait ran out.  Before the grid-dependency wait no stage has been released yet, so running out of room there
+// ends the prologue (ring_flush) instead of waiting.
+__device__ __forceinline__ uint32_t ring_alloc(Ring& r, PipeCtl& c, uint32_t sz, int lane) {
+  for (;;) {
+    uint32_t cand = 0;
+    bool ok;
+    if (r.tail == r.g) {
+      r.head = 0;
+      ok = true;
+    } else {
+      const uint32_t t = c.off[r.tail % kSlots];
+      if (r.head > t) {
+        if (r.head + sz <= kRingBytes) {
+          cand = r.head;
+          ok = true;
+        } else {
+          cand = 0;
+          ok = sz <= t;
+        }
+      } else {
+        cand = r.head;
+        ok = r.head + sz <= t && r.head != t;
+      }
+    }
+    if (ok && r.g - r.tail < kSlots) return cand;
+    if (r.pre) {
+      ring_flush(r, c, lane);
+      continue;
+    }
+    if (!mbar_wait_timed(&c.empty[r.tail % kSlots], (r.tail / kSlots) & 1)) {
+      r.dead = true;
+      return 0xffffffffu;
+    }
+    ++r.tail;
+  }
+}
+
+// One bulk instruction for the whole stage: lane `lane` carries (dst, src, bytes) or bytes == 0.  Activation copies
+// (is_act) issued before the grid-dependency wait are stashed instead.
+__device__ __forceinline__ void ring_issue(Ring& r, PipeCtl& c, uint32_t slot, uint32_t dst, const void* src,
+                                           uint32_t bytes, bool is_act, int lane) {
+  if (r.pre) {
+    c.pend_bytes[slot][lane] = is_act ? bytes : 0;
+    c.pend_dst[slot][lane] = dst;
+    c.pend_src[slot][lane] = reinterpret_cast<uint64_t>(src);
+    if (is_act) bytes = 0;
+  }
+  if (bytes != 0) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
+                 "l"(src), "r"(bytes), "r"(smem_u32(&c.full[slot]))
+                 : "memory");
+  }
+  if (r.pre) ++r.npend;
+  ++r.g;
+}
+
+// Finish: flush a prologue that never ended, then post the end marker.
+__device__ __forceinline__ void ring_finish(Ring& r, PipeCtl& c, int32_t* status, int lane) {
+  if (r.pre) ring_flush(r, c, lane);
+  if (!r.dead) ring_alloc(r, c, 0, lane);
+  if (r.dead) {
+    if (lane == 0) set_status(status, SLORA_STATUS_TIMEOUT);
+    return;
+  }
+  const uint32_t slot = r.g % kSlots;
+  if (lane == 0) {
+    c.off[slot] = r.head;
+    c.meta[slot][0] = FLAG_END;
+    mbar_arrive(&c.full[slot]);
+  }
+}
+
+__device__ __forceinline__ void pipe_init(PipeCtl& c, int tid) {
+  if (tid == 0) {
+#pragma unroll
+    for (int s = 0; s < kSlots; ++s) {
+      mbar_init(&c.full[s], 1);
+      mbar_init(&c.empty[s], kConsumerWarps);
+      c.red_cnt[s] = 0;
+    }
+    fence_barrier_init();
+    fence_proxy_async();
+  }
+  __syncthreads();
 }
 
 template <typename P>
@@ -63,12 +186,15 @@ __device__ __forceinline__ P pick3(P const (&arr)[3], int p) {
   return p == 0 ? arr[0] : (p == 1 ? arr[1] : arr[2]);
 }
 
+__device__ __forceinline__ uint32_t round128(uint32_t v) { return (v + 127u) & ~127u; }
+
 // ------------------------------------------------------------------------------------------------------------
 // shrink
+// stage meta: [0] flags [1] nrows [2] n [3] j0 [4] projection [5] klen [6] ring offset, [8..15] token ids
+// stage bytes: nrows chunks of klen elements (adapter rows), then n chunks of klen elements (token rows)
 // ------------------------------------------------------------------------------------------------------------
 template <typename T>
-__device__ __forceinline__ void shrink_producer(const ShrinkArgs& a, unsigned char* stage_mem, uint64_t* full,
-                                                uint64_t* empty, int (*smeta)[16], int lane) {
+__device__ __forceinline__ void shrink_producer(const ShrinkArgs& a, unsigned char* ring_mem, PipeCtl& c, int lane) {
   const int per_tile = a.nproj * a.max_rb;
   const int64_t n_items = static_cast<int64_t>(tile_count(a.src)) * per_tile;
   const int h_in = a.h_in;
@@ -77,10 +203,10 @@ __device__ __forceinline__ void shrink_producer(const ShrinkArgs& a, unsigned ch
   const T* w = reinterpret_cast<const T*>(a.w);
   const T* x = reinterpret_cast<const T*>(a.x);
   const int64_t G = gridDim.x;
-  uint32_t g = 0;
-  bool waited = false, dead = false;
+  const uint32_t ring_base = smem_u32(ring_mem);
+  Ring r;
 
-  for (int64_t batch0 = blockIdx.x; batch0 < n_items && !dead; batch0 += 32 * G) {
+  for (int64_t batch0 = blockIdx.x; batch0 < n_items && !r.dead; batch0 += 32 * G) {
     // ---- 32 items resolved in parallel, one per lane ----
     const int64_t item = batch0 + lane * G;
     int m_valid = 0, m_n = 0, m_nrows = 0, m_j0 = 0, m_p = 0;
@@ -128,209 +254,226 @@ __device__ __forceinline__ void shrink_producer(const ShrinkArgs& a, unsigned ch
       }
     }
 
-    // ---- feed the ring: stages [lo, hi) of this batch, adapter rows (do_w) and/or activations (do_x) ----
-    auto emit = [&](uint32_t g0, uint32_t lo, uint32_t hi, bool do_w, bool do_x) -> uint32_t {
-      uint32_t gg = g0;
-      for (int k = 0; k < 32; ++k) {
-        if (!__shfl_sync(FULL_MASK, m_valid, k)) continue;
-        const int n = __shfl_sync(FULL_MASK, m_n, k);
-        const int nrows = __shfl_sync(FULL_MASK, m_nrows, k);
-        const int j0 = __shfl_sync(FULL_MASK, m_j0, k);
-        const int p = __shfl_sync(FULL_MASK, m_p, k);
-        int64_t myrow = 0;
-        int mytok = 0;
+    // ---- feed the ring, item by item, chunk by chunk ----
+    for (int k = 0; k < 32 && !r.dead; ++k) {
+      if (!__shfl_sync(FULL_MASK, m_valid, k)) continue;
+      const int n = __shfl_sync(FULL_MASK, m_n, k);
+      const int nrows = __shfl_sync(FULL_MASK, m_nrows, k);
+      const int j0 = __shfl_sync(FULL_MASK, m_j0, k);
+      const int p = __shfl_sync(FULL_MASK, m_p, k);
+      // lane j < 4 carries adapter row j, lane 4 + i carries token i
+      int64_t mysrc = 0;
+      int mytok = 0;
 #pragma unroll
-        for (int j = 0; j < kMaxRows; ++j) {
-          const int64_t v = __shfl_sync(FULL_MASK, m_row[j], k);
-          if (lane == j) myrow = v;
-        }
-#pragma unroll
-        for (int i = 0; i < kTileTokens; ++i) {
-          const int v = __shfl_sync(FULL_MASK, m_tok[i], k);
-          if (lane == kMaxRows + i) mytok = v;
-        }
-        for (int kc = 0; kc < nk; ++kc, ++gg) {
-          if (gg < lo || gg >= hi || dead) continue;
-          const int s = gg % kPipeStages;
-          const uint32_t round = gg / kPipeStages;
-          const int klen = min(kKC, h_in - kc * kKC);
-          const uint32_t bytes = static_cast<uint32_t>(klen) * sizeof(T);
-          T* st = reinterpret_cast<T*>(stage_mem + static_cast<size_t>(s) * kShrinkStageBytes);
-          if (do_w) {
-            if (round > 0 && !mbar_wait_timed(&empty[s], (round - 1) & 1)) {
-              dead = true;
-              continue;
-            }
-            if (lane == 0) {
-              smeta[s][0] = (kc == 0 ? FLAG_FIRST : 0) | (kc == nk - 1 ? FLAG_LAST : 0);
-              smeta[s][1] = nrows;
-              smeta[s][2] = n;
-              smeta[s][3] = j0;
-              smeta[s][4] = p;
-              smeta[s][5] = klen;
-            }
-            if (lane >= kMaxRows && lane < kMaxRows + kTileTokens) smeta[s][8 + lane - kMaxRows] = mytok;
-            __syncwarp();
-            if (lane == 0) mbar_expect_tx(&full[s], static_cast<uint32_t>(nrows + n) * bytes);
-            __syncwarp();
-            if (lane < nrows) bulk_g2s(st + lane * kKC, w + myrow + static_cast<int64_t>(kc) * kKC, bytes, &full[s]);
-          }
-          if (do_x && lane >= kMaxRows && lane < kMaxRows + n) {
-            bulk_g2s(st + lane * kKC, x + static_cast<int64_t>(mytok) * a.x_stride + static_cast<int64_t>(kc) * kKC,
-                     bytes, &full[s]);
-          }
-        }
+      for (int j = 0; j < kMaxRows; ++j) {
+        const int64_t v = __shfl_sync(FULL_MASK, m_row[j], k);
+        if (lane == j) mysrc = v;
       }
-      return gg;
-    };
-
-    if (!waited) {
-      // prologue: adapter rows of the first ring-full of stages go out before the grid dependency resolves
-      emit(0, 0, kPipeStages, true, false);
-      pdl_wait();
-      waited = true;
-      emit(0, 0, kPipeStages, false, true);
-      g = emit(0, kPipeStages, 0xffffffffu, true, true);
-    } else {
-      g = emit(g, 0, 0xffffffffu, true, true);
+#pragma unroll
+      for (int i = 0; i < kTileTokens; ++i) {
+        const int v = __shfl_sync(FULL_MASK, m_tok[i], k);
+        if (lane == kMaxRows + i) mytok = v;
+      }
+      const bool is_w = lane < nrows;
+      const bool is_x = lane >= kMaxRows && lane < kMaxRows + n;
+      const T* src0 = is_w ? w + mysrc : x + static_cast<int64_t>(mytok) * a.x_stride;
+      const int myslot = is_w ? lane : nrows + (lane - kMaxRows);  // position of this lane's chunk in the stage
+      for (int kc = 0; kc < nk; ++kc) {
+        const int klen = min(kKC, h_in - kc * kKC);
+        const uint32_t bytes = static_cast<uint32_t>(klen) * sizeof(T);
+        const uint32_t sz = round128(static_cast<uint32_t>(nrows + n) * bytes);
+        const uint32_t off = ring_alloc(r, c, sz, lane);
+        if (r.dead) break;
+        const uint32_t slot = r.g % kSlots;
+        r.head = off + sz;
+        if (lane == 0) {
+          c.off[slot] = off;
+          c.meta[slot][0] = (kc == 0 ? FLAG_FIRST : 0) | (kc == nk - 1 ? FLAG_LAST : 0);
+          c.meta[slot][1] = nrows;
+          c.meta[slot][2] = n;
+          c.meta[slot][3] = j0;
+          c.meta[slot][4] = p;
+          c.meta[slot][5] = klen;
+          c.meta[slot][6] = static_cast<int>(off);
+        }
+        if (lane >= kMaxRows && lane < kMaxRows + kTileTokens) c.meta[slot][8 + lane - kMaxRows] = mytok;
+        __syncwarp();
+        if (lane == 0) mbar_expect_tx(&c.full[slot], static_cast<uint32_t>(nrows + n) * bytes);
+        __syncwarp();
+        ring_issue(r, c, slot, ring_base + off + static_cast<uint32_t>(myslot) * bytes,
+                   src0 + static_cast<int64_t>(kc) * kKC, (is_w || is_x) ? bytes : 0u, is_x, lane);
+      }
     }
   }
-  if (dead) {
-    if (lane == 0) set_status(a.status, SLORA_STATUS_TIMEOUT);
-    return;
-  }
-  // end marker
-  const int s = g % kPipeStages;
-  const uint32_t round = g / kPipeStages;
-  if (round > 0 && !mbar_wait_timed(&empty[s], (round - 1) & 1)) {
-    if (lane == 0) set_status(a.status, SLORA_STATUS_TIMEOUT);
-    return;
-  }
-  if (lane == 0) {
-    smeta[s][0] = FLAG_END;
-    mbar_arrive(&full[s]);
-  }
+  ring_finish(r, c, a.status, lane);
 }
 
-template <typename T>
-__device__ __forceinline__ void shrink_consumer(const ShrinkArgs& a, const unsigned char* stage_mem, uint64_t* full,
-                                                uint64_t* empty, int (*smeta)[16], int lane, int cw) {
-  pdl_wait();
-  float acc[kTileTokens];
+// Warp-level part of the per-item reduction: V = 4 * NT partial sums per lane (row-major [row][token]) are summed
+// across the warp and handed to the cross-warp buffer; lane l ends up with the total of index l >> (5 - log2 V).
+template <int NT>
+__device__ __forceinline__ void shrink_warp_reduce(const float (&acc)[kMaxRows][kTileTokens], float* red_row, int lane) {
+  constexpr int V = kMaxRows * NT;
+  float v[V];
 #pragma unroll
-  for (int i = 0; i < kTileTokens; ++i) acc[i] = 0.f;
+  for (int j = 0; j < kMaxRows; ++j) {
+#pragma unroll
+    for (int i = 0; i < NT; ++i) v[j * NT + i] = acc[j][i];
+  }
+  const float tot = warp_reduce_scatter<V>(v, lane);
+  constexpr int SH = V == 32 ? 0 : (V == 16 ? 1 : (V == 8 ? 2 : 3));
+  if ((lane & ((1 << SH) - 1)) == 0) red_row[lane >> SH] = tot;
+}
+
+// Consumer warp cw owns the K-slice [cw*256, +256) of every chunk: one 16-byte vector per lane per row / token, so a
+// stage is straight-line code with 4 * n independent FMA chains.  At the item's last chunk the warps' partial sums
+// meet in shared memory; the warp that arrives last (an atomic counter, no waiting) adds them in a fixed order and
+// writes delta.  A reduction buffer is reused only kSlots items later, which the ring guarantees to be after the
+// last warp released the stage it was summing in.
+template <typename T>
+__device__ __forceinline__ void shrink_consumer(const ShrinkArgs& a, const unsigned char* ring_mem, PipeCtl& c,
+                                                int lane, int cw) {
+  pdl_wait();
+  float acc[kMaxRows][kTileTokens];
+#pragma unroll
+  for (int j = 0; j < kMaxRows; ++j) {
+#pragma unroll
+    for (int i = 0; i < kTileTokens; ++i) acc[j][i] = 0.f;
+  }
+  uint32_t item_seq = 0;
   for (uint32_t g = 0;; ++g) {
-    const int s = g % kPipeStages;
-    if (!mbar_wait_timed(&full[s], (g / kPipeStages) & 1)) {
+    const uint32_t slot = g % kSlots;
+    if (!mbar_wait_timed(&c.full[slot], (g / kSlots) & 1)) {
       if (lane == 0) set_status(a.status, SLORA_STATUS_TIMEOUT);
       return;
     }
-    const int* m = smeta[s];
+    const int* m = c.meta[slot];
     const int flags = m[0];
     if (flags & FLAG_END) return;
     const int nrows = m[1], n = m[2], klen = m[5];
-    if (cw < nrows) {
-      const T* st = reinterpret_cast<const T*>(stage_mem + static_cast<size_t>(s) * kShrinkStageBytes);
-      const T* wrow = st + cw * kKC;
-      const T* xs = st + kMaxRows * kKC;
-      if (flags & FLAG_FIRST) {
+    if (flags & FLAG_FIRST) {
 #pragma unroll
-        for (int i = 0; i < kTileTokens; ++i) acc[i] = 0.f;
+      for (int j = 0; j < kMaxRows; ++j) {
+#pragma unroll
+        for (int i = 0; i < kTileTokens; ++i) acc[j][i] = 0.f;
       }
-      for (int k = lane * 8; k < klen; k += 256) {
-        float wf[8];
-        cvt8<T>(*reinterpret_cast<const uint4*>(wrow + k), wf);
+    }
+    const int k = cw * 256 + lane * 8;
+    if (k < klen) {
+      const T* st = reinterpret_cast<const T*>(ring_mem + m[6]);
+      const T* xs = st + nrows * klen;
+      uint4 wv[kMaxRows];
 #pragma unroll
-        for (int i = 0; i < kTileTokens; ++i) {
-          if (i < n) {
-            float xf[8];
-            cvt8<T>(*reinterpret_cast<const uint4*>(xs + i * kKC + k), xf);
-#pragma unroll
-            for (int e = 0; e < 8; ++e) acc[i] = fmaf(wf[e], xf[e], acc[i]);
-          }
-        }
+      for (int j = 0; j < kMaxRows; ++j) {
+        wv[j] = j < nrows ? *reinterpret_cast<const uint4*>(st + j * klen + k) : make_uint4(0u, 0u, 0u, 0u);
       }
-      if (flags & FLAG_LAST) {
-        const int j = m[3] + cw;
-        const float tot = warp_reduce_scatter<kTileTokens>(acc, lane);  // lane l: token l >> 2
-        const int i = lane >> 2;
-        if ((lane & 3) == 0 && i < n && j < a.delta_width) {
-          T* d = reinterpret_cast<T*>(pick3(a.delta, m[4]));
-          d[static_cast<int64_t>(m[8 + i]) * a.delta_stride + j] = from_f32<T>(tot);
+#pragma unroll
+      for (int i = 0; i < kTileTokens; ++i) {
+        if (i < n) {
+          const uint4 xv = *reinterpret_cast<const uint4*>(xs + i * klen + k);
+#pragma unroll
+          for (int j = 0; j < kMaxRows; ++j) dot8<T>(acc[j][i], wv[j], xv);
         }
       }
     }
+    if (flags & FLAG_LAST) {
+      const uint32_t buf = item_seq % kSlots;
+      ++item_seq;
+      float* red_row = c.red[buf][cw];
+      int nt;  // tokens rounded up to a power of two
+      if (n <= 1) {
+        shrink_warp_reduce<1>(acc, red_row, lane);
+        nt = 1;
+      } else if (n <= 2) {
+        shrink_warp_reduce<2>(acc, red_row, lane);
+        nt = 2;
+      } else if (n <= 4) {
+        shrink_warp_reduce<4>(acc, red_row, lane);
+        nt = 4;
+      } else {
+        shrink_warp_reduce<8>(acc, red_row, lane);
+        nt = 8;
+      }
+      __syncwarp();
+      int old = 0;
+      if (lane == 0) {
+        __threadfence_block();
+        old = atomicAdd(&c.red_cnt[buf], 1);
+      }
+      old = __shfl_sync(FULL_MASK, old, 0);
+      if (old == kConsumerWarps - 1) {
+        __threadfence_block();
+        const int j = lane / nt, i = lane - j * nt;  // red_row index = row * nt + token
+        if (lane < kMaxRows * nt) {
+          float sum = 0.f;
+#pragma unroll
+          for (int w = 0; w < kConsumerWarps; ++w) sum += c.red[buf][w][lane];
+          if (j < nrows && i < n && m[3] + j < a.delta_width) {
+            T* d = reinterpret_cast<T*>(pick3(a.delta, m[4]));
+            d[static_cast<int64_t>(m[8 + i]) * a.delta_stride + m[3] + j] = from_f32<T>(sum);
+          }
+        }
+        if (lane == 0) c.red_cnt[buf] = 0;
+      }
+    }
     __syncwarp();
-    if (lane == 0) mbar_arrive(&empty[s]);
+    if (lane == 0) mbar_arrive(&c.empty[slot]);
   }
 }
 
 template <typename T>
 __global__ void __launch_bounds__(kPipeThreads) lora_shrink_pipe_kernel(const ShrinkArgs a) {
-  extern __shared__ __align__(128) unsigned char stage_mem[];
-  __shared__ __align__(8) uint64_t full[kPipeStages];
-  __shared__ __align__(8) uint64_t empty[kPipeStages];
-  __shared__ int smeta[kPipeStages][16];
+  extern __shared__ __align__(128) unsigned char ring_mem[];
+  __shared__ __align__(16) PipeCtl ctl;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  if (tid == 0) {
-#pragma unroll
-    for (int s = 0; s < kPipeStages; ++s) {
-      mbar_init(&full[s], 1);
-      mbar_init(&empty[s], kConsumerWarps);
-    }
-    fence_barrier_init();
-    fence_proxy_async();
-  }
-  __syncthreads();
+  pipe_init(ctl, tid);
   pdl_launch_dependents();
   if (warp == 0) {
-    shrink_producer<T>(a, stage_mem, full, empty, smeta, lane);
+    shrink_producer<T>(a, ring_mem, ctl, lane);
   } else {
-    shrink_consumer<T>(a, stage_mem, full, empty, smeta, lane, warp - 1);
+    shrink_consumer<T>(a, ring_mem, ctl, lane, warp - 1);
   }
 }
 
 // ------------------------------------------------------------------------------------------------------------
 // expand
+// stage meta: [0] flags [1] n [2] r [3] projection [4] clen [5] first output [6] scale bits [7] ring offset,
+//             [8..15] token ids
+// stage bytes: B chunk (clen elements), then n y segments of clen / r elements, then n delta rows of r elements
 // ------------------------------------------------------------------------------------------------------------
 template <typename T>
-__device__ __forceinline__ void expand_producer(const ExpandArgs& a, unsigned char* stage_mem, uint64_t* full,
-                                                uint64_t* empty, int (*smeta)[16], int lane) {
+__device__ __forceinline__ void expand_producer(const ExpandArgs& a, unsigned char* ring_mem, PipeCtl& c, int lane) {
   const int total_chunks = a.chunk_begin[a.nproj];
-  const int per_tile = 2 * total_chunks;
-  const int64_t n_items = static_cast<int64_t>(tile_count(a.src)) * per_tile;
+  const int64_t n_items = static_cast<int64_t>(tile_count(a.src)) * total_chunks;
   const int64_t S = a.tb.pool_stride;
   const T* w = reinterpret_cast<const T*>(a.w);
   const int64_t G = gridDim.x;
-  uint32_t g = 0;
-  bool waited = false, dead = false;
+  const uint32_t ring_base = smem_u32(ring_mem);
+  Ring r;
 
-  for (int64_t batch0 = blockIdx.x; batch0 < n_items && !dead; batch0 += 32 * G) {
+  for (int64_t batch0 = blockIdx.x; batch0 < n_items && !r.dead; batch0 += 32 * G) {
     const int64_t item = batch0 + lane * G;
-    int m_valid = 0, m_nt = 0, m_r = 0, m_p = 0, m_clen = 0, m_obase = 0, m_c0 = 0, m_pr0 = 0;
+    int m_valid = 0, m_n = 0, m_r = 0, m_p = 0, m_clen = 0, m_obase = 0, m_c0 = 0, m_pr0 = 0;
     float m_scale = 0.f;
-    int m_tok[kHalfTokens];
+    int m_tok[kTileTokens];
     int64_t m_e[kSpanRows];
 #pragma unroll
-    for (int i = 0; i < kHalfTokens; ++i) m_tok[i] = 0;
+    for (int i = 0; i < kTileTokens; ++i) m_tok[i] = 0;
 #pragma unroll
     for (int j = 0; j < kSpanRows; ++j) m_e[j] = 0;
     if (item < n_items) {
-      const int tile = static_cast<int>(item / per_tile);
-      const int rem = static_cast<int>(item - static_cast<int64_t>(tile) * per_tile);
-      const int half = rem / total_chunks;
-      int c = rem - half * total_chunks;
+      const int tile = static_cast<int>(item / total_chunks);
+      int ch = static_cast<int>(item - static_cast<int64_t>(tile) * total_chunks);
       int p = 0;
-      while (p + 1 < a.nproj && c >= a.chunk_begin[p + 1]) ++p;
-      c -= a.chunk_begin[p];
+      while (p + 1 < a.nproj && ch >= a.chunk_begin[p + 1]) ++p;
+      ch -= a.chunk_begin[p];
       TileInfo t;
-      if (lookup_tile(a.src, a.tb, tile, t, a.status) && half * kHalfTokens < t.n) {
-        const int r = t.r * a.rank_mult;
+      if (lookup_tile(a.src, a.tb, tile, t, a.status)) {
+        const int rk = t.r * a.rank_mult;
         const int h_out = pick3(a.h_out, p);
-        const int64_t flat_total = static_cast<int64_t>(h_out) * r;
-        const int64_t c0 = static_cast<int64_t>(c) * kChunk;
+        const int64_t flat_total = static_cast<int64_t>(h_out) * rk;
+        const int64_t c0 = static_cast<int64_t>(ch) * kChunk;
         if (c0 < flat_total) {
-          if (r != 8 && r != 16 && r != 32 && r != 64 && r != 128) {
+          if (rk != 8 && rk != 16 && rk != 32 && rk != 64 && rk != 128) {
             set_status(a.status, SLORA_STATUS_BAD_RANK);
           } else {
             const int clen = static_cast<int>(min(static_cast<int64_t>(kChunk), flat_total - c0));
@@ -348,17 +491,17 @@ __device__ __forceinline__ void expand_producer(const ExpandArgs& a, unsigned ch
               }
             }
             if (ok) {
-              m_nt = min(kHalfTokens, t.n - half * kHalfTokens);
 #pragma unroll
-              for (int i = 0; i < kHalfTokens; ++i) {
-                if (i < m_nt) m_tok[i] = tile_token(t, half * kHalfTokens + i);
+              for (int i = 0; i < kTileTokens; ++i) {
+                if (i < t.n) m_tok[i] = tile_token(t, i);
               }
               m_valid = 1;
-              m_r = r;
+              m_n = t.n;
+              m_r = rk;
               m_p = p;
               m_clen = clen;
               m_c0 = static_cast<int>(c0);
-              m_obase = static_cast<int>(c0 / r);
+              m_obase = static_cast<int>(c0 / rk);
               m_pr0 = static_cast<int>(pr0);
               m_scale = to_f32<T>(reinterpret_cast<const T*>(a.scales)[t.adapter]);
             } else {
@@ -369,212 +512,188 @@ __device__ __forceinline__ void expand_producer(const ExpandArgs& a, unsigned ch
       }
     }
 
-    auto emit = [&](uint32_t g0, uint32_t lo, uint32_t hi, bool do_w, bool do_x) -> uint32_t {
-      uint32_t gg = g0;
-      for (int k = 0; k < 32; ++k) {
-        if (!__shfl_sync(FULL_MASK, m_valid, k)) continue;
-        const uint32_t cur = gg++;
-        if (cur < lo || cur >= hi || dead) continue;
-        const int nt = __shfl_sync(FULL_MASK, m_nt, k);
-        const int r = __shfl_sync(FULL_MASK, m_r, k);
-        const int p = __shfl_sync(FULL_MASK, m_p, k);
-        const int clen = __shfl_sync(FULL_MASK, m_clen, k);
-        const int obase = __shfl_sync(FULL_MASK, m_obase, k);
-        const int c0 = __shfl_sync(FULL_MASK, m_c0, k);
-        const int pr0 = __shfl_sync(FULL_MASK, m_pr0, k);
-        const float scale = __shfl_sync(FULL_MASK, m_scale, k);
-        int64_t e[kSpanRows];
+    for (int k = 0; k < 32 && !r.dead; ++k) {
+      if (!__shfl_sync(FULL_MASK, m_valid, k)) continue;
+      const int n = __shfl_sync(FULL_MASK, m_n, k);
+      const int rk = __shfl_sync(FULL_MASK, m_r, k);
+      const int p = __shfl_sync(FULL_MASK, m_p, k);
+      const int clen = __shfl_sync(FULL_MASK, m_clen, k);
+      const int obase = __shfl_sync(FULL_MASK, m_obase, k);
+      const int c0 = __shfl_sync(FULL_MASK, m_c0, k);
+      const int pr0 = __shfl_sync(FULL_MASK, m_pr0, k);
+      const float scale = __shfl_sync(FULL_MASK, m_scale, k);
+      int64_t e[kSpanRows];
 #pragma unroll
-        for (int j = 0; j < kSpanRows; ++j) e[j] = __shfl_sync(FULL_MASK, m_e[j], k);
-        int mytok = 0;
+      for (int j = 0; j < kSpanRows; ++j) e[j] = __shfl_sync(FULL_MASK, m_e[j], k);
+      int mytok = 0;
 #pragma unroll
-        for (int i = 0; i < kHalfTokens; ++i) {
-          const int v = __shfl_sync(FULL_MASK, m_tok[i], k);
-          if ((lane & 3) == i) mytok = v;  // lanes 8..11 (y) and 12..15 (delta) pick token lane & 3
-        }
-        const int s = cur % kPipeStages;
-        const uint32_t round = cur / kPipeStages;
-        const int nout = clen / r;
-        unsigned char* st = stage_mem + static_cast<size_t>(s) * kExpandStageBytes;
-        if (do_w) {
-          if (round > 0 && !mbar_wait_timed(&empty[s], (round - 1) & 1)) {
-            dead = true;
-            continue;
-          }
-          if (lane == 0) {
-            smeta[s][0] = 0;
-            smeta[s][1] = nt;
-            smeta[s][2] = r;
-            smeta[s][3] = p;
-            smeta[s][4] = clen;
-            smeta[s][5] = obase;
-            smeta[s][6] = __float_as_int(scale);
-          }
-          if (lane >= 8 && lane < 8 + kHalfTokens) smeta[s][lane] = mytok;
-          __syncwarp();
-          if (lane == 0) {
-            mbar_expect_tx(&full[s], static_cast<uint32_t>(clen) * sizeof(T) +
-                                         static_cast<uint32_t>(nt) * static_cast<uint32_t>(nout + r) * sizeof(T));
-          }
-          __syncwarp();
-          const int off = lane * a.piece;
-          if (lane < kMaxPieces && off < clen) {
-            const int64_t f = static_cast<int64_t>(c0) + off;
-            const int64_t pr = f / S, col = f - pr * S;
-            const int d = static_cast<int>(pr) - pr0;
-            const int64_t row = d == 0 ? e[0] : (d == 1 ? e[1] : (d == 2 ? e[2] : e[3]));
-            bulk_g2s(st + static_cast<size_t>(off) * sizeof(T), w + row * S + col,
-                     static_cast<uint32_t>(min(a.piece, clen - off)) * sizeof(T), &full[s]);
-          }
-        }
-        if (do_x) {
-          if (lane >= 8 && lane < 8 + nt) {
-            const T* y = reinterpret_cast<const T*>(pick3(a.y, p));
-            bulk_g2s(st + kChunk * 2 + (lane - 8) * kYSlot * 2,
-                     y + static_cast<int64_t>(mytok) * pick3(a.y_stride, p) + obase,
-                     static_cast<uint32_t>(nout) * sizeof(T), &full[s]);
-          } else if (lane >= 12 && lane < 12 + nt) {
-            const T* d = reinterpret_cast<const T*>(pick3(a.delta, p));
-            bulk_g2s(st + kChunk * 2 + kExpandYBytes + (lane - 12) * 256,
-                     d + static_cast<int64_t>(mytok) * a.delta_stride, static_cast<uint32_t>(r) * sizeof(T),
-                     &full[s]);
-          }
-        }
+      for (int i = 0; i < kTileTokens; ++i) {
+        const int v = __shfl_sync(FULL_MASK, m_tok[i], k);
+        if ((lane & 7) == i) mytok = v;  // lanes 8..15 (y) and 16..23 (delta) carry token lane & 7
       }
-      return gg;
-    };
-
-    if (!waited) {
-      emit(0, 0, kPipeStages, true, false);
-      pdl_wait();
-      waited = true;
-      emit(0, 0, kPipeStages, false, true);
-      g = emit(0, kPipeStages, 0xffffffffu, true, true);
-    } else {
-      g = emit(g, 0, 0xffffffffu, true, true);
+      const int nout = clen / rk;
+      const uint32_t b_bytes = static_cast<uint32_t>(clen) * sizeof(T);
+      const uint32_t y_bytes = static_cast<uint32_t>(nout) * sizeof(T);
+      const uint32_t d_bytes = static_cast<uint32_t>(rk) * sizeof(T);
+      const uint32_t total = b_bytes + static_cast<uint32_t>(n) * (y_bytes + d_bytes);
+      const uint32_t sz = round128(total);
+      const uint32_t off = ring_alloc(r, c, sz, lane);
+      if (r.dead) break;
+      const uint32_t slot = r.g % kSlots;
+      r.head = off + sz;
+      if (lane == 0) {
+        c.off[slot] = off;
+        c.meta[slot][0] = 0;
+        c.meta[slot][1] = n;
+        c.meta[slot][2] = rk;
+        c.meta[slot][3] = p;
+        c.meta[slot][4] = clen;
+        c.meta[slot][5] = obase;
+        c.meta[slot][6] = __float_as_int(scale);
+        c.meta[slot][7] = static_cast<int>(off);
+      }
+      if (lane >= 8 && lane < 8 + kTileTokens) c.meta[slot][lane] = mytok;
+      __syncwarp();
+      if (lane == 0) mbar_expect_tx(&c.full[slot], total);
+      __syncwarp();
+      // one copy per lane: 0..7 pieces of the B chunk, 8..15 y segments, 16..23 delta rows
+      uint32_t dst = ring_base + off, bytes = 0;
+      const T* src = w;
+      bool is_act = false;
+      if (lane < kMaxPieces) {
+        const int poff = lane * a.piece;
+        if (poff < clen) {
+          const int64_t f = static_cast<int64_t>(c0) + poff;
+          const int64_t pr = f / S, col = f - pr * S;
+          const int d = static_cast<int>(pr) - pr0;
+          const int64_t row = d == 0 ? e[0] : (d == 1 ? e[1] : (d == 2 ? e[2] : e[3]));
+          src = w + row * S + col;
+          dst += static_cast<uint32_t>(poff) * sizeof(T);
+          bytes = static_cast<uint32_t>(min(a.piece, clen - poff)) * sizeof(T);
+        }
+      } else if (lane < 8 + n) {
+        src = reinterpret_cast<const T*>(pick3(a.y, p)) + static_cast<int64_t>(mytok) * pick3(a.y_stride, p) + obase;
+        dst += b_bytes + static_cast<uint32_t>(lane - 8) * y_bytes;
+        bytes = y_bytes;
+        is_act = true;
+      } else if (lane >= 16 && lane < 16 + n) {
+        src = reinterpret_cast<const T*>(pick3(a.delta, p)) + static_cast<int64_t>(mytok) * a.delta_stride;
+        dst += b_bytes + static_cast<uint32_t>(n) * y_bytes + static_cast<uint32_t>(lane - 16) * d_bytes;
+        bytes = d_bytes;
+        is_act = true;
+      }
+      ring_issue(r, c, slot, dst, src, bytes, is_act, lane);
     }
   }
-  if (dead) {
-    if (lane == 0) set_status(a.status, SLORA_STATUS_TIMEOUT);
-    return;
-  }
-  const int s = g % kPipeStages;
-  const uint32_t round = g / kPipeStages;
-  if (round > 0 && !mbar_wait_timed(&empty[s], (round - 1) & 1)) {
-    if (lane == 0) set_status(a.status, SLORA_STATUS_TIMEOUT);
-    return;
-  }
-  if (lane == 0) {
-    smeta[s][0] = FLAG_END;
-    mbar_arrive(&full[s]);
+  ring_finish(r, c, a.status, lane);
+}
+
+// Butterfly over the 4 per-lane partial sums of an expand consumer warp (LPO = r / 8 lanes share one output): after
+// it lane l owns NV = max(1, 4 / LPO) complete outputs, those of loads m_base(l) + i.
+template <int HALF>
+__device__ __forceinline__ void exch4(float (&v)[4], int lane, int mask) {
+  const bool up = (lane & mask) != 0;
+#pragma unroll
+  for (int i = 0; i < HALF; ++i) {
+    const float keep = up ? v[i + HALF] : v[i];
+    const float send = up ? v[i] : v[i + HALF];
+    v[i] = keep + __shfl_xor_sync(0xffffffffu, send, mask);
   }
 }
 
 // One consumer warp's part of an expand stage.  LPO = lanes per output = r / 8.  The warp owns flat elements
-// [cw*2048, +2048) of the chunk as 8 loads of 256 elements; load m, lane l holds the 8 values of output
-// (cw*8 + m)*(32/LPO) + l/LPO for k in [(l % LPO)*8, +8).
+// [cw*1024, +1024) of the chunk as 4 loads of 256 elements; load m, lane l holds the 8 values of output
+// (cw*4 + m)*(32/LPO) + l/LPO for k in [(l % LPO)*8, +8).
 template <typename T, int LPO>
-__device__ __forceinline__ void expand_stage(const T* bs, const T* ys, const T* ds, const int* m, T* y,
-                                             int64_t y_stride, int h_out, int lane, int cw) {
+__device__ __forceinline__ void expand_stage(const T* bs, const int* m, T* y, int64_t y_stride, int lane, int cw) {
   constexpr int OPL = 32 / LPO;
-  constexpr int NV = LPO >= 8 ? 1 : 8 / LPO;
-  const int nt = m[1], clen = m[4], obase = m[5];
+  constexpr int NV = LPO >= 4 ? 1 : 4 / LPO;
+  constexpr int R = LPO * 8;
+  constexpr int SPAN = kChunk / kConsumerWarps;  // 1024
+  const int n = m[1], clen = m[4], obase = m[5];
+  if (cw * SPAN >= clen) return;
+  const int nout = clen / R;
   const float scale = __int_as_float(m[6]);
-  float bf[8][8];
+  const T* ys = bs + clen;
+  const T* ds = ys + n * nout;
+  uint4 bv[4];
 #pragma unroll
-  for (int mm = 0; mm < 8; ++mm) {
-    const int foff = cw * (kChunk / kConsumerWarps) + mm * 256 + lane * 8;
-    if (foff < clen) {
-      cvt8<T>(*reinterpret_cast<const uint4*>(bs + foff), bf[mm]);
-    } else {
-#pragma unroll
-      for (int e = 0; e < 8; ++e) bf[mm][e] = 0.f;
-    }
+  for (int mm = 0; mm < 4; ++mm) {
+    const int foff = cw * SPAN + mm * 256 + lane * 8;
+    bv[mm] = foff < clen ? *reinterpret_cast<const uint4*>(bs + foff) : make_uint4(0u, 0u, 0u, 0u);
   }
   const int kp = (lane & (LPO - 1)) * 8;
   const int g = lane / LPO;
-  const int m_base = expand_m_base<LPO>(lane);
-  const bool writer = (LPO < 16) || ((lane & 8) == 0);
+  int m_base = 0;
+  if (LPO >= 2) m_base += (lane & 1) ? 2 : 0;
+  if (LPO >= 4) m_base += (lane & 2) ? 1 : 0;
+  const bool writer = (LPO < 8 || (lane & 4) == 0) && (LPO < 16 || (lane & 8) == 0);
   int o_loc[NV];
 #pragma unroll
-  for (int i = 0; i < NV; ++i) o_loc[i] = (cw * 8 + m_base + i) * OPL + g;  // output index inside the chunk
+  for (int i = 0; i < NV; ++i) o_loc[i] = (cw * 4 + m_base + i) * OPL + g;  // output index inside the chunk
 
-  for (int tt = 0; tt < nt; ++tt) {
-    float d[8];
-    cvt8<T>(*reinterpret_cast<const uint4*>(ds + tt * 128 + kp), d);
-    float v[8];
+  for (int tt = 0; tt < n; ++tt) {
+    const uint4 dv = *reinterpret_cast<const uint4*>(ds + tt * R + kp);
+    float yv[NV];
 #pragma unroll
-    for (int mm = 0; mm < 8; ++mm) {
-      float sacc = 0.f;
+    for (int i = 0; i < NV; ++i) yv[i] = (writer && o_loc[i] < nout) ? to_f32<T>(ys[tt * nout + o_loc[i]]) : 0.f;
+    float v[4];
 #pragma unroll
-      for (int e = 0; e < 8; ++e) sacc = fmaf(bf[mm][e], d[e], sacc);
-      v[mm] = sacc;
+    for (int mm = 0; mm < 4; ++mm) {
+      v[mm] = 0.f;
+      dot8<T>(v[mm], bv[mm], dv);
     }
-    expand_butterfly<LPO>(v, lane);
+    if (LPO >= 2) exch4<2>(v, lane, 1);
+    if (LPO >= 4) exch4<1>(v, lane, 2);
+    if (LPO >= 8) v[0] += __shfl_xor_sync(0xffffffffu, v[0], 4);
+    if (LPO >= 16) v[0] += __shfl_xor_sync(0xffffffffu, v[0], 8);
     T* yrow = y + static_cast<int64_t>(m[8 + tt]) * y_stride + obase;
 #pragma unroll
     for (int i = 0; i < NV; ++i) {
-      if (writer && obase + o_loc[i] < h_out) {
-        yrow[o_loc[i]] = from_f32<T>(to_f32<T>(ys[tt * kYSlot + o_loc[i]]) + scale * v[i]);
-      }
+      if (writer && o_loc[i] < nout) yrow[o_loc[i]] = from_f32<T>(fmaf(scale, v[i], yv[i]));
     }
   }
 }
 
 template <typename T>
-__device__ __forceinline__ void expand_consumer(const ExpandArgs& a, const unsigned char* stage_mem, uint64_t* full,
-                                                uint64_t* empty, int (*smeta)[16], int lane, int cw) {
+__device__ __forceinline__ void expand_consumer(const ExpandArgs& a, const unsigned char* ring_mem, PipeCtl& c,
+                                                int lane, int cw) {
   pdl_wait();
   for (uint32_t g = 0;; ++g) {
-    const int s = g % kPipeStages;
-    if (!mbar_wait_timed(&full[s], (g / kPipeStages) & 1)) {
+    const uint32_t slot = g % kSlots;
+    if (!mbar_wait_timed(&c.full[slot], (g / kSlots) & 1)) {
       if (lane == 0) set_status(a.status, SLORA_STATUS_TIMEOUT);
       return;
     }
-    const int* m = smeta[s];
+    const int* m = c.meta[slot];
     if (m[0] & FLAG_END) return;
-    const unsigned char* st = stage_mem + static_cast<size_t>(s) * kExpandStageBytes;
-    const T* bs = reinterpret_cast<const T*>(st);
-    const T* ys = reinterpret_cast<const T*>(st + kChunk * 2);
-    const T* ds = reinterpret_cast<const T*>(st + kChunk * 2 + kExpandYBytes);
+    const T* bs = reinterpret_cast<const T*>(ring_mem + m[7]);
     const int p = m[3];
     T* y = reinterpret_cast<T*>(pick3(a.y, p));
     const int64_t ystr = pick3(a.y_stride, p);
-    const int h_out = pick3(a.h_out, p);
     switch (m[2]) {
-      case 8: expand_stage<T, 1>(bs, ys, ds, m, y, ystr, h_out, lane, cw); break;
-      case 16: expand_stage<T, 2>(bs, ys, ds, m, y, ystr, h_out, lane, cw); break;
-      case 32: expand_stage<T, 4>(bs, ys, ds, m, y, ystr, h_out, lane, cw); break;
-      case 64: expand_stage<T, 8>(bs, ys, ds, m, y, ystr, h_out, lane, cw); break;
-      default: expand_stage<T, 16>(bs, ys, ds, m, y, ystr, h_out, lane, cw); break;
+      case 8: expand_stage<T, 1>(bs, m, y, ystr, lane, cw); break;
+      case 16: expand_stage<T, 2>(bs, m, y, ystr, lane, cw); break;
+      case 32: expand_stage<T, 4>(bs, m, y, ystr, lane, cw); break;
+      case 64: expand_stage<T, 8>(bs, m, y, ystr, lane, cw); break;
+      default: expand_stage<T, 16>(bs, m, y, ystr, lane, cw); break;
     }
     __syncwarp();
-    if (lane == 0) mbar_arrive(&empty[s]);
+    if (lane == 0) mbar_arrive(&c.empty[slot]);
   }
 }
 
 template <typename T>
 __global__ void __launch_bounds__(kPipeThreads) lora_expand_pipe_kernel(const ExpandArgs a) {
-  extern __shared__ __align__(128) unsigned char stage_mem[];
-  __shared__ __align__(8) uint64_t full[kPipeStages];
-  __shared__ __align__(8) uint64_t empty[kPipeStages];
-  __shared__ int smeta[kPipeStages][16];
+  extern __shared__ __align__(128) unsigned char ring_mem[];
+  __shared__ __align__(16) PipeCtl ctl;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  if (tid == 0) {
-#pragma unroll
-    for (int s = 0; s < kPipeStages; ++s) {
-      mbar_init(&full[s], 1);
-      mbar_init(&empty[s], kConsumerWarps);
-    }
-    fence_barrier_init();
-    fence_proxy_async();
-  }
-  __syncthreads();
+  pipe_init(ctl, tid);
   pdl_launch_dependents();
   if (warp == 0) {
-    expand_producer<T>(a, stage_mem, full, empty, smeta, lane);
+    expand_producer<T>(a, ring_mem, ctl, lane);
   } else {
-    expand_consumer<T>(a, stage_mem, full, empty, smeta, lane, warp - 1);
+    expand_consumer<T>(a, ring_mem, ctl, lane, warp - 1);
   }
 }
 
