@@ -285,7 +285,6 @@ int run_expand(const TileSrc& src, const Tables& tb, const void* w, const void* 
   a.w = w;
   a.scales = scales;
   a.nproj = nproj;
-  a.chunk_begin[0] = 0;
   for (int p = 0; p < nproj; ++p) {
     if (!y[p] || !delta[p]) return fail(SLORA_ERR_NULL, "y[%d] or delta[%d] is null", p, p);
     if (qkvo[p] < 0 || qkvo[p] > 3) return fail(SLORA_ERR_QKVO, "qkvo=%d outside 0..3", qkvo[p]);
@@ -296,23 +295,31 @@ int run_expand(const TileSrc& src, const Tables& tb, const void* w, const void* 
     a.h_out[p] = h_out[p];
     a.delta[p] = delta[p];
     a.qkvo[p] = qkvo[p];
-    const int64_t chunks = (static_cast<int64_t>(h_out[p]) * max_rank + kChunk - 1) / kChunk;
-    a.chunk_begin[p + 1] = a.chunk_begin[p] + static_cast<int>(chunks);
   }
+  // work items per (tile, projection): chunks of `chunk` flat B elements at the widest rank the delta can hold
+  auto set_chunks = [&](int chunk) {
+    a.chunk_begin[0] = 0;
+    for (int p = 0; p < nproj; ++p) {
+      const int64_t chunks = (static_cast<int64_t>(h_out[p]) * max_rank + chunk - 1) / chunk;
+      a.chunk_begin[p + 1] = a.chunk_begin[p] + static_cast<int>(chunks);
+    }
+  };
   a.delta_stride = delta_stride;
   a.delta_parts = delta_parts;
   a.delta_part_stride = delta_part_stride;
   a.rank_mult = rank_mult;
-  a.piece = piece;
   a.status = status;
-  bool can_pipe = delta_parts == 1 && delta_stride % 8 == 0 && piece * kMaxPieces >= kChunk &&
-                  (kChunk - 1) / tb.pool_stride + 2 <= kSpanRows;
+  const int pipe_piece = pow2_divisor(tb.pool_stride, kPipeChunk);
+  bool can_pipe = delta_parts == 1 && delta_stride % 8 == 0 && pipe_piece * kMaxPieces >= kPipeChunk &&
+                  (kPipeChunk - 1) / tb.pool_stride + 2 <= kSpanRows;
   for (int p = 0; p < nproj; ++p)
     can_pipe = can_pipe && aligned16(y[p]) && y_stride[p] % 8 == 0 && aligned16(delta[p]);
   const KernelChoice choice = kernel_choice();
   if (choice == CHOOSE_PIPELINED && !can_pipe)
     return fail(SLORA_ERR_ALIGN, "pipelined expand needs 16-byte aligned y and delta rows and a plain delta layout");
   if (can_pipe && choice != CHOOSE_SIMPLE) {
+    a.piece = pipe_piece;
+    set_chunks(kPipeChunk);
     const int64_t items = static_cast<int64_t>(src.slots) * a.chunk_begin[nproj];
     const int64_t grid = items < sm_count() ? items : sm_count();
     const size_t smem = kRingBytes;
@@ -325,6 +332,8 @@ int run_expand(const TileSrc& src, const Tables& tb, const void* w, const void* 
     rc = ensure_dyn_smem(k, 3, smem);
     return rc ? rc : launch(k, grid, kPipeThreads, smem, flags, stream, a, "expand(pipelined)");
   }
+  a.piece = piece;
+  set_chunks(kChunk);
   const int64_t grid = static_cast<int64_t>(src.slots) * a.chunk_begin[nproj];
   if (dtype == SLORA_F16) return launch(lora_expand_kernel<__half>, grid, kThreads, 0, flags, stream, a, "expand");
   return launch(lora_expand_kernel<__nv_bfloat16>, grid, kThreads, 0, flags, stream, a, "expand");

@@ -1,9 +1,10 @@
 // Persistent, warp-specialised, mbarrier-pipelined LoRA shrink / expand kernels (the fast path).
 //
-// One CTA per SM walks its share of the work items (item i belongs to CTA i mod gridDim.x).  Warp 0 is the
-// producer: its 32 lanes resolve 32 upcoming items in parallel (tile record -> table entries -> row addresses and
-// token ids), then feed a ring of shared-memory stages with bulk asynchronous copies (cp.async.bulk + mbarrier
-// complete_tx).  Warps 1..8 are consumers: they wait on a stage's "full" barrier, do the arithmetic and release the
+// One CTA per SM walks its share of the work items (item i belongs to CTA i mod gridDim.x).  Warps 0 and 1 are
+// producers: the 32 lanes of each resolve 32 upcoming items in parallel (tile record -> table entries -> row
+// addresses and token ids), then feed a ring of shared-memory stages with bulk asynchronous copies (cp.async.bulk +
+// mbarrier complete_tx).  Both producers run the same deterministic allocation; stage g is issued by producer
+// g mod 2, because a single warp cannot issue bulk copies faster than ~35 GB/s.  Warps 2..9 are consumers: they wait on a stage's "full" barrier, do the arithmetic and release the
 // stage through its "empty" barrier.  Consumer warps never wait for each other (shrink: each warp owns a K-slice and
 // the last warp to finish an item, elected by an atomic counter, adds the partial sums; expand: each warp owns a
 // 1024-element span of the B chunk), so every wait in the kernel is an mbarrier wait with a time limit.
@@ -19,9 +20,10 @@
 // those stages; they go out right after the wait.  With a ring of 96 KB two kernels fit on an SM, so the next
 // kernel's prologue overlaps this kernel's tail.
 //
-// Shrink stage  = K-chunk of up to kKC elements of one item (tile, projection, block of <= 4 rows):
-//                 [nrows adapter-row chunks][n token-row chunks]; accumulators stay in registers across the chunks.
-// Expand stage  = one item (tile, projection, 8192-element chunk of B): [B chunk][n y segments][n delta rows].
+// Shrink stage  = one item (tile, projection, block of <= 4 rows), or a K-chunk of it when the item exceeds
+//                 kMaxStageBytes: [nrows adapter-row chunks][n token-row chunks]; accumulators stay in registers
+//                 across the chunks of an item.
+// Expand stage  = one item (tile, projection, 16384-element chunk of B): [B chunk][n y segments][n delta rows].
 //                 y is read through the stage and written back with plain coalesced stores.
 #pragma once
 
@@ -30,12 +32,15 @@
 namespace slora {
 
 constexpr int kSlots = 8;  // stage descriptors (barrier pairs) in flight
-constexpr int kRingBytes = 96 * 1024;
+constexpr int kRingBytes = 92 * 1024;  // ring + control block stay below half an SM's shared memory
+constexpr int kPendSlots = 4;           // stages that may be issued before the grid-dependency wait
+constexpr int kProducerWarps = 2;  // stage g is fed by producer warp g % kProducerWarps
 constexpr int kConsumerWarps = 8;
-constexpr int kPipeThreads = 32 * (1 + kConsumerWarps);
-constexpr int kKC = 2048;  // K elements per shrink stage
-constexpr int kMaxPieces = 8;  // B copies per expand stage (lanes 0..7); y copies use lanes 8..15, delta 16..23
-constexpr int kSpanRows = 4;   // pool rows a B chunk may touch
+constexpr int kPipeThreads = 32 * (kProducerWarps + kConsumerWarps);
+constexpr int kMaxStageBytes = 46 * 1024;  // a shrink item is cut into K-chunks no larger than this
+constexpr int kPipeChunk = 16384;          // flat B elements per expand item (32 KB)
+constexpr int kMaxPieces = 16;  // B copies per expand stage (lanes 0..15); y copies use lanes 16..23, delta 24..31
+constexpr int kSpanRows = 6;    // pool rows a B chunk may touch
 
 constexpr int FLAG_FIRST = 1, FLAG_LAST = 2, FLAG_END = 4;
 constexpr uint32_t FULL_MASK = 0xffffffffu;
@@ -59,11 +64,18 @@ struct PipeCtl {
   uint64_t full[kSlots];
   uint64_t empty[kSlots];
   int meta[kSlots][16];
-  uint32_t off[kSlots];          // producer only: byte offset of the stage in the ring
-  // activation copies of the stages issued before the grid-dependency wait (producer only, one entry per lane)
-  uint64_t pend_src[kSlots][32];
-  uint32_t pend_dst[kSlots][32];
-  uint32_t pend_bytes[kSlots][32];
+  // one private copy per producer warp of everything below
+  struct Prod {
+    uint32_t off[kSlots];  // byte offset of each stage in the ring
+    // activation copies of the stages issued before the grid-dependency wait (one entry per lane)
+    uint64_t pend_src[kPendSlots][32];
+    uint32_t pend_dst[kPendSlots][32];
+    uint32_t pend_bytes[kPendSlots][32];
+    // the 32 items a batch resolves, one per lane, parked here so that the lanes that carry the copies read what
+    // they need instead of receiving it through shuffles
+    int64_t d_l[32][kSpanRows];
+    int d_i[32][16];
+  } prod[kProducerWarps];
   // shrink only: per-item partial sums of the consumer warps and the arrival counter that elects the last warp
   float red[kSlots][kConsumerWarps][32];
   int red_cnt[kSlots];
@@ -71,6 +83,7 @@ struct PipeCtl {
 
 // Producer-side ring state (identical in all 32 lanes).
 struct Ring {
+  int role = 0;       // which producer warp this is
   uint32_t g = 0;     // next stage index
   uint32_t tail = 0;  // oldest stage not yet known to be released
   uint32_t head = 0;  // next free byte
@@ -81,12 +94,13 @@ struct Ring {
 
 __device__ __forceinline__ void ring_flush(Ring& r, PipeCtl& c, int lane) {
   pdl_wait();
+  PipeCtl::Prod& pp = c.prod[r.role];
   for (int i = 0; i < r.npend; ++i) {
     const uint32_t slot = (r.g - r.npend + i) % kSlots;
-    if (c.pend_bytes[slot][lane] != 0) {
+    if (pp.pend_bytes[i][lane] != 0) {
       asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
-                       c.pend_dst[slot][lane]),
-                   "l"(c.pend_src[slot][lane]), "r"(c.pend_bytes[slot][lane]), "r"(smem_u32(&c.full[slot]))
+                       pp.pend_dst[i][lane]),
+                   "l"(pp.pend_src[i][lane]), "r"(pp.pend_bytes[i][lane]), "r"(smem_u32(&c.full[slot]))
                    : "memory");
     }
   }
@@ -105,7 +119,7 @@ __device__ __forceinline__ uint32_t ring_alloc(Ring& r, PipeCtl& c, uint32_t sz,
       r.head = 0;
       ok = true;
     } else {
-      const uint32_t t = c.off[r.tail % kSlots];
+      const uint32_t t = c.prod[r.role].off[r.tail % kSlots];
       if (r.head > t) {
         if (r.head + sz <= kRingBytes) {
           cand = r.head;
@@ -119,7 +133,7 @@ __device__ __forceinline__ uint32_t ring_alloc(Ring& r, PipeCtl& c, uint32_t sz,
         ok = r.head + sz <= t && r.head != t;
       }
     }
-    if (ok && r.g - r.tail < kSlots) return cand;
+    if (ok && r.g - r.tail < kSlots && !(r.pre && r.npend == kPendSlots)) return cand;
     if (r.pre) {
       ring_flush(r, c, lane);
       continue;
@@ -136,10 +150,12 @@ __device__ __forceinline__ uint32_t ring_alloc(Ring& r, PipeCtl& c, uint32_t sz,
 // (is_act) issued before the grid-dependency wait are stashed instead.
 __device__ __forceinline__ void ring_issue(Ring& r, PipeCtl& c, uint32_t slot, uint32_t dst, const void* src,
                                            uint32_t bytes, bool is_act, int lane) {
+  if (static_cast<int>(r.g % kProducerWarps) != r.role) bytes = 0;  // the other producer's stage
   if (r.pre) {
-    c.pend_bytes[slot][lane] = is_act ? bytes : 0;
-    c.pend_dst[slot][lane] = dst;
-    c.pend_src[slot][lane] = reinterpret_cast<uint64_t>(src);
+    PipeCtl::Prod& pp = c.prod[r.role];
+    pp.pend_bytes[r.npend][lane] = is_act ? bytes : 0;
+    pp.pend_dst[r.npend][lane] = dst;
+    pp.pend_src[r.npend][lane] = reinterpret_cast<uint64_t>(src);
     if (is_act) bytes = 0;
   }
   if (bytes != 0) {
@@ -160,8 +176,7 @@ __device__ __forceinline__ void ring_finish(Ring& r, PipeCtl& c, int32_t* status
     return;
   }
   const uint32_t slot = r.g % kSlots;
-  if (lane == 0) {
-    c.off[slot] = r.head;
+  if (lane == 0 && static_cast<int>(r.g % kProducerWarps) == r.role) {
     c.meta[slot][0] = FLAG_END;
     mbar_arrive(&c.full[slot]);
   }
@@ -194,28 +209,24 @@ __device__ __forceinline__ uint32_t round128(uint32_t v) { return (v + 127u) & ~
 // stage bytes: nrows chunks of klen elements (adapter rows), then n chunks of klen elements (token rows)
 // ------------------------------------------------------------------------------------------------------------
 template <typename T>
-__device__ __forceinline__ void shrink_producer(const ShrinkArgs& a, unsigned char* ring_mem, PipeCtl& c, int lane) {
+__device__ __forceinline__ void shrink_producer(const ShrinkArgs& a, unsigned char* ring_mem, PipeCtl& c, int lane,
+                                                int role) {
   const int per_tile = a.nproj * a.max_rb;
   const int64_t n_items = static_cast<int64_t>(tile_count(a.src)) * per_tile;
   const int h_in = a.h_in;
-  const int nk = (h_in + kKC - 1) / kKC;
   const int64_t S = a.tb.pool_stride;
   const T* w = reinterpret_cast<const T*>(a.w);
   const T* x = reinterpret_cast<const T*>(a.x);
   const int64_t G = gridDim.x;
   const uint32_t ring_base = smem_u32(ring_mem);
+  PipeCtl::Prod& pp = c.prod[role];
   Ring r;
+  r.role = role;
 
   for (int64_t batch0 = blockIdx.x; batch0 < n_items && !r.dead; batch0 += 32 * G) {
-    // ---- 32 items resolved in parallel, one per lane ----
+    // ---- 32 items resolved in parallel, one per lane; d_i[lane] = {valid, n, nrows, j0, p, -, -, -, tok[8]} ----
     const int64_t item = batch0 + lane * G;
-    int m_valid = 0, m_n = 0, m_nrows = 0, m_j0 = 0, m_p = 0;
-    int m_tok[kTileTokens];
-    int64_t m_row[kMaxRows];
-#pragma unroll
-    for (int i = 0; i < kTileTokens; ++i) m_tok[i] = 0;
-#pragma unroll
-    for (int j = 0; j < kMaxRows; ++j) m_row[j] = 0;
+    int valid = 0;
     if (item < n_items) {
       const int tile = static_cast<int>(item / per_tile);
       const int rem = static_cast<int>(item - static_cast<int64_t>(tile) * per_tile);
@@ -234,76 +245,74 @@ __device__ __forceinline__ void shrink_producer(const ShrinkArgs& a, unsigned ch
               const int64_t pr = f / S, col = f - pr * S;
               const int64_t e = pr < t.r ? a.tb.loc[base + pr] : -1;
               if (e < 0 || e >= a.tb.pool_rows) ok = false;
-              m_row[j] = e * S + col;
+              pp.d_l[lane][j] = e * S + col;
             }
           }
           if (ok) {
 #pragma unroll
-            for (int i = 0; i < kTileTokens; ++i) {
-              if (i < t.n) m_tok[i] = tile_token(t, i);
-            }
-            m_valid = 1;
-            m_n = t.n;
-            m_nrows = nrows;
-            m_j0 = j0;
-            m_p = p;
+            for (int i = 0; i < kTileTokens; ++i) pp.d_i[lane][8 + i] = i < t.n ? tile_token(t, i) : 0;
+            pp.d_i[lane][1] = t.n;
+            pp.d_i[lane][2] = nrows;
+            pp.d_i[lane][3] = j0;
+            pp.d_i[lane][4] = p;
+            valid = 1;
           } else {
             set_status(a.status, SLORA_STATUS_BAD_TABLE);
           }
         }
       }
     }
+    const uint32_t valid_mask = __ballot_sync(FULL_MASK, valid != 0);
+    __syncwarp();
 
-    // ---- feed the ring, item by item, chunk by chunk ----
-    for (int k = 0; k < 32 && !r.dead; ++k) {
-      if (!__shfl_sync(FULL_MASK, m_valid, k)) continue;
-      const int n = __shfl_sync(FULL_MASK, m_n, k);
-      const int nrows = __shfl_sync(FULL_MASK, m_nrows, k);
-      const int j0 = __shfl_sync(FULL_MASK, m_j0, k);
-      const int p = __shfl_sync(FULL_MASK, m_p, k);
-      // lane j < 4 carries adapter row j, lane 4 + i carries token i
-      int64_t mysrc = 0;
-      int mytok = 0;
-#pragma unroll
-      for (int j = 0; j < kMaxRows; ++j) {
-        const int64_t v = __shfl_sync(FULL_MASK, m_row[j], k);
-        if (lane == j) mysrc = v;
-      }
-#pragma unroll
-      for (int i = 0; i < kTileTokens; ++i) {
-        const int v = __shfl_sync(FULL_MASK, m_tok[i], k);
-        if (lane == kMaxRows + i) mytok = v;
-      }
+    // ---- feed the ring, item by item (lane j < 4 carries adapter row j, lane 4 + i carries token i) ----
+    for (uint32_t left = valid_mask; left != 0 && !r.dead; left &= left - 1) {
+      const int k = __ffs(left) - 1;
+      const int* di = pp.d_i[k];
+      const int n = di[1], nrows = di[2];
       const bool is_w = lane < nrows;
       const bool is_x = lane >= kMaxRows && lane < kMaxRows + n;
-      const T* src0 = is_w ? w + mysrc : x + static_cast<int64_t>(mytok) * a.x_stride;
+      const int mytok = (lane >= kMaxRows && lane < kMaxRows + kTileTokens) ? di[8 + lane - kMaxRows] : 0;
+      const T* src0 = is_w ? w + pp.d_l[k][lane & (kMaxRows - 1)] : x + static_cast<int64_t>(mytok) * a.x_stride;
       const int myslot = is_w ? lane : nrows + (lane - kMaxRows);  // position of this lane's chunk in the stage
-      for (int kc = 0; kc < nk; ++kc) {
-        const int klen = min(kKC, h_in - kc * kKC);
+      // cut the item into K-chunks that are multiples of 2048 elements (so the element -> consumer lane mapping, and
+      // with it the summation order, does not depend on how many tokens share the tile) and, where that allows,
+      // no larger than kMaxStageBytes
+      const int fit = kMaxStageBytes / ((nrows + n) * static_cast<int>(sizeof(T))) / 2048 * 2048;
+      const int kc_elems = fit < 2048 ? 2048 : fit;
+      for (int k0 = 0; k0 < h_in; k0 += kc_elems) {
+        const int klen = min(kc_elems, h_in - k0);
         const uint32_t bytes = static_cast<uint32_t>(klen) * sizeof(T);
         const uint32_t sz = round128(static_cast<uint32_t>(nrows + n) * bytes);
         const uint32_t off = ring_alloc(r, c, sz, lane);
         if (r.dead) break;
         const uint32_t slot = r.g % kSlots;
+        const bool mine = static_cast<int>(r.g % kProducerWarps) == role;
         r.head = off + sz;
+        if (lane == 0) pp.off[slot] = off;
+        if (!mine) {
+          __syncwarp();
+          ring_issue(r, c, slot, 0, nullptr, 0u, false, lane);
+          continue;
+        }
         if (lane == 0) {
-          c.off[slot] = off;
-          c.meta[slot][0] = (kc == 0 ? FLAG_FIRST : 0) | (kc == nk - 1 ? FLAG_LAST : 0);
+          c.meta[slot][0] = (k0 == 0 ? FLAG_FIRST : 0) | (k0 + klen >= h_in ? FLAG_LAST : 0);
           c.meta[slot][1] = nrows;
           c.meta[slot][2] = n;
-          c.meta[slot][3] = j0;
-          c.meta[slot][4] = p;
+          c.meta[slot][3] = di[3];
+          c.meta[slot][4] = di[4];
           c.meta[slot][5] = klen;
           c.meta[slot][6] = static_cast<int>(off);
+        } else if (lane >= kMaxRows && lane < kMaxRows + kTileTokens) {
+          c.meta[slot][8 + lane - kMaxRows] = mytok;
         }
-        if (lane >= kMaxRows && lane < kMaxRows + kTileTokens) c.meta[slot][8 + lane - kMaxRows] = mytok;
-        __syncwarp();
+        __syncwarp();  // the arrive below publishes every lane's part of the stage record
         if (lane == 0) mbar_expect_tx(&c.full[slot], static_cast<uint32_t>(nrows + n) * bytes);
-        __syncwarp();
-        ring_issue(r, c, slot, ring_base + off + static_cast<uint32_t>(myslot) * bytes,
-                   src0 + static_cast<int64_t>(kc) * kKC, (is_w || is_x) ? bytes : 0u, is_x, lane);
+        ring_issue(r, c, slot, ring_base + off + static_cast<uint32_t>(myslot) * bytes, src0 + k0,
+                   (is_w || is_x) ? bytes : 0u, is_x, lane);
       }
     }
+    __syncwarp();
   }
   ring_finish(r, c, a.status, lane);
 }
@@ -357,10 +366,9 @@ __device__ __forceinline__ void shrink_consumer(const ShrinkArgs& a, const unsig
         for (int i = 0; i < kTileTokens; ++i) acc[j][i] = 0.f;
       }
     }
-    const int k = cw * 256 + lane * 8;
-    if (k < klen) {
-      const T* st = reinterpret_cast<const T*>(ring_mem + m[6]);
-      const T* xs = st + nrows * klen;
+    const T* st = reinterpret_cast<const T*>(ring_mem + m[6]);
+    const T* xs = st + nrows * klen;
+    for (int k = cw * 256 + lane * 8; k < klen; k += kConsumerWarps * 256) {
       uint4 wv[kMaxRows];
 #pragma unroll
       for (int j = 0; j < kMaxRows; ++j) {
@@ -427,10 +435,10 @@ __global__ void __launch_bounds__(kPipeThreads) lora_shrink_pipe_kernel(const Sh
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   pipe_init(ctl, tid);
   pdl_launch_dependents();
-  if (warp == 0) {
-    shrink_producer<T>(a, ring_mem, ctl, lane);
+  if (warp < kProducerWarps) {
+    shrink_producer<T>(a, ring_mem, ctl, lane, warp);
   } else {
-    shrink_consumer<T>(a, ring_mem, ctl, lane, warp - 1);
+    shrink_consumer<T>(a, ring_mem, ctl, lane, warp - kProducerWarps);
   }
 }
 
@@ -441,25 +449,23 @@ __global__ void __launch_bounds__(kPipeThreads) lora_shrink_pipe_kernel(const Sh
 // stage bytes: B chunk (clen elements), then n y segments of clen / r elements, then n delta rows of r elements
 // ------------------------------------------------------------------------------------------------------------
 template <typename T>
-__device__ __forceinline__ void expand_producer(const ExpandArgs& a, unsigned char* ring_mem, PipeCtl& c, int lane) {
+__device__ __forceinline__ void expand_producer(const ExpandArgs& a, unsigned char* ring_mem, PipeCtl& c, int lane,
+                                                int role) {
   const int total_chunks = a.chunk_begin[a.nproj];
   const int64_t n_items = static_cast<int64_t>(tile_count(a.src)) * total_chunks;
   const int64_t S = a.tb.pool_stride;
   const T* w = reinterpret_cast<const T*>(a.w);
   const int64_t G = gridDim.x;
   const uint32_t ring_base = smem_u32(ring_mem);
+  PipeCtl::Prod& pp = c.prod[role];
   Ring r;
+  r.role = role;
 
   for (int64_t batch0 = blockIdx.x; batch0 < n_items && !r.dead; batch0 += 32 * G) {
+    // d_i[lane] = {valid, n, r, p, clen, first output, scale bits, c0, tok[8]}, d_l[lane][j] = pool row of slot row
+    // pr0 + j; d_i[lane][0] doubles as pr0
     const int64_t item = batch0 + lane * G;
-    int m_valid = 0, m_n = 0, m_r = 0, m_p = 0, m_clen = 0, m_obase = 0, m_c0 = 0, m_pr0 = 0;
-    float m_scale = 0.f;
-    int m_tok[kTileTokens];
-    int64_t m_e[kSpanRows];
-#pragma unroll
-    for (int i = 0; i < kTileTokens; ++i) m_tok[i] = 0;
-#pragma unroll
-    for (int j = 0; j < kSpanRows; ++j) m_e[j] = 0;
+    int valid = 0;
     if (item < n_items) {
       const int tile = static_cast<int>(item / total_chunks);
       int ch = static_cast<int>(item - static_cast<int64_t>(tile) * total_chunks);
@@ -471,12 +477,12 @@ __device__ __forceinline__ void expand_producer(const ExpandArgs& a, unsigned ch
         const int rk = t.r * a.rank_mult;
         const int h_out = pick3(a.h_out, p);
         const int64_t flat_total = static_cast<int64_t>(h_out) * rk;
-        const int64_t c0 = static_cast<int64_t>(ch) * kChunk;
+        const int64_t c0 = static_cast<int64_t>(ch) * kPipeChunk;
         if (c0 < flat_total) {
           if (rk != 8 && rk != 16 && rk != 32 && rk != 64 && rk != 128) {
             set_status(a.status, SLORA_STATUS_BAD_RANK);
           } else {
-            const int clen = static_cast<int>(min(static_cast<int64_t>(kChunk), flat_total - c0));
+            const int clen = static_cast<int>(min(static_cast<int64_t>(kPipeChunk), flat_total - c0));
             const int64_t base = t.loc_base + static_cast<int64_t>(t.r) * pick3(a.qkvo, p);
             const int64_t pr0 = c0 / S, pr1 = (c0 + clen - 1) / S;
             bool ok = pr1 - pr0 < kSpanRows && pr1 < t.r;
@@ -486,24 +492,22 @@ __device__ __forceinline__ void expand_producer(const ExpandArgs& a, unsigned ch
                 if (pr0 + j <= pr1) {
                   const int64_t e = a.tb.loc[base + pr0 + j];
                   if (e < 0 || e >= a.tb.pool_rows) ok = false;
-                  m_e[j] = e;
+                  pp.d_l[lane][j] = e;
                 }
               }
             }
             if (ok) {
 #pragma unroll
-              for (int i = 0; i < kTileTokens; ++i) {
-                if (i < t.n) m_tok[i] = tile_token(t, i);
-              }
-              m_valid = 1;
-              m_n = t.n;
-              m_r = rk;
-              m_p = p;
-              m_clen = clen;
-              m_c0 = static_cast<int>(c0);
-              m_obase = static_cast<int>(c0 / rk);
-              m_pr0 = static_cast<int>(pr0);
-              m_scale = to_f32<T>(reinterpret_cast<const T*>(a.scales)[t.adapter]);
+              for (int i = 0; i < kTileTokens; ++i) pp.d_i[lane][8 + i] = i < t.n ? tile_token(t, i) : 0;
+              pp.d_i[lane][0] = static_cast<int>(pr0);
+              pp.d_i[lane][1] = t.n;
+              pp.d_i[lane][2] = rk;
+              pp.d_i[lane][3] = p;
+              pp.d_i[lane][4] = clen;
+              pp.d_i[lane][5] = static_cast<int>(c0 / rk);
+              pp.d_i[lane][6] = __float_as_int(to_f32<T>(reinterpret_cast<const T*>(a.scales)[t.adapter]));
+              pp.d_i[lane][7] = static_cast<int>(c0);
+              valid = 1;
             } else {
               set_status(a.status, SLORA_STATUS_BAD_TABLE);
             }
@@ -511,26 +515,14 @@ __device__ __forceinline__ void expand_producer(const ExpandArgs& a, unsigned ch
         }
       }
     }
+    const uint32_t valid_mask = __ballot_sync(FULL_MASK, valid != 0);
+    __syncwarp();
 
-    for (int k = 0; k < 32 && !r.dead; ++k) {
-      if (!__shfl_sync(FULL_MASK, m_valid, k)) continue;
-      const int n = __shfl_sync(FULL_MASK, m_n, k);
-      const int rk = __shfl_sync(FULL_MASK, m_r, k);
-      const int p = __shfl_sync(FULL_MASK, m_p, k);
-      const int clen = __shfl_sync(FULL_MASK, m_clen, k);
-      const int obase = __shfl_sync(FULL_MASK, m_obase, k);
-      const int c0 = __shfl_sync(FULL_MASK, m_c0, k);
-      const int pr0 = __shfl_sync(FULL_MASK, m_pr0, k);
-      const float scale = __shfl_sync(FULL_MASK, m_scale, k);
-      int64_t e[kSpanRows];
-#pragma unroll
-      for (int j = 0; j < kSpanRows; ++j) e[j] = __shfl_sync(FULL_MASK, m_e[j], k);
-      int mytok = 0;
-#pragma unroll
-      for (int i = 0; i < kTileTokens; ++i) {
-        const int v = __shfl_sync(FULL_MASK, m_tok[i], k);
-        if ((lane & 7) == i) mytok = v;  // lanes 8..15 (y) and 16..23 (delta) carry token lane & 7
-      }
+    // one copy per lane: 0..15 pieces of the B chunk, 16..23 y segments, 24..31 delta rows
+    for (uint32_t left = valid_mask; left != 0 && !r.dead; left &= left - 1) {
+      const int k = __ffs(left) - 1;
+      const int* di = pp.d_i[k];
+      const int n = di[1], rk = di[2], p = di[3], clen = di[4], obase = di[5];
       const int nout = clen / rk;
       const uint32_t b_bytes = static_cast<uint32_t>(clen) * sizeof(T);
       const uint32_t y_bytes = static_cast<uint32_t>(nout) * sizeof(T);
@@ -540,113 +532,100 @@ __device__ __forceinline__ void expand_producer(const ExpandArgs& a, unsigned ch
       const uint32_t off = ring_alloc(r, c, sz, lane);
       if (r.dead) break;
       const uint32_t slot = r.g % kSlots;
+      const bool mine = static_cast<int>(r.g % kProducerWarps) == role;
       r.head = off + sz;
+      if (lane == 0) pp.off[slot] = off;
+      if (!mine) {
+        __syncwarp();
+        ring_issue(r, c, slot, 0, nullptr, 0u, false, lane);
+        continue;
+      }
+      const int mytok = lane >= 16 ? di[8 + (lane & 7)] : 0;
       if (lane == 0) {
-        c.off[slot] = off;
         c.meta[slot][0] = 0;
         c.meta[slot][1] = n;
         c.meta[slot][2] = rk;
         c.meta[slot][3] = p;
         c.meta[slot][4] = clen;
         c.meta[slot][5] = obase;
-        c.meta[slot][6] = __float_as_int(scale);
+        c.meta[slot][6] = di[6];
         c.meta[slot][7] = static_cast<int>(off);
+      } else if (lane >= 16 && lane < 24) {
+        c.meta[slot][8 + lane - 16] = mytok;
       }
-      if (lane >= 8 && lane < 8 + kTileTokens) c.meta[slot][lane] = mytok;
-      __syncwarp();
-      if (lane == 0) mbar_expect_tx(&c.full[slot], total);
-      __syncwarp();
-      // one copy per lane: 0..7 pieces of the B chunk, 8..15 y segments, 16..23 delta rows
       uint32_t dst = ring_base + off, bytes = 0;
       const T* src = w;
       bool is_act = false;
       if (lane < kMaxPieces) {
         const int poff = lane * a.piece;
         if (poff < clen) {
-          const int64_t f = static_cast<int64_t>(c0) + poff;
+          const int64_t f = static_cast<int64_t>(di[7]) + poff;
           const int64_t pr = f / S, col = f - pr * S;
-          const int d = static_cast<int>(pr) - pr0;
-          const int64_t row = d == 0 ? e[0] : (d == 1 ? e[1] : (d == 2 ? e[2] : e[3]));
-          src = w + row * S + col;
+          src = w + pp.d_l[k][static_cast<int>(pr) - di[0]] * S + col;
           dst += static_cast<uint32_t>(poff) * sizeof(T);
           bytes = static_cast<uint32_t>(min(a.piece, clen - poff)) * sizeof(T);
         }
-      } else if (lane < 8 + n) {
+      } else if (lane < 16 + n) {
         src = reinterpret_cast<const T*>(pick3(a.y, p)) + static_cast<int64_t>(mytok) * pick3(a.y_stride, p) + obase;
-        dst += b_bytes + static_cast<uint32_t>(lane - 8) * y_bytes;
+        dst += b_bytes + static_cast<uint32_t>(lane - 16) * y_bytes;
         bytes = y_bytes;
         is_act = true;
-      } else if (lane >= 16 && lane < 16 + n) {
+      } else if (lane >= 24 && lane < 24 + n) {
         src = reinterpret_cast<const T*>(pick3(a.delta, p)) + static_cast<int64_t>(mytok) * a.delta_stride;
-        dst += b_bytes + static_cast<uint32_t>(n) * y_bytes + static_cast<uint32_t>(lane - 16) * d_bytes;
+        dst += b_bytes + static_cast<uint32_t>(n) * y_bytes + static_cast<uint32_t>(lane - 24) * d_bytes;
         bytes = d_bytes;
         is_act = true;
       }
+      __syncwarp();  // the arrive below publishes every lane's part of the stage record
+      if (lane == 0) mbar_expect_tx(&c.full[slot], total);
       ring_issue(r, c, slot, dst, src, bytes, is_act, lane);
     }
+    __syncwarp();
   }
   ring_finish(r, c, a.status, lane);
 }
 
-// Butterfly over the 4 per-lane partial sums of an expand consumer warp (LPO = r / 8 lanes share one output): after
-// it lane l owns NV = max(1, 4 / LPO) complete outputs, those of loads m_base(l) + i.
-template <int HALF>
-__device__ __forceinline__ void exch4(float (&v)[4], int lane, int mask) {
-  const bool up = (lane & mask) != 0;
-#pragma unroll
-  for (int i = 0; i < HALF; ++i) {
-    const float keep = up ? v[i + HALF] : v[i];
-    const float send = up ? v[i] : v[i + HALF];
-    v[i] = keep + __shfl_xor_sync(0xffffffffu, send, mask);
-  }
-}
-
 // One consumer warp's part of an expand stage.  LPO = lanes per output = r / 8.  The warp owns flat elements
-// [cw*1024, +1024) of the chunk as 4 loads of 256 elements; load m, lane l holds the 8 values of output
-// (cw*4 + m)*(32/LPO) + l/LPO for k in [(l % LPO)*8, +8).
+// [cw*2048, +2048) of the chunk as 8 loads of 256 elements; load m, lane l holds the 8 values of output
+// (cw*8 + m)*(32/LPO) + l/LPO for k in [(l % LPO)*8, +8).
 template <typename T, int LPO>
 __device__ __forceinline__ void expand_stage(const T* bs, const int* m, T* y, int64_t y_stride, int lane, int cw) {
   constexpr int OPL = 32 / LPO;
-  constexpr int NV = LPO >= 4 ? 1 : 4 / LPO;
+  constexpr int NV = LPO >= 8 ? 1 : 8 / LPO;
   constexpr int R = LPO * 8;
-  constexpr int SPAN = kChunk / kConsumerWarps;  // 1024
+  constexpr int SPAN = kPipeChunk / kConsumerWarps;  // 2048
   const int n = m[1], clen = m[4], obase = m[5];
   if (cw * SPAN >= clen) return;
   const int nout = clen / R;
   const float scale = __int_as_float(m[6]);
   const T* ys = bs + clen;
   const T* ds = ys + n * nout;
-  uint4 bv[4];
+  uint4 bv[8];
 #pragma unroll
-  for (int mm = 0; mm < 4; ++mm) {
+  for (int mm = 0; mm < 8; ++mm) {
     const int foff = cw * SPAN + mm * 256 + lane * 8;
     bv[mm] = foff < clen ? *reinterpret_cast<const uint4*>(bs + foff) : make_uint4(0u, 0u, 0u, 0u);
   }
   const int kp = (lane & (LPO - 1)) * 8;
   const int g = lane / LPO;
-  int m_base = 0;
-  if (LPO >= 2) m_base += (lane & 1) ? 2 : 0;
-  if (LPO >= 4) m_base += (lane & 2) ? 1 : 0;
-  const bool writer = (LPO < 8 || (lane & 4) == 0) && (LPO < 16 || (lane & 8) == 0);
+  const int m_base = expand_m_base<LPO>(lane);
+  const bool writer = (LPO < 16) || ((lane & 8) == 0);
   int o_loc[NV];
 #pragma unroll
-  for (int i = 0; i < NV; ++i) o_loc[i] = (cw * 4 + m_base + i) * OPL + g;  // output index inside the chunk
+  for (int i = 0; i < NV; ++i) o_loc[i] = (cw * 8 + m_base + i) * OPL + g;  // output index inside the chunk
 
   for (int tt = 0; tt < n; ++tt) {
     const uint4 dv = *reinterpret_cast<const uint4*>(ds + tt * R + kp);
     float yv[NV];
 #pragma unroll
     for (int i = 0; i < NV; ++i) yv[i] = (writer && o_loc[i] < nout) ? to_f32<T>(ys[tt * nout + o_loc[i]]) : 0.f;
-    float v[4];
+    float v[8];
 #pragma unroll
-    for (int mm = 0; mm < 4; ++mm) {
+    for (int mm = 0; mm < 8; ++mm) {
       v[mm] = 0.f;
       dot8<T>(v[mm], bv[mm], dv);
     }
-    if (LPO >= 2) exch4<2>(v, lane, 1);
-    if (LPO >= 4) exch4<1>(v, lane, 2);
-    if (LPO >= 8) v[0] += __shfl_xor_sync(0xffffffffu, v[0], 4);
-    if (LPO >= 16) v[0] += __shfl_xor_sync(0xffffffffu, v[0], 8);
+    expand_butterfly<LPO>(v, lane);
     T* yrow = y + static_cast<int64_t>(m[8 + tt]) * y_stride + obase;
 #pragma unroll
     for (int i = 0; i < NV; ++i) {
@@ -690,10 +669,10 @@ __global__ void __launch_bounds__(kPipeThreads) lora_expand_pipe_kernel(const Ex
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   pipe_init(ctl, tid);
   pdl_launch_dependents();
-  if (warp == 0) {
-    expand_producer<T>(a, ring_mem, ctl, lane);
+  if (warp < kProducerWarps) {
+    expand_producer<T>(a, ring_mem, ctl, lane, warp);
   } else {
-    expand_consumer<T>(a, ring_mem, ctl, lane, warp - 1);
+    expand_consumer<T>(a, ring_mem, ctl, lane, warp - kProducerWarps);
   }
 }
 
