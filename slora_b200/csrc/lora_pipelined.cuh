@@ -1,10 +1,11 @@
 // Persistent, warp-specialised, mbarrier-pipelined LoRA shrink / expand kernels (the fast path).
 //
-// One CTA per SM walks its share of the work items (item i belongs to CTA i mod gridDim.x).  Warps 0 and 1 are
-// producers: the 32 lanes of each resolve 32 upcoming items in parallel (tile record -> table entries -> row
-// addresses and token ids), then feed a ring of shared-memory stages with bulk asynchronous copies (cp.async.bulk +
-// mbarrier complete_tx).  Both producers run the same deterministic allocation; stage g is issued by producer
-// g mod 2, because a single warp cannot issue bulk copies faster than ~35 GB/s.  Warps 2..9 are consumers: they wait on a stage's "full" barrier, do the arithmetic and release the
+// One CTA per SM walks its share of the work items (item i belongs to CTA i mod gridDim.x).  The first
+// kProducerWarps warps are producers: the 32 lanes of each resolve 32 upcoming items in parallel (tile record ->
+// table entries -> row addresses and token ids), then feed a ring of shared-memory stages with bulk asynchronous
+// copies (cp.async.bulk + mbarrier complete_tx).  With more than one producer all run the same deterministic
+// allocation and stage g is issued by producer g mod kProducerWarps (measured: no gain on B200 while the consumers
+// are the bottleneck, so one producer is configured).  The remaining warps are consumers: they wait on a stage's "full" barrier, do the arithmetic and release the
 // stage through its "empty" barrier.  Consumer warps never wait for each other (shrink: each warp owns a K-slice and
 // the last warp to finish an item, elected by an atomic counter, adds the partial sums; expand: each warp owns a
 // 1024-element span of the B chunk), so every wait in the kernel is an mbarrier wait with a time limit.
@@ -32,19 +33,19 @@
 namespace slora {
 
 constexpr int kSlots = 8;  // stage descriptors (barrier pairs) in flight
-constexpr int kRingBytes = 92 * 1024;  // ring + control block stay below half an SM's shared memory
+constexpr int kRingBytes = 96 * 1024;  // ring + control block stay below half an SM's shared memory
 constexpr int kPendSlots = 4;           // stages that may be issued before the grid-dependency wait
-constexpr int kProducerWarps = 2;  // stage g is fed by producer warp g % kProducerWarps
+constexpr int kProducerWarps = 1;  // stage g is fed by producer warp g % kProducerWarps
 constexpr int kConsumerWarps = 8;
 constexpr int kPipeThreads = 32 * (kProducerWarps + kConsumerWarps);
-constexpr int kMaxStageBytes = 46 * 1024;  // a shrink item is cut into K-chunks no larger than this
+constexpr int kMaxStageBytes = 48 * 1024;  // a shrink item is cut into K-chunks no larger than this
 constexpr int kPipeChunk = 16384;          // flat B elements per expand item (32 KB)
 constexpr int kMaxPieces = 16;  // B copies per expand stage (lanes 0..15); y copies use lanes 16..23, delta 24..31
 constexpr int kSpanRows = 6;    // pool rows a B chunk may touch
 
 constexpr int FLAG_FIRST = 1, FLAG_LAST = 2, FLAG_END = 4;
 constexpr uint32_t FULL_MASK = 0xffffffffu;
-constexpr long long kWaitCycles = 4000000000ll;  // about two seconds of SM clock
+constexpr long long kWaitCycles = 400000000ll;  // about 0.2 s of SM clock: far beyond any legitimate wait here
 
 // Wait for a barrier phase for a bounded time (SM cycle counter); false on timeout.
 __device__ __forceinline__ bool mbar_wait_timed(uint64_t* bar, uint32_t parity) {

@@ -1,0 +1,144 @@
+"""S-LoRA tensor parallelism for the adapter path (one process per GPU, ``torch.distributed``).
+
+The reference describes the scheme only as a figure (``figures/slora_tp.png``, ``README.md:96-100``); its code asserts
+``world_size == 1`` for adapters (``slora/models/peft/lora_adapter.py:24``) and has the LoRA all-reduce commented out
+(``slora/models/peft/lora_unordered_batch_infer.py:223-224,247-248``).  What is built here is the rule of that figure
+for a column-parallel projection, applied to q, k, v and o with replicated activations:
+
+* A is sharded over the rank dimension: GPU ``g`` owns rank rows ``[g*r/N, (g+1)*r/N)`` of every adapter (full
+  ``h_in`` each) and computes ``delta_g[T, r/N]``;
+* the small intermediates are all-gathered (one collective per call: q, k and v travel together) into
+  ``[N, nproj, T, R/N]``;
+* B is sharded over the output dimension (rows of its stored ``[h_out, r]`` layout): GPU ``g`` owns outputs
+  ``[g*h_out/N, (g+1)*h_out/N)`` and adds ``scale * delta @ B_g^T`` into its ``[T, h_out/N]`` slice of the base
+  model's column-parallel output -- for o that slice lands in the partial sum the base model all-reduces anyway.
+
+Per-rank pool layout: rows of ``pool_stride`` elements; an adapter of rank ``r`` takes ``4 * r / N`` rows per buffer
+(slot of ``r/N`` rows per projection): the A shard is ``[r/N, h_in]`` and the B shard ``[h_out/N, r]``, both row-major
+in the slot's flat space (``h_in == pool_stride``; ``h_out/N * r <= r/N * pool_stride``).  The kernels read the B shard
+with ``rank_mult = N`` and the gathered delta with ``delta_parts = N``.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import List, Sequence
+
+import torch
+
+
+def shard_adapter(A: Sequence[torch.Tensor], B: Sequence[torch.Tensor], rank: int, world: int, pool_stride: int):
+    """Rows one adapter contributes to rank ``rank``'s A pool and B pool.
+
+    ``A[p]``: ``[r, h_in]``, ``B[p]``: ``[h_out_p, r]`` for p = q, k, v, o.  Returns ``(rows_a, rows_b)``, each
+    ``[4 * r / world, pool_stride]``.
+    """
+    r = A[0].shape[0]
+    if r % world != 0:
+        raise ValueError(f"rank {r} is not divisible by the tensor-parallel size {world}")
+    rs = r // world
+    rows_a, rows_b = [], []
+    for p in range(4):
+        h_in, h_out = A[p].shape[1], B[p].shape[0]
+        if h_in != pool_stride:
+            raise ValueError("the A shard needs pool_stride == h_in")
+        if h_out % world != 0:
+            raise ValueError(f"h_out {h_out} is not divisible by the tensor-parallel size {world}")
+        rows_a.append(A[p][rank * rs:(rank + 1) * rs])
+        ho = h_out // world
+        flat = B[p][rank * ho:(rank + 1) * ho].reshape(-1)
+        if flat.numel() > rs * pool_stride:
+            raise ValueError("the B shard does not fit its slot")
+        slot = torch.zeros(rs * pool_stride, dtype=flat.dtype)
+        slot[:flat.numel()] = flat
+        rows_b.append(slot.view(rs, pool_stride))
+    return torch.cat(rows_a), torch.cat(rows_b)
+
+
+@dataclass
+class TpTables:
+    """Per-rank index tables (same meaning as InferAdapter's, with ``a_len = 4 * r / N``)."""
+    a_start: torch.Tensor
+    a_len: torch.Tensor
+    a_loc: torch.Tensor
+    a_scaling: torch.Tensor
+
+
+class TpLoraOps:
+    """Per-rank LoRA operator under S-LoRA tensor parallelism.
+
+    ``backend`` supplies the two local operations (the CUDA kernels in production, see :class:`CudaBackend`);
+    ``group`` is the ``torch.distributed`` process group of the N ranks.  ``max_rank`` is the full (unsharded) maximum
+    rank of the batch's adapters.
+    """
+
+    def __init__(self, tables: TpTables, pools_a: List[torch.Tensor], pools_b: List[torch.Tensor], max_rank: int,
+                 world: int, rank: int, backend, group=None):
+        if max_rank % world != 0:
+            raise ValueError("max_rank must be divisible by the tensor-parallel size")
+        self.t, self.pools_a, self.pools_b = tables, pools_a, pools_b
+        self.R, self.N, self.rank = max_rank, world, rank
+        self.Rl = max_rank // world
+        self.backend, self.group = backend, group
+        self.ids = None
+
+    def prepare(self, token_adapter_ids: torch.Tensor):
+        self.ids = token_adapter_ids.contiguous()
+        T = self.ids.numel()
+        dev, dt = self.ids.device, self.pools_a[0].dtype
+        self.local = torch.zeros((3, T, self.Rl), dtype=dt, device=dev)
+        self.gathered = torch.zeros((self.N, 3, T, self.Rl), dtype=dt, device=dev)
+        self.plan = self.backend.make_plan(self.ids, self.t)
+        return self
+
+    def _exchange(self, nproj):
+        """All-gather of the rank-sharded intermediates: ``[nproj, T, R/N]`` per rank -> ``[N, 3, T, R/N]``."""
+        import torch.distributed as dist
+        if nproj == 3:
+            dist.all_gather_into_tensor(self.gathered.view(-1), self.local.view(-1), group=self.group)
+        else:
+            # o uses slot 0 only: gather that slab ([T, R/N] per rank) into a contiguous staging view
+            stage = self.gathered.view(-1)[: self.N * self.local[0].numel()].view(self.N, *self.local[0].shape)
+            dist.all_gather_into_tensor(stage.view(-1), self.local[0].contiguous().view(-1), group=self.group)
+            return stage, self.local[0].numel()
+        return self.gathered, self.local.numel()
+
+    def lora_qkv(self, layer, x, q_g, k_g, v_g):
+        """``q_g/k_g/v_g``: this rank's ``[T, h_out/N]`` slices, updated in place."""
+        t = self.t
+        self.backend.shrink(self.plan, self.ids, [0, 1, 2], [self.local[0], self.local[1], self.local[2]], x,
+                            self.pools_a[layer], t)
+        gathered, part_stride = self._exchange(3)
+        T = self.ids.numel()
+        deltas = [gathered[0, p] for p in range(3)]
+        self.backend.expand(self.plan, self.ids, [0, 1, 2], [q_g, k_g, v_g], deltas, self.pools_b[layer], t,
+                            delta_stride=self.Rl, delta_width=self.Rl, delta_parts=self.N,
+                            delta_part_stride=part_stride, rank_mult=self.N)
+
+    def lora_o(self, layer, x, o_g):
+        t = self.t
+        self.backend.shrink(self.plan, self.ids, [3], [self.local[0]], x, self.pools_a[layer], t)
+        stage, part_stride = self._exchange(1)
+        self.backend.expand(self.plan, self.ids, [3], [o_g], [stage[0]], self.pools_b[layer], t,
+                            delta_stride=self.Rl, delta_width=self.Rl, delta_parts=self.N,
+                            delta_part_stride=part_stride, rank_mult=self.N)
+
+
+class CudaBackend:
+    """The local operations of :class:`TpLoraOps` on the CUDA kernels."""
+
+    def __init__(self, use_pdl=False):
+        from . import _lib
+        self.flags = _lib.FLAG_PDL if use_pdl else 0
+
+    def make_plan(self, ids, t):
+        from .batch_infer import BatchPlan
+        return BatchPlan(ids, t.a_start, t.a_len, t.a_loc.numel())
+
+    def shrink(self, plan, ids, qkvo, deltas, x, pool_a, t):
+        from .batch_infer import shrink_multi
+        shrink_multi(plan, ids, qkvo, deltas, x, pool_a, t.a_start, t.a_len, t.a_loc, self.flags)
+
+    def expand(self, plan, ids, qkvo, ys, deltas, pool_b, t, **kw):
+        from .batch_infer import expand_multi
+        expand_multi(plan, ids, qkvo, ys, deltas, pool_b, t.a_start, t.a_len, t.a_loc, t.a_scaling, flags=self.flags,
+                     **kw)

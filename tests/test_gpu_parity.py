@@ -256,3 +256,50 @@ def test_unsupported_inputs_raise():
     x_odd = torch.zeros((wl.T, 1020), dtype=wl.dtype, device=DEV)
     with pytest.raises(RuntimeError, match="No suitable kernel"):
         sl.dispatch_bgmv(d, x_odd, ka, w.a_start, w.a_len, w.a_loc, w.ids, 0, w.a_scaling)
+
+
+def test_tensor_parallel_shards_on_one_gpu():
+    """The per-rank shard layout of slora_b200.tp through the real kernels: the N ranks are run one after the other on
+    one GPU, their intermediates concatenated the way the all-gather would, and the output slices compared with the
+    single-rank formula."""
+    from slora_b200 import tp
+    H, N, T = 1024, 4, 24
+    ranks = [8, 16, 32, 8]
+    g = torch.Generator().manual_seed(21)
+    ads = [([torch.randn((r, H), generator=g) / 32 for _ in range(4)],
+            [torch.randn((H, r), generator=g) * 0.02 for _ in range(4)]) for r in ranks]
+    x = torch.randn((T, H), generator=g).to(torch.float16)
+    ids = torch.randint(0, len(ranks), (T,), generator=g)
+    R, Rl = max(ranks), max(ranks) // N
+    shards = []
+    for rank in range(N):
+        a_start, a_len, a_loc = make_tables([r // N for r in ranks], 512, 300 + rank, True)
+        pa = torch.zeros((512, H), dtype=torch.float16)
+        pb = torch.zeros((512, H), dtype=torch.float16)
+        for i, (A, B) in enumerate(ads):
+            ra, rb = tp.shard_adapter(A, B, rank, N, H)
+            loc = a_loc[a_start[i]: a_start[i] + a_len[i]]
+            pa[loc] = ra.to(torch.float16)
+            pb[loc] = rb.to(torch.float16)
+        t = tp.TpTables(a_start.to(DEV), a_len.to(DEV), a_loc.to(DEV),
+                        torch.tensor([16.0 / r for r in ranks], dtype=torch.float16, device=DEV))
+        shards.append((t, pa.to(DEV), pb.to(DEV)))
+    be = tp.CudaBackend()
+    xd, idd = x.to(DEV), ids.to(DEV)
+    for p in range(4):
+        gathered = torch.zeros((N, 1, T, Rl), dtype=torch.float16, device=DEV)
+        for rank, (t, pa, pb) in enumerate(shards):
+            plan = be.make_plan(idd, t)
+            be.shrink(plan, idd, [p], [gathered[rank, 0]], xd, pa, t)
+        slices = []
+        for rank, (t, pa, pb) in enumerate(shards):
+            y = torch.zeros((T, H // N), dtype=torch.float16, device=DEV)
+            plan = be.make_plan(idd, t)
+            be.expand(plan, idd, [p], [y], [gathered[0, 0]], pb, t, delta_stride=Rl, delta_width=Rl, delta_parts=N,
+                      delta_part_stride=T * Rl, rank_mult=N)
+            slices.append(y)
+        torch.cuda.synchronize()
+        got = torch.cat(slices, dim=1)
+        want = torch.stack([(x[i].float() @ ads[int(ids[i])][0][p].half().float().T)
+                            @ ads[int(ids[i])][1][p].half().float().T * (16.0 / ranks[int(ids[i])]) for i in range(T)])
+        assert_parity(got, want.numpy(), what=f"tp proj {p}")
