@@ -242,10 +242,32 @@ class Runner:
             self.step_eager()
 
 
-def kernel_roofline(run, peak_gbs, peak_kind, reps=3):
-    """Per-launch CUDA-event timing of the q/k/v expand launch (the largest kernel of the step) and of the q/k/v
-    shrink launch, issued one at a time (no overlap with neighbours) over all layers."""
-    from slora_b200 import batch_infer
+def _graph_time(fn, launches, iters=5):
+    """Microseconds per launch of `fn`'s launches, replayed from a CUDA graph (no host time between kernels)."""
+    s = torch.cuda.Stream()
+    s.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(s):
+        fn()
+    torch.cuda.current_stream().wait_stream(s)
+    torch.cuda.synchronize()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g, stream=s):
+        fn()
+    g.replay()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(iters):
+        g.replay()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) * 1e3 / iters / launches
+
+
+def kernel_roofline(run, peak_gbs, peak_kind):
+    """Average duration of the q/k/v expand launch (the largest kernel of the step) and of the q/k/v shrink launch:
+    a CUDA graph holding one launch per layer of that kernel alone, CUDA-event timed."""
+    from slora_b200 import batch_infer, _lib
     wl, ops = run.wl, run.ops
     dims = wl.proj_dims()
     distinct = torch.unique(wl.ids).tolist()
@@ -254,29 +276,30 @@ def kernel_roofline(run, peak_gbs, peak_kind, reps=3):
     y_bytes = wl.T * sum(2 * dims[p][1] * es for p in range(3))
     a_bytes = sum(wl.ranks[a] * dims[p][0] * es for a in distinct for p in range(3))
     x_bytes = wl.T * dims[0][0] * es
-    ev = [[torch.cuda.Event(enable_timing=True) for _ in range(3)] for _ in range(run.L * reps)]
-    i = 0
-    for _ in range(reps):
+    flags = 0 if run.args.no_pdl else _lib.FLAG_PDL
+
+    def shrinks():
         for l in range(run.L):
             p = l % run.P
-            ev[i][0].record()
             batch_infer.shrink_multi(ops.plan, wl.ids, [0, 1, 2], ops.delta, wl.x_qkv[p], wl.pools_a[p], wl.a_start,
-                                     wl.a_len, wl.a_loc)
-            ev[i][1].record()
+                                     wl.a_len, wl.a_loc, flags)
+
+    def expands():
+        for l in range(run.L):
+            p = l % run.P
             batch_infer.expand_multi(ops.plan, wl.ids, [0, 1, 2], [run.q[p], run.k[p], run.v[p]], ops.delta,
                                      wl.pools_b[p], wl.a_start, wl.a_len, wl.a_loc, wl.a_scaling,
-                                     ops.delta[0].stride(0), wl.max_rank)
-            ev[i][2].record()
-            i += 1
-    torch.cuda.synchronize()
-    t_shrink = statistics.mean(e[0].elapsed_time(e[1]) for e in ev) * 1e-3
-    t_expand = statistics.mean(e[1].elapsed_time(e[2]) for e in ev) * 1e-3
+                                     ops.delta[0].stride(0), wl.max_rank, flags=flags)
+
+    t_shrink = _graph_time(shrinks, run.L) * 1e-6
+    t_expand = _graph_time(expands, run.L) * 1e-6
     out = {}
-    for name, t, nbytes in (("lora_expand_kernel(qkv)", t_expand, b_bytes + y_bytes),
-                            ("lora_shrink_kernel(qkv)", t_shrink, a_bytes + x_bytes)):
+    for name, t, nbytes in (("lora_pipe_kernel<expand>(qkv)", t_expand, b_bytes + y_bytes),
+                            ("lora_pipe_kernel<shrink>(qkv)", t_shrink, a_bytes + x_bytes)):
         out[name] = {"bound": "hbm", "achieved": nbytes / t / 1e9, "peak": peak_gbs, "unit": "GB/s",
                      "frac": nbytes / t / 1e9 / peak_gbs, "traffic": None, "kernel": name,
-                     "us_per_launch": t * 1e6, "algorithmic_bytes_per_launch": nbytes, "peak_kind": peak_kind}
+                     "us_per_launch": t * 1e6, "algorithmic_bytes_per_launch": nbytes, "peak_kind": peak_kind,
+                     "how": "CUDA graph of one launch per layer of this kernel alone, CUDA events around the replay"}
     return out
 
 
@@ -394,7 +417,7 @@ def main():
         cpu, _ = run_cpu_baseline(args.config, min(wl.spec.pool_rows, 65536 if args.config != 4 else 327680),
                                   args.cpu_seconds)
     if rank == 0:
-        main_roof = roof["lora_expand_kernel(qkv)"]
+        main_roof = roof["lora_pipe_kernel<expand>(qkv)"]
         line = {
             "metric": "lora_delta_tokens_per_s", "value": value, "unit": "tokens/s", "n_gpus": world,
             "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True,
@@ -407,7 +430,7 @@ def main():
                              "reuse between layers" % (bytes_layer * min(run.P, run.L) // 2 ** 20),
                        "graph": not args.no_graph, "pdl": not args.no_pdl, "plan": not args.no_plan},
             "roofline": main_roof,
-            "roofline_shrink": roof["lora_shrink_kernel(qkv)"],
+            "roofline_shrink": roof["lora_pipe_kernel<shrink>(qkv)"],
             "step_hbm": {"algorithmic_bytes_per_step": bytes_layer * run.L, "achieved": step_gbs, "peak": peak_gbs,
                          "frac": step_gbs / peak_gbs, "unit": "GB/s", "peak_kind": peak_kind,
                          "frac_of_nominal_8TBs": step_gbs / 8000.0},

@@ -177,11 +177,12 @@ def fill_pool_rows(pool, loc, std, gen, chunk=8192):
 
 def build_workload(cfg: int, device="cpu", dtype=torch.float16, phys_layers=1, pool_rows=None, n_adapters=None,
                    decode_tokens=None, hidden=None, h_kv=None, permute=True, rank_choices=None, prefill="default",
-                   with_activations=True) -> Workload:
+                   with_activations=True, rank_div=1) -> Workload:
     """Build configuration ``cfg`` (1..5), optionally shrunk (fewer adapters / rows / tokens) for tests.
 
     Tables and batch composition are always drawn on CPU; pool contents and activations are drawn on ``device``
     (seeded per device type, so CPU-built and CUDA-built workloads differ in values but not in structure).
+    ``rank_div`` > 1 gives the tables and (random) pool contents of one rank of an N-way tensor-parallel group.
     """
     base = SPECS[cfg]
     spec = WorkloadSpec(base.name, hidden or base.hidden, h_kv or (hidden if hidden and base.h_kv == base.hidden
@@ -194,7 +195,8 @@ def build_workload(cfg: int, device="cpu", dtype=torch.float16, phys_layers=1, p
     g_b = torch.Generator().manual_seed(3000 + cfg)
     choice = torch.randint(0, len(spec.rank_choices), (spec.n_adapters,), generator=g_w).tolist()
     ranks = [spec.rank_choices[c] for c in choice]
-    a_start, a_len, a_loc = make_tables(ranks, spec.pool_rows, 2000 + cfg, permute)
+    # rank_div = N builds one tensor-parallel rank's tables: slots of r / N rows (Workload.ranks keeps the full r)
+    a_start, a_len, a_loc = make_tables([r // rank_div for r in ranks], spec.pool_rows, 2000 + cfg, permute)
     a_scaling = torch.tensor([ALPHA / r for r in ranks], dtype=dtype)
     ids, segments = build_batch(spec, g_b)
     wl = Workload(spec, dtype, ranks, a_start, a_len, a_loc, a_scaling, ids, segments)
