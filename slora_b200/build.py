@@ -1,4 +1,7 @@
-"""Build ``libslora_b200.so`` in-tree with nvcc for sm_100a:  ``python -m slora_b200.build [--force] [-v]``."""
+"""Build ``libslora_b200.so`` in-tree with nvcc for sm_100a:  ``python slora_b200/build.py [--force] [-v]``.
+
+Run as a script (or load this file by path): importing the package needs the library to exist already.
+"""
 from __future__ import annotations
 
 import os

@@ -15,7 +15,10 @@ def pytest_configure(config):
 @pytest.fixture(scope="session", autouse=True)
 def _built_library():
     """The tests exercise the in-tree shared library; build it if the tree has none yet."""
-    from slora_b200 import build as b
+    import importlib.util
+    spec = importlib.util.spec_from_file_location("slora_b200_build", os.path.join(ROOT, "slora_b200", "build.py"))
+    b = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(b)
     if b.needs_build():
         b.build()
     yield
