@@ -22,7 +22,7 @@ STATUS_BITS = {1: "bad adapter id", 2: "bad table entry", 4: "unsupported rank",
 def _load():
     if not os.path.exists(LIB_PATH):
         raise ImportError(
-            f"{LIB_PATH} is missing: build it with `python -m slora_b200.build` (needs nvcc, sm_100a). "
+            f"{LIB_PATH} is missing: build it with `python slora_b200/build.py` (needs nvcc, sm_100a). "
             "slora_b200 has no CPU or PyTorch fallback.")
     return ctypes.CDLL(LIB_PATH)
 
@@ -60,6 +60,8 @@ _SIGS = {
                                      c_int, c_int64, c_int, c_uint, _P]),
     "slora_batch_lora_o": (c_int, [_P, _P, _P, c_int64, c_int, _P, c_int64, c_int, _P, _P, c_int64, c_int64, _P, _P,
                                    _P, _P, c_int64, c_int64, _P, c_int64, c_int, c_int64, c_int, c_uint, _P]),
+    "slora_batch_lora_o_noalloc": (c_int, [_P, _P, c_int64, c_int, _P, c_int64, c_int, _P, _P, c_int64, c_int64, _P, _P,
+                                           _P, _P, c_int64, c_int64, c_int, c_int64, c_int, c_uint, _P]),
     "slora_validate_tables": (c_int, [_P, _P, _P, _P, c_int64, c_int64, c_int64, c_int64, _P, _P]),
 }
 

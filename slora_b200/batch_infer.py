@@ -159,3 +159,20 @@ def expand_multi(plan, ids, qkvo, ys, deltas, pool_b, a_start, a_len, a_loc, a_s
         delta_width, delta_parts, delta_part_stride, rank_mult, pool_b.data_ptr(), pool_b.size(0), pool_b.stride(0),
         a_start.data_ptr(), a_len.data_ptr(), a_loc.data_ptr(), a_scaling.data_ptr(), a_start.numel(),
         a_loc.numel(), T, _lib.dtype_code(ys[0].dtype), flags, _lib.current_stream_ptr()))
+
+
+def lora_o_noalloc(ids, x, o, pool_a, pool_b, a_start, a_len, a_loc, a_scaling, max_rank, flags=0):
+    """``o += lora_o(x)`` through the entry point that allocates nothing (C entry ``slora_batch_lora_o_noalloc``).
+
+    For callers that may not allocate device memory (a serving process whose own pool holds the whole GPU, a path
+    where ``cudaMalloc`` is forbidden): the plan and the intermediate live in 320 KB built into the library, so this
+    wrapper creates no tensor either.  Limits: 1024 tokens, 4096 adapters, rank up to 128.  Calls on one stream may
+    follow each other; calls that could overlap on the GPU would race on the shared scratch.
+    """
+    _lib.require_cuda(ids, x, o, pool_a, pool_b, a_start, a_len, a_loc, a_scaling)
+    _lib.check(_lib.lib.slora_batch_lora_o_noalloc(
+        ids.data_ptr(), o.data_ptr(), o.stride(0), o.size(1), x.data_ptr(), x.stride(0), x.size(1), pool_a.data_ptr(),
+        pool_b.data_ptr(), pool_a.size(0), pool_a.stride(0), a_start.data_ptr(), a_len.data_ptr(), a_loc.data_ptr(),
+        a_scaling.data_ptr(), a_start.numel(), a_loc.numel(), int(max_rank), x.size(0), _lib.dtype_code(x.dtype), flags,
+        _lib.current_stream_ptr()))
+    return o

@@ -591,6 +591,67 @@ int slora_batch_lora_o(const void* plan, const int64_t* ids, void* o, int64_t o_
                                  flags, stream);
 }
 
+// ---- entry point that allocates nothing ------------------------------------------------------------------------
+// Scratch of slora_batch_lora_o_noalloc: the batch plan (first kNoAllocPlanBytes) and the rank-r intermediate of up to
+// kNoAllocMaxTokens tokens x 128 columns.  One copy per GPU that loads the library, held until the process exits and
+// shared by every call on that GPU.
+constexpr int64_t kNoAllocMaxTokens = 1024;
+constexpr int64_t kNoAllocMaxAdapters = 4096;
+constexpr size_t kNoAllocPlanBytes = 64 * 1024;
+constexpr size_t kNoAllocDeltaBytes = static_cast<size_t>(kNoAllocMaxTokens) * 128 * 2;
+static __device__ __align__(256) unsigned char g_noalloc_scratch[kNoAllocPlanBytes + kNoAllocDeltaBytes];
+
+// Device address of the scratch array on the current device.  In host code the array's name is only a handle; the
+// address a kernel can use comes from cudaGetSymbolAddress, asked once per device with that device current.
+static int noalloc_scratch(unsigned char** out) {
+  static unsigned char* addr[64];
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess || dev < 0 || dev >= 64) {
+    cudaGetLastError();
+    return fail(SLORA_ERR_LAUNCH, "cudaGetDevice: %s", e == cudaSuccess ? "device index out of range" : cudaGetErrorString(e));
+  }
+  if (addr[dev] == nullptr) {
+    void* p = nullptr;
+    e = cudaGetSymbolAddress(&p, g_noalloc_scratch);
+    if (e != cudaSuccess || p == nullptr) {
+      cudaGetLastError();
+      return fail(SLORA_ERR_LAUNCH, "cudaGetSymbolAddress(scratch): %s", cudaGetErrorString(e));
+    }
+    addr[dev] = static_cast<unsigned char*>(p);
+  }
+  *out = addr[dev];
+  return SLORA_OK;
+}
+
+int slora_batch_lora_o_noalloc(const int64_t* ids, void* o, int64_t o_stride, int h_out, const void* x,
+                               int64_t x_stride, int h_in, const void* pool_a, const void* pool_b, int64_t pool_rows,
+                               int64_t pool_stride, const int64_t* start, const int64_t* ranks4, const int64_t* loc,
+                               const void* scales, int64_t n_adapters, int64_t loc_len, int max_rank, int64_t T,
+                               int dtype, unsigned flags, void* stream) {
+  if (T < 0 || T > kNoAllocMaxTokens)
+    return fail(SLORA_ERR_WORKSPACE, "slora_batch_lora_o_noalloc: T=%lld exceeds the built-in scratch (max %lld tokens)",
+                (long long)T, (long long)kNoAllocMaxTokens);
+  if (n_adapters < 0 || n_adapters > kNoAllocMaxAdapters)
+    return fail(SLORA_ERR_WORKSPACE, "slora_batch_lora_o_noalloc: n_adapters=%lld exceeds the built-in scratch (max %lld)",
+                (long long)n_adapters, (long long)kNoAllocMaxAdapters);
+  if (max_rank <= 0 || max_rank > 128 || max_rank % 8 != 0)
+    return fail(SLORA_ERR_RANK, "slora_batch_lora_o_noalloc: max_rank=%d must be a multiple of 8 up to 128", max_rank);
+  if (slora_plan_workspace_bytes(T, n_adapters) > kNoAllocPlanBytes)
+    return fail(SLORA_ERR_WORKSPACE, "slora_batch_lora_o_noalloc: plan of %zu bytes exceeds the built-in %zu",
+                slora_plan_workspace_bytes(T, n_adapters), kNoAllocPlanBytes);
+  unsigned char* scratch = nullptr;
+  int rc = noalloc_scratch(&scratch);
+  if (rc) return rc;
+  if (T == 0) return SLORA_OK;
+  // the plan kernel clears its own counters; the intermediate needs no clearing (only columns < r are written and read)
+  rc = slora_plan_build(scratch, kNoAllocPlanBytes, ids, T, start, ranks4, n_adapters, loc_len, stream);
+  if (rc) return rc;
+  return slora_batch_lora_o(scratch, ids, o, o_stride, h_out, x, x_stride, h_in, pool_a, pool_b, pool_rows, pool_stride,
+                            start, ranks4, loc, scales, n_adapters, loc_len, scratch + kNoAllocPlanBytes, max_rank,
+                            max_rank, T, dtype, flags, stream);
+}
+
 int slora_validate_tables(const int64_t* start, const int64_t* ranks4, const int64_t* loc, const int64_t* ids,
                           int64_t n_adapters, int64_t loc_len, int64_t T, int64_t pool_rows, int32_t* report,
                           void* stream) {
