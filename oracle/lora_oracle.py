@@ -25,7 +25,7 @@ What it restates (all paths are inside the S-LoRA reference tree):
 Parity pin: the reference stores no golden values for this path (its kernel scripts draw CUDA random numbers
 and only print a max delta).  The oracle is therefore pinned (1) by formula against the HF-layout identity above
 and (2) by outputs of the reference's own CUDA kernels compiled from the reference tree by ``oracle/Makefile``
-and run once on a B200 (fixtures under ``tests/golden/`` with the script that made them).
+and run on a B200 (``tests/golden/ref_kernels.npz``, made by ``tests/golden/make_ref_golden.py``).
 
 Arithmetic: inputs are taken as given (fp16/bf16 values upcast), everything is accumulated in float32 with no
 intermediate rounding; :func:`lora_delta_ref_rounding` additionally mimics the reference kernels' fp16 rounding of

@@ -303,3 +303,21 @@ def test_tensor_parallel_shards_on_one_gpu():
         want = torch.stack([(x[i].float() @ ads[int(ids[i])][0][p].half().float().T)
                             @ ads[int(ids[i])][1][p].half().float().T * (16.0 / ranks[int(ids[i])]) for i in range(T)])
         assert_parity(got, want.numpy(), what=f"tp proj {p}")
+
+
+@pytest.mark.parametrize("case", ["cfg1", "mixed"])
+def test_against_outputs_of_the_reference_kernels(case):
+    """This library against tests/golden/ref_kernels.npz (outputs of the reference's own CUDA kernels on a B200)."""
+    import importlib.util, os
+    from tests.helpers import ROOT
+    gdir = os.path.join(ROOT, "tests", "golden")
+    spec = importlib.util.spec_from_file_location("make_ref_golden", os.path.join(gdir, "make_ref_golden.py"))
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    g = np.load(os.path.join(gdir, "ref_kernels.npz"))
+    wl = build_workload(**mod.CASES[case])
+    outs, deltas = _dispatch_layer(wl.to(DEV))
+    for p in range(4):
+        ref_d = torch.from_numpy(g[f"{case}_delta_p{p}"].astype(np.float32))
+        assert (deltas[p].float().cpu() - ref_d).abs().max() <= 2e-3 * ref_d.abs().max()
+        assert_parity(outs[p][:, mod.COLS], g[f"{case}_y_p{p}"].astype(np.float32), what=f"ref kernels {case} p{p}")
