@@ -334,6 +334,33 @@ __device__ __forceinline__ void shrink_warp_reduce(const float (&acc)[kMaxRows][
   if ((lane & ((1 << SH) - 1)) == 0) red_row[lane >> SH] = tot;
 }
 
+// Multiply-accumulate part of a shrink stage for a tile of at most NT tokens, free of data-dependent branches (each
+// branch costs the lone warp of a scheduler ~10-20 cycles of resolve latency): rows and tokens beyond the real counts
+// are clamped to the last real one, so their accumulators hold duplicates that are never written out.
+template <typename T, int NT>
+__device__ __forceinline__ void shrink_accumulate(float (&acc)[kMaxRows][kTileTokens], const T* st, int nrows, int n,
+                                                  int klen, int cw, int lane) {
+  const T* xs = st + nrows * klen;
+  const T* wrow[kMaxRows];
+#pragma unroll
+  for (int j = 0; j < kMaxRows; ++j) wrow[j] = st + min(j, nrows - 1) * klen;
+  const T* xrow[NT];
+#pragma unroll
+  for (int i = 0; i < NT; ++i) xrow[i] = xs + min(i, n - 1) * klen;
+#pragma unroll 1
+  for (int k = cw * 256 + lane * 8; k < klen; k += kConsumerWarps * 256) {
+    uint4 wv[kMaxRows];
+#pragma unroll
+    for (int j = 0; j < kMaxRows; ++j) wv[j] = *reinterpret_cast<const uint4*>(wrow[j] + k);
+#pragma unroll
+    for (int i = 0; i < NT; ++i) {
+      const uint4 xv = *reinterpret_cast<const uint4*>(xrow[i] + k);
+#pragma unroll
+      for (int j = 0; j < kMaxRows; ++j) dot8<T>(acc[j][i], wv[j], xv);
+    }
+  }
+}
+
 // Consumer warp cw owns the K-slice [cw*256, +256) of every chunk: one 16-byte vector per lane per row / token, so a
 // stage is straight-line code with 4 * n independent FMA chains.  At the item's last chunk the warps' partial sums
 // meet in shared memory; the warp that arrives last (an atomic counter, no waiting) adds them in a fixed order and
@@ -368,21 +395,14 @@ __device__ __forceinline__ void shrink_consumer(const ShrinkArgs& a, const unsig
       }
     }
     const T* st = reinterpret_cast<const T*>(ring_mem + m[6]);
-    const T* xs = st + nrows * klen;
-    for (int k = cw * 256 + lane * 8; k < klen; k += kConsumerWarps * 256) {
-      uint4 wv[kMaxRows];
-#pragma unroll
-      for (int j = 0; j < kMaxRows; ++j) {
-        wv[j] = j < nrows ? *reinterpret_cast<const uint4*>(st + j * klen + k) : make_uint4(0u, 0u, 0u, 0u);
-      }
-#pragma unroll
-      for (int i = 0; i < kTileTokens; ++i) {
-        if (i < n) {
-          const uint4 xv = *reinterpret_cast<const uint4*>(xs + i * klen + k);
-#pragma unroll
-          for (int j = 0; j < kMaxRows; ++j) dot8<T>(acc[j][i], wv[j], xv);
-        }
-      }
+    if (n <= 1) {
+      shrink_accumulate<T, 1>(acc, st, nrows, n, klen, cw, lane);
+    } else if (n <= 2) {
+      shrink_accumulate<T, 2>(acc, st, nrows, n, klen, cw, lane);
+    } else if (n <= 4) {
+      shrink_accumulate<T, 4>(acc, st, nrows, n, klen, cw, lane);
+    } else {
+      shrink_accumulate<T, 8>(acc, st, nrows, n, klen, cw, lane);
     }
     if (flags & FLAG_LAST) {
       const uint32_t buf = item_seq % kSlots;
@@ -589,7 +609,7 @@ __device__ __forceinline__ void expand_producer(const ExpandArgs& a, unsigned ch
 // One consumer warp's part of an expand stage.  LPO = lanes per output = r / 8.  The warp owns flat elements
 // [cw*2048, +2048) of the chunk as 8 loads of 256 elements; load m, lane l holds the 8 values of output
 // (cw*8 + m)*(32/LPO) + l/LPO for k in [(l % LPO)*8, +8).
-template <typename T, int LPO>
+template <typename T, int LPO, bool FULL>
 __device__ __forceinline__ void expand_stage(const T* bs, const int* m, T* y, int64_t y_stride, int lane, int cw) {
   constexpr int OPL = 32 / LPO;
   constexpr int NV = LPO >= 8 ? 1 : 8 / LPO;
@@ -605,7 +625,7 @@ __device__ __forceinline__ void expand_stage(const T* bs, const int* m, T* y, in
 #pragma unroll
   for (int mm = 0; mm < 8; ++mm) {
     const int foff = cw * SPAN + mm * 256 + lane * 8;
-    bv[mm] = foff < clen ? *reinterpret_cast<const uint4*>(bs + foff) : make_uint4(0u, 0u, 0u, 0u);
+    bv[mm] = (FULL || foff < clen) ? *reinterpret_cast<const uint4*>(bs + foff) : make_uint4(0u, 0u, 0u, 0u);
   }
   const int kp = (lane & (LPO - 1)) * 8;
   const int g = lane / LPO;
@@ -619,7 +639,9 @@ __device__ __forceinline__ void expand_stage(const T* bs, const int* m, T* y, in
     const uint4 dv = *reinterpret_cast<const uint4*>(ds + tt * R + kp);
     float yv[NV];
 #pragma unroll
-    for (int i = 0; i < NV; ++i) yv[i] = (writer && o_loc[i] < nout) ? to_f32<T>(ys[tt * nout + o_loc[i]]) : 0.f;
+    for (int i = 0; i < NV; ++i) {
+      yv[i] = (FULL || (writer && o_loc[i] < nout)) ? to_f32<T>(ys[tt * nout + o_loc[i]]) : 0.f;
+    }
     float v[8];
 #pragma unroll
     for (int mm = 0; mm < 8; ++mm) {
@@ -630,7 +652,7 @@ __device__ __forceinline__ void expand_stage(const T* bs, const int* m, T* y, in
     T* yrow = y + static_cast<int64_t>(m[8 + tt]) * y_stride + obase;
 #pragma unroll
     for (int i = 0; i < NV; ++i) {
-      if (writer && o_loc[i] < nout) yrow[o_loc[i]] = from_f32<T>(fmaf(scale, v[i], yv[i]));
+      if (writer && (FULL || o_loc[i] < nout)) yrow[o_loc[i]] = from_f32<T>(fmaf(scale, v[i], yv[i]));
     }
   }
 }
@@ -651,12 +673,22 @@ __device__ __forceinline__ void expand_consumer(const ExpandArgs& a, const unsig
     const int p = m[3];
     T* y = reinterpret_cast<T*>(pick3(a.y, p));
     const int64_t ystr = pick3(a.y_stride, p);
-    switch (m[2]) {
-      case 8: expand_stage<T, 1>(bs, m, y, ystr, lane, cw); break;
-      case 16: expand_stage<T, 2>(bs, m, y, ystr, lane, cw); break;
-      case 32: expand_stage<T, 4>(bs, m, y, ystr, lane, cw); break;
-      case 64: expand_stage<T, 8>(bs, m, y, ystr, lane, cw); break;
-      default: expand_stage<T, 16>(bs, m, y, ystr, lane, cw); break;
+    if (m[4] == kPipeChunk) {  // complete chunk: no bounds checks
+      switch (m[2]) {
+        case 8: expand_stage<T, 1, true>(bs, m, y, ystr, lane, cw); break;
+        case 16: expand_stage<T, 2, true>(bs, m, y, ystr, lane, cw); break;
+        case 32: expand_stage<T, 4, true>(bs, m, y, ystr, lane, cw); break;
+        case 64: expand_stage<T, 8, true>(bs, m, y, ystr, lane, cw); break;
+        default: expand_stage<T, 16, true>(bs, m, y, ystr, lane, cw); break;
+      }
+    } else {
+      switch (m[2]) {
+        case 8: expand_stage<T, 1, false>(bs, m, y, ystr, lane, cw); break;
+        case 16: expand_stage<T, 2, false>(bs, m, y, ystr, lane, cw); break;
+        case 32: expand_stage<T, 4, false>(bs, m, y, ystr, lane, cw); break;
+        case 64: expand_stage<T, 8, false>(bs, m, y, ystr, lane, cw); break;
+        default: expand_stage<T, 16, false>(bs, m, y, ystr, lane, cw); break;
+      }
     }
     __syncwarp();
     if (lane == 0) mbar_arrive(&c.empty[slot]);
