@@ -94,6 +94,13 @@ int slora_bgmv_expand(void* y, const void* delta, const void* w, const int64_t* 
  * (slora/models/peft/triton_kernel/lora/lora_prefill.py:139-164 and :105-136).  seg_start/seg_len are int32
  * (the reference's b_start_loc / b_seq_len), seg_adapter int64 (req_bins).  max_seg_len bounds the grid exactly as
  * the reference's max_input_len does.
+ *
+ * Segments of 32 tokens or more whose adapter has 8..128 slot rows (a multiple of 8) are computed on the tensor
+ * cores (tcgen05, FP32 accumulation in tensor memory) in tiles of 128 tokens, when the layout allows: for the
+ * shrink pool_stride == h_in and h_in % 64 == 0; for the expand 16-byte aligned y and delta rows.  Everything else
+ * of the same call runs on the CUDA-core kernels; the two launches write disjoint tokens.  Results of the two
+ * paths differ in summation order only (same tolerance against the FP32 oracle).  SLORA_MMA=0 in the environment
+ * keeps every segment on the CUDA-core kernels.
  */
 int slora_sgmv_shrink(void* delta, const void* x, const void* w, const int64_t* start, const int64_t* ranks4,
                       const int64_t* loc, const int32_t* seg_start, const int32_t* seg_len,
@@ -194,6 +201,13 @@ int slora_batch_lora_o_noalloc(const int64_t* ids, void* o, int64_t o_stride, in
 int slora_validate_tables(const int64_t* start, const int64_t* ranks4, const int64_t* loc, const int64_t* ids,
                           int64_t n_adapters, int64_t loc_len, int64_t T, int64_t pool_rows, int32_t* report,
                           void* stream);
+
+/* Kernels this process has launched through the library so far, per family:
+ * out[0] simple (one CTA per work item), out[1] pipelined (persistent, warp-specialised), out[2] tensor core
+ * (tcgen05, long segments), out[3] plan building and table validation.  The counters only ever grow; a caller
+ * that wants the launches of a region subtracts two readings.  (Accounting aid: the reference has no counterpart;
+ * its kernel launches are counted by the profiler.) */
+void slora_launch_counts(int64_t out[4]);
 
 #ifdef __cplusplus
 }

@@ -13,7 +13,7 @@ Public surface (each item names the reference symbol it stands in for):
 * ``InferAdapter``                                -- ``slora.server.router.model_infer.infer_adapter.InferAdapter``
 * ``tp``                                          -- S-LoRA tensor parallelism for the adapter path
 """
-from ._lib import EXPORTS, LIB_PATH, lib  # noqa: F401  (fails loudly when the library is not built)
+from ._lib import EXPORTS, LIB_PATH, launch_counts, lib  # noqa: F401  (fails loudly when the library is not built)
 from ._kernels import dispatch_bgmv, validate_tables  # noqa: F401
 from .lora_prefill import lora_get_qkvo_fwd_expand, lora_get_qkvo_fwd_shrink  # noqa: F401
 from .batch_infer import BatchPlan, LoraBatchOps  # noqa: F401

@@ -63,6 +63,7 @@ _SIGS = {
     "slora_batch_lora_o_noalloc": (c_int, [_P, _P, c_int64, c_int, _P, c_int64, c_int, _P, _P, c_int64, c_int64, _P, _P,
                                            _P, _P, c_int64, c_int64, c_int, c_int64, c_int, c_uint, _P]),
     "slora_validate_tables": (c_int, [_P, _P, _P, _P, c_int64, c_int64, c_int64, c_int64, _P, _P]),
+    "slora_launch_counts": (None, [_P]),
 }
 
 EXPORTS = tuple(_SIGS)
@@ -71,6 +72,14 @@ for _name, (_res, _args) in _SIGS.items():
     _fn = getattr(lib, _name)  # AttributeError here means the header and the library disagree
     _fn.restype = _res
     _fn.argtypes = _args
+
+
+def launch_counts():
+    """Kernels launched by the library so far: ``{"simple", "pipelined", "tensor_core", "plan"}`` (growing counters)."""
+    import ctypes
+    buf = (ctypes.c_int64 * 4)()
+    lib.slora_launch_counts(buf)
+    return dict(zip(("simple", "pipelined", "tensor_core", "plan"), (int(v) for v in buf)))
 
 
 def last_error() -> str:

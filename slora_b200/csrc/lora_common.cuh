@@ -36,6 +36,8 @@ struct TileSrc {
   int n_seg;
   int tiles_per_seg;
   int slots;  // tile slots the launch enumerates (upper bound of the number of tiles)
+  int seg_split;          // SEGMENT: > 0 when segments at least this long go to the tensor-core kernels
+  int mma_tiles_per_seg;  // SEGMENT: 128-token tiles enumerated per segment by the tensor-core kernels
   int64_t T;
 };
 
@@ -75,6 +77,7 @@ struct ShrinkArgs {
   int rows_per_cta;  // <= kMaxRows
   int tok_pass;      // simple kernel: tokens staged per pass
   int piece;         // simple kernel: elements per bulk copy
+  int mma_stage_bytes;  // tensor-core kernel: bytes of one pipeline stage
   int32_t* status;
 };
 
@@ -284,6 +287,10 @@ __device__ __forceinline__ bool lookup_tile(const TileSrc& s, const Tables& tb, 
   t.adapter = static_cast<int>(adapter);
   t.r = static_cast<int>(r4 >> 2);
   t.loc_base = st;
+  // long segments of an adapter the tensor-core kernels can serve are theirs (same predicate as mma_serves)
+  if (s.mode == MODE_SEGMENT && s.seg_split > 0 && s.seg_len[tile_idx / s.tiles_per_seg] >= s.seg_split &&
+      t.r >= 8 && t.r <= 128 && t.r % 8 == 0 && tb.pool_stride % t.r == 0)
+    return false;
   return t.r > 0;
 }
 

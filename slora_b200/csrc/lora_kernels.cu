@@ -8,6 +8,7 @@
 // Kernels: lora_plan.cuh groups a batch's tokens by adapter; lora_pipelined.cuh holds the persistent
 // warp-specialised kernels used whenever the layout allows; lora_simple.cuh holds the one-CTA-per-item kernels that
 // serve every other layout.  SLORA_KERNELS=simple|pipelined in the environment forces a choice (for A/B timing).
+#include <atomic>
 #include <cstdarg>
 #include <cstdio>
 #include <cstdlib>
@@ -15,6 +16,7 @@
 
 #include "lora_common.cuh"
 #include "lora_pipelined.cuh"
+#include "lora_mma.cuh"
 #include "lora_plan.cuh"
 #include "lora_simple.cuh"
 
@@ -72,9 +74,13 @@ int pow2_divisor(int64_t v, int cap) {
   return p;
 }
 
-int check_launch(const char* what) {
+// Kernels launched so far by this process, per family: 0 simple, 1 pipelined, 2 tensor core, 3 plan / tables.
+std::atomic<long long> g_launches[4];
+
+int check_launch(const char* what, int kernels) {
   const cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return fail(SLORA_ERR_LAUNCH, "%s: %s", what, cudaGetErrorString(e));
+  g_launches[3].fetch_add(kernels, std::memory_order_relaxed);
   return SLORA_OK;
 }
 
@@ -119,6 +125,15 @@ KernelChoice kernel_choice() {
   return choice;
 }
 
+// The tensor-core kernels for long segments can be switched off with SLORA_MMA=0.
+bool mma_enabled() {
+  static const bool on = [] {
+    const char* e = getenv("SLORA_MMA");
+    return !(e && strcmp(e, "0") == 0);
+  }();
+  return on && kernel_choice() != CHOOSE_SIMPLE;
+}
+
 int sm_count() {
   static int count[64];
   int dev = 0;
@@ -133,6 +148,12 @@ int sm_count() {
     count[dev] = n;
   }
   return count[dev];
+}
+
+int family_of(const char* what) {
+  if (strstr(what, "tensor core")) return 2;
+  if (strstr(what, "pipelined")) return 1;
+  return 0;
 }
 
 template <typename K, typename A>
@@ -160,13 +181,14 @@ int launch(K kernel, int64_t grid, int threads, size_t smem, unsigned flags, cud
     cudaGetLastError();
     return fail(SLORA_ERR_LAUNCH, "%s: %s", what, cudaGetErrorString(e));
   }
+  g_launches[family_of(what)].fetch_add(1, std::memory_order_relaxed);
   return SLORA_OK;
 }
 
 // Opt in to more than 48 KB of dynamic shared memory, once per (kernel, device) and size high-water mark.
 template <typename K>
 int ensure_dyn_smem(K kernel, int which, size_t smem) {
-  static int high_water[4][64];
+  static int high_water[8][64];
   if (smem <= 48 * 1024) return SLORA_OK;
   int dev = 0;
   cudaGetDevice(&dev);
@@ -220,6 +242,33 @@ int run_shrink(const TileSrc& src, const Tables& tb, const void* w, const void* 
   a.delta_stride = delta_stride;
   a.delta_width = delta_width;
   a.status = status;
+  // long segments first go to the tensor-core kernel; the launch below then skips them
+  a.src.seg_split = 0;
+  if (src.mode == MODE_SEGMENT && src.seg_split > 0 && mma_enabled() && S == h_in && h_in % kMmaKBlock == 0) {
+    bool consecutive = true;
+    for (int p = 1; p < nproj; ++p) consecutive = consecutive && qkvo[p] == qkvo[0] + p;
+    const int wmax = delta_width < kMmaMaxRank ? delta_width : kMmaMaxRank;
+    const int gp = (consecutive && nproj * wmax <= kMmaMaxRows) ? nproj : 1;
+    const int npad_max = (gp * wmax + 15) & ~15;
+    ShrinkArgs m = a;
+    m.src.seg_split = src.seg_split;
+    m.rows_per_cta = gp;
+    m.max_rb = nproj / gp;
+    m.mma_stage_bytes = kMmaXTileBytes + npad_max * kMmaKBlock * 2;
+    const size_t smem = static_cast<size_t>(kMmaStages) * m.mma_stage_bytes + kMmaSlack;
+    const int64_t grid = static_cast<int64_t>(src.n_seg) * src.mma_tiles_per_seg * m.max_rb;
+    if (dtype == SLORA_F16) {
+      auto k = lora_shrink_mma_kernel<__half>;
+      rc = ensure_dyn_smem(k, 4, smem);
+      if (!rc) rc = launch(k, grid, kMmaThreads, smem, flags, stream, m, "shrink(tensor core)");
+    } else {
+      auto k = lora_shrink_mma_kernel<__nv_bfloat16>;
+      rc = ensure_dyn_smem(k, 5, smem);
+      if (!rc) rc = launch(k, grid, kMmaThreads, smem, flags, stream, m, "shrink(tensor core)");
+    }
+    if (rc) return rc;
+    a.src.seg_split = src.seg_split;
+  }
   const bool can_pipe = (S % h_in == 0);
   const KernelChoice choice = kernel_choice();
   if (choice == CHOOSE_PIPELINED && !can_pipe)
@@ -309,6 +358,31 @@ int run_expand(const TileSrc& src, const Tables& tb, const void* w, const void* 
   a.delta_part_stride = delta_part_stride;
   a.rank_mult = rank_mult;
   a.status = status;
+  a.src.seg_split = 0;
+  bool can_mma = src.mode == MODE_SEGMENT && src.seg_split > 0 && mma_enabled() && delta_parts == 1 &&
+                 rank_mult == 1 && delta_stride % 8 == 0;
+  for (int p = 0; p < nproj; ++p)
+    can_mma = can_mma && aligned16(y[p]) && y_stride[p] % 8 == 0 && aligned16(delta[p]);
+  if (can_mma) {
+    ExpandArgs m = a;
+    m.src.seg_split = src.seg_split;
+    m.chunk_begin[0] = 0;
+    for (int p = 0; p < nproj; ++p)
+      m.chunk_begin[p + 1] = m.chunk_begin[p] + (h_out[p] + kMmaOutPerCta - 1) / kMmaOutPerCta;
+    const size_t smem = 3 * static_cast<size_t>(kMmaOperandBytes) + kMmaSlack;
+    const int64_t grid = static_cast<int64_t>(src.n_seg) * src.mma_tiles_per_seg * m.chunk_begin[nproj];
+    if (dtype == SLORA_F16) {
+      auto k = lora_expand_mma_kernel<__half>;
+      rc = ensure_dyn_smem(k, 6, smem);
+      if (!rc) rc = launch(k, grid, kMmaThreads, smem, flags, stream, m, "expand(tensor core)");
+    } else {
+      auto k = lora_expand_mma_kernel<__nv_bfloat16>;
+      rc = ensure_dyn_smem(k, 7, smem);
+      if (!rc) rc = launch(k, grid, kMmaThreads, smem, flags, stream, m, "expand(tensor core)");
+    }
+    if (rc) return rc;
+    a.src.seg_split = src.seg_split;
+  }
   const int pipe_piece = pow2_divisor(tb.pool_stride, kPipeChunk);
   bool can_pipe = delta_parts == 1 && delta_stride % 8 == 0 && pipe_piece * kMaxPieces >= kPipeChunk &&
                   (kPipeChunk - 1) / tb.pool_stride + 2 <= kSpanRows;
@@ -370,6 +444,8 @@ int make_seg_src(const int32_t* seg_start, const int32_t* seg_len, const int64_t
   src->seg_len = seg_len;
   src->n_seg = n_seg;
   src->tiles_per_seg = (max_seg_len + kTileTokens - 1) / kTileTokens;
+  src->mma_tiles_per_seg = (max_seg_len + kMmaTokens - 1) / kMmaTokens;
+  src->seg_split = max_seg_len >= kMmaMinTokens ? kMmaMinTokens : 0;
   src->T = (n_seg == 0 || src->tiles_per_seg == 0) ? 0 : T;
   if (static_cast<int64_t>(n_seg) * src->tiles_per_seg > 0x3fffffff)
     return fail(SLORA_ERR_SHAPE, "too many segment tiles");
@@ -397,7 +473,11 @@ Tables make_tables(const int64_t* start, const int64_t* ranks4, const int64_t* l
 // ------------------------------------------------------------------------------------------------------------
 extern "C" {
 
-int slora_version(void) { return 100; }
+int slora_version(void) { return 101; }
+
+void slora_launch_counts(int64_t out[4]) {
+  for (int i = 0; i < 4; ++i) out[i] = g_launches[i].load(std::memory_order_relaxed);
+}
 
 const char* slora_last_error(void) { return g_err; }
 
@@ -502,7 +582,7 @@ int slora_plan_build(void* workspace, size_t workspace_bytes, const int64_t* ids
       reinterpret_cast<int32_t*>(workspace), ids, start, ranks4, loc_len, static_cast<int>(T),
       static_cast<int>(n_adapters), l.max_tiles);
   plan_fence_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>();
-  return check_launch("plan_build");
+  return check_launch("plan_build", 2);
 }
 
 int slora_plan_status(const void* workspace, int* status_out, int* n_tiles_out, void* stream) {
@@ -659,7 +739,7 @@ int slora_validate_tables(const int64_t* start, const int64_t* ranks4, const int
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   zero_report_kernel<<<1, 32, 0, s>>>(report);
   validate_tables_kernel<<<64, 256, 0, s>>>(start, ranks4, loc, ids, n_adapters, loc_len, T, pool_rows, report);
-  return check_launch("validate_tables");
+  return check_launch("validate_tables", 2);
 }
 
 }  // extern "C"
