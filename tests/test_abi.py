@@ -12,7 +12,7 @@ def _header_functions():
     text = open(os.path.join(ROOT, "include", "slora_b200.h")).read()
     text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
     out = {}
-    for m in re.finditer(r"\b(?:int|size_t|const char\*)\s+(slora_\w+)\s*\(([^;]*?)\)\s*;", text, flags=re.S):
+    for m in re.finditer(r"\b(?:int|void|size_t|const char\*)\s+(slora_\w+)\s*\(([^;]*?)\)\s*;", text, flags=re.S):
         args = m.group(2).strip()
         out[m.group(1)] = 0 if args == "void" else len(args.split(","))
     return out
