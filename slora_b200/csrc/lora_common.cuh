@@ -78,6 +78,7 @@ struct ShrinkArgs {
   int tok_pass;      // simple kernel: tokens staged per pass
   int piece;         // simple kernel: elements per bulk copy
   int mma_stage_bytes;  // tensor-core kernel: bytes of one pipeline stage
+  int mma_stages;       // tensor-core kernel: pipeline stages
   int32_t* status;
 };
 
@@ -98,6 +99,7 @@ struct ExpandArgs {
   int64_t delta_part_stride;
   int rank_mult;
   int piece;  // elements per bulk copy (power of two dividing pool_stride, <= kChunk)
+  int mma_stage_bytes;  // tensor-core kernel: bytes of one operand tile [128 x kpad_max]
   int32_t* status;
 };
 

@@ -185,11 +185,73 @@ int launch(K kernel, int64_t grid, int threads, size_t smem, unsigned flags, cud
   return SLORA_OK;
 }
 
+// The same with a second kernel argument (a tensor map or a set of them).
+template <typename K, typename A, typename B>
+int launch2(K kernel, int64_t grid, int threads, size_t smem, unsigned flags, cudaStream_t stream, const A& args,
+            const B& extra, const char* what) {
+  if (grid <= 0) return SLORA_OK;
+  if (grid > 0x7fffffffLL) return fail(SLORA_ERR_SHAPE, "%s: grid of %lld CTAs is too large", what, (long long)grid);
+  cudaLaunchConfig_t cfg;
+  memset(&cfg, 0, sizeof(cfg));
+  cfg.gridDim = dim3(static_cast<unsigned>(grid), 1, 1);
+  cfg.blockDim = dim3(static_cast<unsigned>(threads), 1, 1);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  int nattr = 0;
+  if (flags & SLORA_FLAG_PDL) {
+    attr[nattr].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[nattr].val.programmaticStreamSerializationAllowed = 1;
+    ++nattr;
+  }
+  cfg.attrs = attr;
+  cfg.numAttrs = nattr;
+  const cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, args, extra);
+  if (e != cudaSuccess) {
+    cudaGetLastError();
+    return fail(SLORA_ERR_LAUNCH, "%s: %s", what, cudaGetErrorString(e));
+  }
+  g_launches[family_of(what)].fetch_add(1, std::memory_order_relaxed);
+  return SLORA_OK;
+}
+
+// 2-D tensor map over a row-major [rows x inner] matrix of 16-bit elements with a box of [box_rows x 64] elements
+// and the 128-byte swizzle (the layout tcgen05.mma and the TMA reduce of the tensor-core kernels expect).  The
+// driver's encoder is looked up once through the runtime, so the library does not link against libcuda.
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+int make_tmap(CUtensorMap* map, int dtype, const void* base, int64_t inner, int64_t rows, int64_t row_stride_elems,
+              int box_rows) {
+  static EncodeTiledFn encode = [] {
+    void* fn = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q) != cudaSuccess ||
+        q != cudaDriverEntryPointSuccess) {
+      cudaGetLastError();
+      fn = nullptr;
+    }
+    return reinterpret_cast<EncodeTiledFn>(fn);
+  }();
+  if (!encode) return fail(SLORA_ERR_LAUNCH, "cuTensorMapEncodeTiled is not available from this driver");
+  const cuuint64_t dims[2] = {static_cast<cuuint64_t>(inner), static_cast<cuuint64_t>(rows)};
+  const cuuint64_t strides[1] = {static_cast<cuuint64_t>(row_stride_elems) * 2};
+  const cuuint32_t box[2] = {64, static_cast<cuuint32_t>(box_rows)};
+  const cuuint32_t estr[2] = {1, 1};
+  const CUresult r = encode(map, dtype == SLORA_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16,
+                            2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                            CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail(SLORA_ERR_LAUNCH, "cuTensorMapEncodeTiled failed with code %d", (int)r);
+  return SLORA_OK;
+}
+
 // Opt in to more than 48 KB of dynamic shared memory, once per (kernel, device) and size high-water mark.
+// (Kernels with sizeable static shared memory pass static_bytes: the 48 KB default limit covers both kinds.)
 template <typename K>
-int ensure_dyn_smem(K kernel, int which, size_t smem) {
+int ensure_dyn_smem(K kernel, int which, size_t smem, size_t static_bytes = 0) {
   static int high_water[8][64];
-  if (smem <= 48 * 1024) return SLORA_OK;
+  if (smem + static_bytes <= 48 * 1024) return SLORA_OK;
   int dev = 0;
   cudaGetDevice(&dev);
   if (dev < 0 || dev >= 64) dev = 0;
@@ -244,7 +306,8 @@ int run_shrink(const TileSrc& src, const Tables& tb, const void* w, const void* 
   a.status = status;
   // long segments first go to the tensor-core kernel; the launch below then skips them
   a.src.seg_split = 0;
-  if (src.mode == MODE_SEGMENT && src.seg_split > 0 && mma_enabled() && S == h_in && h_in % kMmaKBlock == 0) {
+  if (src.mode == MODE_SEGMENT && src.seg_split > 0 && mma_enabled() && S == h_in && h_in % kMmaKBlock == 0 &&
+      src.T < 0x7fffffff) {
     bool consecutive = true;
     for (int p = 1; p < nproj; ++p) consecutive = consecutive && qkvo[p] == qkvo[0] + p;
     const int wmax = delta_width < kMmaMaxRank ? delta_width : kMmaMaxRank;
@@ -255,16 +318,21 @@ int run_shrink(const TileSrc& src, const Tables& tb, const void* w, const void* 
     m.rows_per_cta = gp;
     m.max_rb = nproj / gp;
     m.mma_stage_bytes = kMmaXTileBytes + npad_max * kMmaKBlock * 2;
-    const size_t smem = static_cast<size_t>(kMmaStages) * m.mma_stage_bytes + kMmaSlack;
+    m.mma_stages = (kMmaSmemBudget - 1024) / m.mma_stage_bytes;
+    if (m.mma_stages > kMmaMaxStages) m.mma_stages = kMmaMaxStages;
+    const size_t smem = static_cast<size_t>(m.mma_stages) * m.mma_stage_bytes + 1024;
     const int64_t grid = static_cast<int64_t>(src.n_seg) * src.mma_tiles_per_seg * m.max_rb;
+    CUtensorMap x_map;
+    rc = make_tmap(&x_map, dtype, x, h_in, src.T, x_stride, kMmaTokens);
+    if (rc) return rc;
     if (dtype == SLORA_F16) {
       auto k = lora_shrink_mma_kernel<__half>;
-      rc = ensure_dyn_smem(k, 4, smem);
-      if (!rc) rc = launch(k, grid, kMmaThreads, smem, flags, stream, m, "shrink(tensor core)");
+      rc = ensure_dyn_smem(k, 4, smem, 4096);
+      if (!rc) rc = launch2(k, grid, kMmaShrinkThreads, smem, flags, stream, m, x_map, "shrink(tensor core)");
     } else {
       auto k = lora_shrink_mma_kernel<__nv_bfloat16>;
-      rc = ensure_dyn_smem(k, 5, smem);
-      if (!rc) rc = launch(k, grid, kMmaThreads, smem, flags, stream, m, "shrink(tensor core)");
+      rc = ensure_dyn_smem(k, 5, smem, 4096);
+      if (!rc) rc = launch2(k, grid, kMmaShrinkThreads, smem, flags, stream, m, x_map, "shrink(tensor core)");
     }
     if (rc) return rc;
     a.src.seg_split = src.seg_split;
@@ -363,22 +431,31 @@ int run_expand(const TileSrc& src, const Tables& tb, const void* w, const void* 
                  rank_mult == 1 && delta_stride % 8 == 0;
   for (int p = 0; p < nproj; ++p)
     can_mma = can_mma && aligned16(y[p]) && y_stride[p] % 8 == 0 && aligned16(delta[p]);
+  for (int p = 0; p < nproj; ++p) can_mma = can_mma && h_out[p] >= 64;
+  can_mma = can_mma && tb.pool_stride < 0x7fffffff && src.T < 0x7fffffff;
   if (can_mma) {
     ExpandArgs m = a;
     m.src.seg_split = src.seg_split;
     m.chunk_begin[0] = 0;
     for (int p = 0; p < nproj; ++p)
       m.chunk_begin[p + 1] = m.chunk_begin[p] + (h_out[p] + kMmaOutPerCta - 1) / kMmaOutPerCta;
-    const size_t smem = 3 * static_cast<size_t>(kMmaOperandBytes) + kMmaSlack;
+    const int wmax = delta_width < kMmaMaxRank ? delta_width : kMmaMaxRank;
+    m.mma_stage_bytes = kMmaTokens * ((wmax + 15) & ~15) * 2;
+    const size_t smem = kMmaOutTileBytes + static_cast<size_t>(1 + kMmaExStages) * m.mma_stage_bytes + 1024;
     const int64_t grid = static_cast<int64_t>(src.n_seg) * src.mma_tiles_per_seg * m.chunk_begin[nproj];
+    TmapSet y_maps;
+    memset(&y_maps, 0, sizeof(y_maps));
+    for (int p = 0; p < nproj && !rc; ++p)
+      rc = make_tmap(&y_maps.m[p], dtype, y[p], h_out[p], src.T, y_stride[p], kMmaTokens);
+    if (rc) return rc;
     if (dtype == SLORA_F16) {
       auto k = lora_expand_mma_kernel<__half>;
-      rc = ensure_dyn_smem(k, 6, smem);
-      if (!rc) rc = launch(k, grid, kMmaThreads, smem, flags, stream, m, "expand(tensor core)");
+      rc = ensure_dyn_smem(k, 6, smem, 12288);
+      if (!rc) rc = launch2(k, grid, kMmaExpandThreads, smem, flags, stream, m, y_maps, "expand(tensor core)");
     } else {
       auto k = lora_expand_mma_kernel<__nv_bfloat16>;
-      rc = ensure_dyn_smem(k, 7, smem);
-      if (!rc) rc = launch(k, grid, kMmaThreads, smem, flags, stream, m, "expand(tensor core)");
+      rc = ensure_dyn_smem(k, 7, smem, 12288);
+      if (!rc) rc = launch2(k, grid, kMmaExpandThreads, smem, flags, stream, m, y_maps, "expand(tensor core)");
     }
     if (rc) return rc;
     a.src.seg_split = src.seg_split;

@@ -3,39 +3,57 @@
 // A prefill sequence gives hundreds of consecutive tokens that share one adapter: its shrink is the small GEMM
 // delta[n x r] = X[n x h_in] * A^T and its expand y[n x h_out] += scale * delta[n x r] * B^T.  At rank 64 these run
 // at ~45 flop per byte, beyond what the FP32 pipes sustain at HBM speed, so tiles of 128 tokens go to the 5th
-// generation tensor cores: operands are staged in shared memory in the un-swizzled K-major core-matrix layout with
-// 16-byte cp.async copies (token rows and pool rows are gathered through the same index tables as everywhere else,
-// so no tensor map is needed), one thread issues tcgen05.mma with the accumulator in tensor memory, completion is
-// tracked with tcgen05.commit on an mbarrier, and the epilogue reads the accumulator back with tcgen05.ld.
+// generation tensor cores.  Both kernels are warp-specialised:
 //
-// Operand layout in shared memory (both operands, element size 2): the tile [rows x 8*chunks] is cut into 16-byte
-// chunks (8 elements of K); chunk (row, c) lives at  c * rows * 16 + row * 16.  Eight consecutive rows of one chunk
-// form a contiguous 128-byte core matrix, so the descriptor's stride between 8-row groups (SBO) is 128 bytes and
-// the stride between the two K-chunks of one K=16 instruction (LBO) is rows * 16 bytes.
+//   shrink   one lane issues TMA tile loads of the activations (tensor map over x, 128-byte swizzle), eight loader
+//            warps gather the adapter rows through the index tables with 16-byte cp.async copies (one K-block in
+//            flight per warp, so the proxy fence each warp needs after its copies never stalls another warp's),
+//            one lane issues tcgen05.mma with the accumulator in tensor memory and frees stages with
+//            tcgen05.commit, four warps read the accumulator back with tcgen05.ld and store delta.
+//   expand   two loader warps gather chunks of 128 outputs of B with cp.async, one lane issues the MMAs into a
+//            double-buffered accumulator, four warps scale and round the result into a swizzled shared-memory tile
+//            that one lane adds into y with a TMA reduce (an element-wise 16-bit add in L2, which is also how the
+//            reference accumulates: it rounds the FP32 sum to the output type and then adds, bgmv_impl.cuh:185-199).
 //
-// Every wait is bounded; a CTA that gives up records SLORA_STATUS_TIMEOUT, drains its copies and frees its tensor
-// memory before it returns.
+// Operand layouts in shared memory.  Gathered operands (adapter rows, B chunks, delta tile) use the un-swizzled
+// K-major core-matrix layout: the tile [rows x 8*chunks] is cut into 16-byte chunks (8 elements of K); chunk
+// (row, c) lives at c * rows * 16 + row * 16, so eight consecutive rows of one chunk form a contiguous 128-byte
+// core matrix, the descriptor's stride between 8-row groups (SBO) is 128 bytes and the stride between the two
+// K-chunks of one K=16 instruction (LBO) is rows * 16 bytes.  TMA-loaded activations use the 128-byte swizzled
+// K-major layout (rows of 64 elements, SBO = 1024 bytes, K advanced by 32 bytes inside the swizzle span).
+//
+// Every wait is bounded; a CTA that gives up records SLORA_STATUS_TIMEOUT and frees its tensor memory before it
+// returns.  No load uses cluster multicast.
 #pragma once
+
+#include <cuda.h>
 
 #include "lora_pipelined.cuh"
 
 namespace slora {
 
 constexpr int kMmaTokens = 128;    // tokens per tile = M of one tcgen05.mma
-constexpr int kMmaThreads = 128;   // four warps: warp w reads accumulator lanes [32w, 32w + 32)
-constexpr int kMmaKBlock = 64;     // K elements staged per pipeline stage of the shrink
-constexpr int kMmaKChunks = kMmaKBlock / 8;
-constexpr int kMmaStages = 4;
+constexpr int kMmaKBlock = 64;     // K elements per pipeline stage of the shrink (one 128-byte swizzle span)
 constexpr int kMmaMinTokens = 32;  // segments at least this long are served here
 constexpr int kMmaMaxRows = 256;   // adapter rows one shrink CTA multiplies by (N of the instruction)
-constexpr int kMmaShrinkCols = 256;
-constexpr int kMmaSlack = 8 * 1024;  // unused tail of the dynamic shared memory
-constexpr int kMmaOutChunk = 128;    // outputs per accumulator tile of the expand
-constexpr int kMmaOutPerCta = 512;   // outputs one expand CTA walks through
-constexpr int kMmaExpandCols = 128;
 constexpr int kMmaMaxRank = 128;
-constexpr int kMmaXTileBytes = kMmaTokens * kMmaKBlock * 2;         // 16 KB
-constexpr int kMmaOperandBytes = kMmaTokens * kMmaMaxRank * 2;      // 32 KB: [128 x 128] expand operand
+constexpr int kMmaMaxStages = 8;
+constexpr int kMmaLoaderWarps = 8;  // shrink: one stage per loader warp
+constexpr int kMmaShrinkThreads = (kMmaLoaderWarps + 2) * 32;  // + activation TMA warp + MMA warp
+constexpr int kMmaXTileBytes = kMmaTokens * kMmaKBlock * 2;    // 16 KB
+constexpr int kMmaSmemBudget = 200 * 1024;
+constexpr int kMmaOutChunk = 128;   // outputs per accumulator tile of the expand
+constexpr int kMmaOutPerCta = 512;  // outputs one expand CTA walks through
+constexpr int kMmaExLoaderWarps = 2;
+constexpr int kMmaExStages = 2;
+constexpr int kMmaExpandThreads = (4 + kMmaExLoaderWarps + 1) * 32;
+constexpr int kMmaOutTileBytes = kMmaTokens * kMmaOutChunk * 2;  // 32 KB: two swizzled halves of 64 columns
+constexpr int kMmaExpandCols = 256;                              // two accumulators of 128 columns
+
+// Tensor maps of the y buffers of one expand call.
+struct TmapSet {
+  CUtensorMap m[3];
+};
 
 // ---- PTX wrappers ---------------------------------------------------------------------------------------------
 __device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
@@ -115,6 +133,57 @@ __device__ __forceinline__ uint32_t umma_idesc(int n) {
          (static_cast<uint32_t>(kMmaTokens >> 4) << 24);
 }
 
+// TMA tile load (2-D tensor map) into this CTA's shared memory, completion on an mbarrier.
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cta.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];" ::"r"(dst),
+      "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar)), "r"(x), "r"(y)
+      : "memory");
+}
+// TMA tile reduce: global[tile] += shared[tile], element-wise in the tensor map's type.
+__device__ __forceinline__ void tma_reduce_add_2d(const CUtensorMap* map, int x, int y, uint32_t src) {
+  asm volatile("cp.reduce.async.bulk.tensor.2d.global.shared::cta.add.bulk_group [%0, {%2, %3}], [%1];" ::"l"(
+                   reinterpret_cast<uint64_t>(map)),
+               "r"(src), "r"(x), "r"(y)
+               : "memory");
+}
+__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void bulk_wait_read() {
+  asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory");
+}
+template <int N>
+__device__ __forceinline__ void bulk_wait() {
+  asm volatile("cp.async.bulk.wait_group %0;" ::"n"(N) : "memory");
+}
+__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_all;" ::: "memory"); }
+// Barrier among `threads` threads of the CTA (hardware barrier 1; barrier 0 is __syncthreads), and the same with an
+// AND-reduction of a predicate.
+__device__ __forceinline__ void named_sync(int threads) { asm volatile("bar.sync 1, %0;" ::"r"(threads) : "memory"); }
+__device__ __forceinline__ bool named_and(int threads, bool pred) {
+  uint32_t out;
+  asm volatile(
+      "{\n"
+      ".reg .pred p, q;\n"
+      "setp.ne.u32 q, %1, 0;\n"
+      "bar.red.and.pred p, 1, %2, q;\n"
+      "selp.u32 %0, 1, 0, p;\n"
+      "}\n"
+      : "=r"(out)
+      : "r"(static_cast<uint32_t>(pred)), "r"(threads)
+      : "memory");
+  return out != 0;
+}
+// Shared-memory matrix descriptor, K-major, 128-byte swizzle: rows of 128 bytes, 8-row groups 1024 bytes apart.
+__device__ __forceinline__ uint64_t umma_smem_desc_sw128(uint32_t addr) {
+  uint64_t d = static_cast<uint64_t>((addr & 0x3ffffu) >> 4);
+  d |= static_cast<uint64_t>(1) << 16;
+  d |= static_cast<uint64_t>(1024 >> 4) << 32;
+  d |= static_cast<uint64_t>(1) << 46;
+  d |= static_cast<uint64_t>(2) << 61;
+  return d;
+}
+
 // ---- tiles ----------------------------------------------------------------------------------------------------
 struct MmaTile {
   int adapter;
@@ -161,14 +230,23 @@ __device__ __forceinline__ bool lookup_mma_tile(const TileSrc& s, const Tables& 
 
 // ------------------------------------------------------------------------------------------------------------
 // shrink: delta[p][tok, j] = sum_k x[tok, k] * A_p[j, k] for the projections p of this CTA's group
-// grid: (segment tile, projection group).  dynamic shared memory: kMmaStages stages of
-//   [x tile 128 x 64][adapter rows npad_max x 64], then kMmaSlack unused bytes
+// grid: (segment tile, projection group).  dynamic shared memory (1024-byte aligned): `mma_stages` stages of
+//   [x tile 128 x 64, swizzled][adapter rows npad_max x 64, core-matrix layout]
 // ------------------------------------------------------------------------------------------------------------
+struct ShrinkMmaCtl {
+  uint64_t full[kMmaMaxStages];   // 2 arrivals: the stage's loader warp, the activation TMA (with its bytes)
+  uint64_t empty[kMmaMaxStages];  // 1 arrival: tcgen05.commit after the stage's MMAs
+  uint64_t acc_done;
+  uint32_t tmem;
+  int bad;
+  int64_t row_off[kMmaMaxRows];  // element offset of each adapter row in the pool
+};
+
 template <typename T>
-__global__ void __launch_bounds__(kMmaThreads, 1) lora_shrink_mma_kernel(const ShrinkArgs a) {
-  extern __shared__ __align__(128) unsigned char dyn_smem[];
-  __shared__ __align__(8) uint64_t mma_done[kMmaStages];
-  __shared__ uint32_t s_tmem;
+__global__ void __launch_bounds__(kMmaShrinkThreads, 1)
+    lora_shrink_mma_kernel(const ShrinkArgs a, const __grid_constant__ CUtensorMap x_map) {
+  extern __shared__ __align__(1024) unsigned char mma_smem[];
+  __shared__ ShrinkMmaCtl ctl;
 
   pdl_launch_dependents();
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -190,109 +268,119 @@ __global__ void __launch_bounds__(kMmaThreads, 1) lora_shrink_mma_kernel(const S
 
   // every adapter row this CTA reads is checked before anything is copied
   bool rows_ok = true;
-  for (int j = tid; j < rows; j += kMmaThreads) {
-    const int64_t e = a.tb.loc[base + j];
+  for (int j = tid; j < npad; j += kMmaShrinkThreads) {
+    const int64_t e = a.tb.loc[base + min(j, rows - 1)];
     if (e < 0 || e >= a.tb.pool_rows) rows_ok = false;
+    ctl.row_off[j] = e * S;
   }
   if (!__syncthreads_and(rows_ok)) {
     if (tid == 0) set_status(a.status, SLORA_STATUS_BAD_TABLE);
     return;
   }
 
-  // this thread's share of every stage: chunk c of eight token rows and of up to sixteen adapter rows
-  const int c = (tid >> 3) & (kMmaKChunks - 1);
-  const int row0 = ((tid >> 6) << 3) | (tid & 7);
-  const T* xsrc[8];
-#pragma unroll
-  for (int i = 0; i < 8; ++i) {
-    const int row = row0 + i * 16;
-    const int tok = t.first + min(row, t.n - 1);
-    xsrc[i] = reinterpret_cast<const T*>(a.x) + static_cast<int64_t>(tok) * a.x_stride + c * 8;
-  }
-  const int na = npad >> 4;  // adapter-row copies per thread and stage
-  const T* asrc[16];
-#pragma unroll
-  for (int i = 0; i < 16; ++i) {
-    const int row = min(row0 + i * 16, rows - 1);
-    const int64_t e = (i < na) ? a.tb.loc[base + row] : 0;
-    asrc[i] = reinterpret_cast<const T*>(a.w) + e * S + c * 8;
-  }
-  const uint32_t smem0 = smem_u32(dyn_smem);
+  const int nst = a.mma_stages;
+  const uint32_t smem0 = (smem_u32(mma_smem) + 1023u) & ~1023u;
   const uint32_t stage_bytes = static_cast<uint32_t>(a.mma_stage_bytes);
-  const uint32_t x_dst = c * (kMmaTokens * 16) + row0 * 16;
-  const uint32_t a_dst = kMmaXTileBytes + c * (npad * 16) + row0 * 16;
-
+  const int nkb = a.h_in / kMmaKBlock;
   if (tid == 0) {
-#pragma unroll
-    for (int s = 0; s < kMmaStages; ++s) mbar_init(&mma_done[s], 1);
+    for (int s = 0; s < nst; ++s) {
+      mbar_init(&ctl.full[s], 2);
+      mbar_init(&ctl.empty[s], 1);
+    }
+    mbar_init(&ctl.acc_done, 1);
+    ctl.bad = 0;
     fence_barrier_init();
+    fence_proxy_async();
   }
   // accumulator columns: a power of two covering the widest tile of this launch
-  const uint32_t cols = (a.mma_stage_bytes - kMmaXTileBytes) / (kMmaKBlock * 2) > 128 ? kMmaShrinkCols : 128;
+  const uint32_t cols = (a.mma_stage_bytes - kMmaXTileBytes) / (kMmaKBlock * 2) > 128 ? 256 : 128;
   if (warp == 0) {
-    tmem_alloc(&s_tmem, cols);
+    tmem_alloc(&ctl.tmem, cols);
     tmem_relinquish();
   }
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
-  const uint32_t tmem = s_tmem;
-  const uint32_t idesc = umma_idesc<T>(npad);
-  const int nkb = a.h_in / kMmaKBlock;
+  const uint32_t tmem = ctl.tmem;
 
-  pdl_wait();  // activations come from the kernel before this one
-  bool ok = true;
-  for (int kb = 0; kb < nkb + kMmaStages - 1; ++kb) {
-    if (kb < nkb) {
-      const int s = kb % kMmaStages;
-      // the MMAs that read this stage's previous contents must have completed
-      if (kb >= kMmaStages) ok = ok && mbar_wait_timed(&mma_done[s], ((kb / kMmaStages) - 1) & 1);
-      if (ok) {
-        const uint32_t sb = smem0 + s * stage_bytes;
-        const int k0 = kb * kMmaKBlock;
-#pragma unroll
-        for (int i = 0; i < 8; ++i) cp_async16(sb + x_dst + i * 256, xsrc[i] + k0);
-#pragma unroll
-        for (int i = 0; i < 16; ++i) {
-          if (i < na) cp_async16(sb + a_dst + i * 256, asrc[i] + k0);
+  if (warp < kMmaLoaderWarps) {
+    // ---- loader warp: gathers the adapter rows of K-blocks warp, warp + nst, ... into stage `warp` ----
+    if (warp < nst) {
+      const int row_lo = lane & 7, c_lo = lane >> 3;
+      const T* w = reinterpret_cast<const T*>(a.w);
+      const uint32_t dst0 = smem0 + warp * stage_bytes + kMmaXTileBytes + row_lo * 16;
+      for (int kb = warp, use = 0; kb < nkb; kb += nst, ++use) {
+        if (use > 0 && !mbar_wait_timed(&ctl.empty[warp], (use - 1) & 1)) {
+          ctl.bad = 1;
+          break;
         }
+        const int k0 = kb * kMmaKBlock;
+        for (int rg = 0; rg < npad; rg += 8) {
+          const T* src = w + ctl.row_off[rg + row_lo] + k0;
+#pragma unroll
+          for (int ch = 0; ch < 2; ++ch) {
+            const int c = ch * 4 + c_lo;
+            cp_async16(dst0 + c * (npad * 16) + rg * 16, src + c * 8);
+          }
+        }
+        cp_async_wait_all();
+        fence_proxy_async();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&ctl.full[warp]);
       }
     }
-    cp_async_commit();
-    const int kc = kb - (kMmaStages - 1);
-    if (kc >= 0) {
-      cp_async_wait<kMmaStages - 1>();
-      fence_proxy_async();
-      if (!__syncthreads_and(ok)) {
-        ok = false;
-        break;
+  } else if (warp == kMmaLoaderWarps) {
+    // ---- activation tiles by TMA ----
+    if (lane == 0) {
+      pdl_wait();  // activations come from the kernel before this one
+      for (int kb = 0; kb < nkb; ++kb) {
+        const int s = kb % nst, use = kb / nst;
+        if (use > 0 && !mbar_wait_timed(&ctl.empty[s], (use - 1) & 1)) {
+          ctl.bad = 1;
+          break;
+        }
+        mbar_expect_tx(&ctl.full[s], kMmaXTileBytes);
+        tma_load_2d(smem0 + s * stage_bytes, &x_map, kb * kMmaKBlock, t.first, &ctl.full[s]);
       }
-      if (tid == 0) {
+    }
+  } else {
+    // ---- MMA issue ----
+    if (lane == 0) {
+      const uint32_t idesc = umma_idesc<T>(npad);
+      bool ok = true;
+      for (int kb = 0; kb < nkb; ++kb) {
+        const int s = kb % nst, use = kb / nst;
+        if (!mbar_wait_timed(&ctl.full[s], use & 1)) {
+          ctl.bad = 1;
+          ok = false;
+          break;
+        }
         tc_fence_after();
-        const uint32_t sb = smem0 + (kc % kMmaStages) * stage_bytes;
+        const uint32_t sb = smem0 + s * stage_bytes;
 #pragma unroll
         for (int ks = 0; ks < kMmaKBlock / 16; ++ks) {
-          const uint64_t da = umma_smem_desc(sb + ks * 2 * (kMmaTokens * 16), kMmaTokens * 16, 128);
+          const uint64_t da = umma_smem_desc_sw128(sb + ks * 32);
           const uint64_t db = umma_smem_desc(sb + kMmaXTileBytes + ks * 2 * (npad * 16), npad * 16, 128);
-          umma_f16(tmem, da, db, idesc, (kc > 0 || ks > 0) ? 1u : 0u);
+          umma_f16(tmem, da, db, idesc, (kb > 0 || ks > 0) ? 1u : 0u);
         }
-        umma_commit(&mma_done[kc % kMmaStages]);
+        umma_commit(&ctl.empty[s]);
       }
+      if (ok) umma_commit(&ctl.acc_done);
     }
   }
-  cp_async_wait<0>();
-  if (ok) ok = mbar_wait_timed(&mma_done[(nkb - 1) % kMmaStages], ((nkb - 1) / kMmaStages) & 1);
-  ok = __syncthreads_and(ok);
-  tc_fence_after();
 
-  if (ok) {
-    // epilogue: thread (warp, lane) owns accumulator lane 32 * warp + lane = one token of the tile
+  // ---- epilogue: thread (warp, lane) of warps 0..3 owns accumulator lane 32 * warp + lane = one token ----
+  bool ok = true;
+  if (warp < 4) ok = mbar_wait_timed(&ctl.acc_done, 0);
+  ok = __syncthreads_and(ok) && ctl.bad == 0;
+  tc_fence_after();
+  if (ok && warp < 4) {
     const int row = warp * 32 + lane;
     const bool live = row < t.n;
     const int64_t tok = t.first + (live ? row : 0);
-    bool vec = (r % 8 == 0) && (a.delta_stride % 8 == 0);
+    bool vec = (a.delta_stride % 8 == 0);
     for (int q = 0; q < gp; ++q) vec = vec && ((reinterpret_cast<uintptr_t>(pick3(a.delta, p0 + q)) & 15) == 0);
-    int p = 0, jj = 0;  // column j = p * r + jj
+    int p = 0, jj = 0;  // column j = p * r + jj; r is a multiple of 8
     for (int c0 = 0; c0 < npad; c0 += 16) {
       uint32_t v[16];
       tmem_ld16(tmem + (static_cast<uint32_t>(warp * 32) << 16) + c0, v);
@@ -301,43 +389,29 @@ __global__ void __launch_bounds__(kMmaThreads, 1) lora_shrink_mma_kernel(const S
       for (int h = 0; h < 2; ++h) {
         if (c0 + h * 8 < rows) {
           T* drow = reinterpret_cast<T*>(pick3(a.delta, p0 + p)) + tok * a.delta_stride;
-          if (vec) {
-            if (live && jj + 8 <= a.delta_width) {
-              union {
-                uint4 q;
-                T e[8];
-              } pk;
+          if (live && vec && jj + 8 <= a.delta_width) {
+            union {
+              uint4 q;
+              T e[8];
+            } pk;
 #pragma unroll
-              for (int e = 0; e < 8; ++e) pk.e[e] = from_f32<T>(__uint_as_float(v[h * 8 + e]));
-              *reinterpret_cast<uint4*>(drow + jj) = pk.q;
-            } else if (live) {
-#pragma unroll
-              for (int e = 0; e < 8; ++e) {
-                if (jj + e < a.delta_width) drow[jj + e] = from_f32<T>(__uint_as_float(v[h * 8 + e]));
-              }
-            }
-            jj += 8;
-            if (jj >= r) {
-              jj = 0;
-              ++p;
-            }
-          } else {
+            for (int e = 0; e < 8; ++e) pk.e[e] = from_f32<T>(__uint_as_float(v[h * 8 + e]));
+            *reinterpret_cast<uint4*>(drow + jj) = pk.q;
+          } else if (live) {
 #pragma unroll
             for (int e = 0; e < 8; ++e) {
-              if (c0 + h * 8 + e < rows) {
-                if (live && jj < a.delta_width)
-                  drow[jj] = from_f32<T>(__uint_as_float(v[h * 8 + e]));
-                if (++jj >= r) {
-                  jj = 0;
-                  ++p;
-                }
-              }
+              if (jj + e < a.delta_width) drow[jj + e] = from_f32<T>(__uint_as_float(v[h * 8 + e]));
             }
+          }
+          jj += 8;
+          if (jj >= r) {
+            jj = 0;
+            ++p;
           }
         }
       }
     }
-  } else if (tid == 0) {
+  } else if (!ok && tid == 0) {
     set_status(a.status, SLORA_STATUS_TIMEOUT);
   }
   tc_fence_before();
@@ -347,14 +421,26 @@ __global__ void __launch_bounds__(kMmaThreads, 1) lora_shrink_mma_kernel(const S
 
 // ------------------------------------------------------------------------------------------------------------
 // expand: y[p][tok, o] += scale * sum_k delta[p][tok, k] * B_p[o, k],  B_p[o, k] = flat slot element o * r + k
-// grid: (segment tile, projection, range of kMmaOutPerCta outputs).  dynamic shared memory:
-//   [delta tile 128 x kpad][B chunk stage 0: 128 x kpad][B chunk stage 1], 32 KB each, then kMmaSlack unused bytes
+// grid: (segment tile, projection, range of kMmaOutPerCta outputs).  dynamic shared memory (1024-byte aligned):
+//   [out tile] 32 KB (two 128-byte-swizzled halves of 64 columns),
+//   [delta tile 128 x kpad_max][B chunk stage 0][B chunk stage 1] of `mma_stage_bytes` each (core-matrix layout)
 // ------------------------------------------------------------------------------------------------------------
+struct ExpandMmaCtl {
+  uint64_t d_full;                    // arrivals: the loader warps (delta tile landed)
+  uint64_t b_full[kMmaExStages];      // 1 arrival: the chunk's loader warp
+  uint64_t b_empty[kMmaExStages];     // 1 arrival: tcgen05.commit
+  uint64_t acc_full[2];               // 1 arrival: tcgen05.commit
+  uint64_t acc_empty[2];              // 4 arrivals: the epilogue warps
+  uint32_t tmem;
+  int bad;
+};
+
 template <typename T>
-__global__ void __launch_bounds__(kMmaThreads) lora_expand_mma_kernel(const ExpandArgs a) {
-  extern __shared__ __align__(128) unsigned char dyn_smem[];
-  __shared__ __align__(8) uint64_t acc_done;
-  __shared__ uint32_t s_tmem;
+__global__ void __launch_bounds__(kMmaExpandThreads)
+    lora_expand_mma_kernel(const ExpandArgs a, const __grid_constant__ TmapSet y_maps) {
+  extern __shared__ __align__(1024) unsigned char mma_smem[];
+  __shared__ ExpandMmaCtl ctl;
+  __shared__ int64_t s_row_off[kMmaOutPerCta * kMmaMaxRank / 8 / 8 + 2];  // pool rows behind this CTA's outputs
 
   pdl_launch_dependents();
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -372,19 +458,26 @@ __global__ void __launch_bounds__(kMmaThreads) lora_expand_mma_kernel(const Expa
   if (o_begin >= h_out) return;
   const int o_end = min(h_out, o_begin + kMmaOutPerCta);
   const int nch = (o_end - o_begin + kMmaOutChunk - 1) / kMmaOutChunk;
-  const int64_t S = a.tb.pool_stride;
+  const uint32_t S = static_cast<uint32_t>(a.tb.pool_stride);
   const int64_t base = t.loc_base + static_cast<int64_t>(R) * pick3(a.qkvo, p);
+  const int kpad = (R + 15) & ~15;  // K of the contraction, zero-padded to the instruction's K = 16
+  const uint32_t tile_bytes = static_cast<uint32_t>(a.mma_stage_bytes);
+  if (static_cast<uint32_t>(kMmaTokens * kpad * 2) > tile_bytes) {
+    if (tid == 0) set_status(a.status, SLORA_STATUS_BAD_RANK);  // wider than the caller's delta_width promised
+    return;
+  }
 
   // the pool rows behind outputs [o_begin, o_end) are checked before anything is copied
-  const int pr_first = static_cast<int>(static_cast<int64_t>(o_begin) * R / S);
-  const int pr_last = static_cast<int>((static_cast<int64_t>(o_end) * R - 1) / S);
-  bool rows_ok = true;
-  for (int pr = pr_first + tid; pr <= pr_last; pr += kMmaThreads) {
-    if (pr >= R) {
+  const uint32_t pr_first = static_cast<uint32_t>(o_begin) * R / S;
+  const uint32_t pr_last = (static_cast<uint32_t>(o_end) * R - 1) / S;
+  bool rows_ok = pr_last - pr_first < sizeof(s_row_off) / sizeof(s_row_off[0]);
+  for (uint32_t pr = pr_first + tid; pr <= pr_last && rows_ok; pr += kMmaExpandThreads) {
+    if (pr >= static_cast<uint32_t>(R)) {
       rows_ok = false;
     } else {
       const int64_t e = a.tb.loc[base + pr];
       if (e < 0 || e >= a.tb.pool_rows) rows_ok = false;
+      s_row_off[pr - pr_first] = e * static_cast<int64_t>(S);
     }
   }
   if (!__syncthreads_and(rows_ok)) {
@@ -392,151 +485,170 @@ __global__ void __launch_bounds__(kMmaThreads) lora_expand_mma_kernel(const Expa
     return;
   }
 
-  const int cpr = R >> 3;             // 16-byte chunks per operand row
-  const int kpad = (R + 15) & ~15;    // K of the contraction, zero-padded to the instruction's K = 16
-  const uint32_t smem0 = smem_u32(dyn_smem);
-  const uint32_t d_smem = smem0;
-  const uint32_t b_smem = smem0 + kMmaOperandBytes;
+  const int cpr = R >> 3;  // 16-byte chunks per operand row
+  const uint32_t smem0 = (smem_u32(mma_smem) + 1023u) & ~1023u;
+  const uint32_t out_smem = smem0;
+  const uint32_t d_smem = smem0 + kMmaOutTileBytes;
+  const uint32_t b_smem = d_smem + tile_bytes;
   constexpr uint32_t kLbo = kMmaTokens * 16;  // both operands hold 128 rows
 
-  // This thread's cpr copies of every operand tile: item id = it * 128 + tid -> (row, chunk).
-  uint32_t item_dst[16];  // byte offset inside an operand tile
-  uint32_t item_rel[16];  // row * R + chunk * 8
-#pragma unroll
-  for (int it = 0; it < 16; ++it) {
-    const int id = it * kMmaThreads + tid;
-    const int g = id / (8 * cpr);
-    const int rem = id - g * (8 * cpr);
-    const int ch = rem >> 3;
-    const int row = g * 8 + (rem & 7);
-    item_dst[it] = ch * kLbo + row * 16;
-    item_rel[it] = (static_cast<uint32_t>(row) << 16) | static_cast<uint32_t>(ch);
-  }
-  if (kpad != R) {
-    // the chunk that pads K to a multiple of 16 is zero in all three operand tiles and never overwritten
-    const uint4 z = make_uint4(0, 0, 0, 0);
-    for (int row = tid; row < 3 * kMmaTokens; row += kMmaThreads) {
-      const int which = row / kMmaTokens;
-      const int rr = row - which * kMmaTokens;
-      *reinterpret_cast<uint4*>(dyn_smem + which * kMmaOperandBytes + cpr * kLbo + rr * 16) = z;
-    }
-  }
-
-  auto load_b_chunk = [&](int ch_idx) {
-    const int o0 = o_begin + ch_idx * kMmaOutChunk;
-    const uint32_t dst = b_smem + (ch_idx & 1) * kMmaOperandBytes;
-#pragma unroll
-    for (int it = 0; it < 16; ++it) {
-      if (it < cpr) {
-        const int row = static_cast<int>(item_rel[it] >> 16);
-        const int chk = static_cast<int>(item_rel[it] & 0xffff);
-        const int o = min(o0 + row, h_out - 1);
-        const int64_t f = static_cast<int64_t>(o) * R + chk * 8;
-        const int64_t pr = f / S;
-        const int64_t col = f - pr * S;
-        const int64_t e = a.tb.loc[base + pr];
-        cp_async16(dst + item_dst[it], reinterpret_cast<const T*>(a.w) + e * S + col);
-      }
-    }
-  };
-
   if (tid == 0) {
-    mbar_init(&acc_done, 1);
+    mbar_init(&ctl.d_full, kMmaExLoaderWarps);
+    for (int s = 0; s < kMmaExStages; ++s) {
+      mbar_init(&ctl.b_full[s], 1);
+      mbar_init(&ctl.b_empty[s], 1);
+    }
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(&ctl.acc_full[s], 1);
+      mbar_init(&ctl.acc_empty[s], 4);
+    }
+    ctl.bad = 0;
     fence_barrier_init();
+    fence_proxy_async();
   }
   if (warp == 0) {
-    tmem_alloc(&s_tmem, kMmaExpandCols);
+    tmem_alloc(&ctl.tmem, kMmaExpandCols);
     tmem_relinquish();
   }
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
-  const uint32_t tmem = s_tmem;
+  const uint32_t tmem = ctl.tmem;
 
-  load_b_chunk(0);  // the pool does not depend on the kernel before this one
-  cp_async_commit();
-  pdl_wait();
-  {
-    const T* dsrc = reinterpret_cast<const T*>(pick3(a.delta, p));
-#pragma unroll
-    for (int it = 0; it < 16; ++it) {
-      if (it < cpr) {
-        const int row = static_cast<int>(item_rel[it] >> 16);
-        const int chk = static_cast<int>(item_rel[it] & 0xffff);
-        const int64_t tok = t.first + min(row, t.n - 1);
-        cp_async16(d_smem + item_dst[it], dsrc + tok * a.delta_stride + chk * 8);
+  if (warp < 4) {
+    // ---- epilogue: scale, round, stage in shared memory, add into y with a TMA reduce ----
+    const float scale = to_f32<T>(reinterpret_cast<const T*>(a.scales)[t.adapter]);
+    const int row = warp * 32 + lane;
+    const bool live = row < t.n;
+    const CUtensorMap* ymap = &y_maps.m[p];
+    pdl_wait();  // y is also written by the kernel before this one
+    for (int ch = 0; ch < nch; ++ch) {
+      const int ab = ch & 1;
+      const int o0 = o_begin + ch * kMmaOutChunk;
+      const int ncols = min(kMmaOutChunk, o_end - o0);  // a multiple of 8
+      const int npad = (ncols + 15) & ~15;
+      // the previous chunk's reduce must have finished reading the out tile
+      if (tid == 0) bulk_wait_read<0>();
+      const bool got = mbar_wait_timed(&ctl.acc_full[ab], (ch >> 1) & 1);
+      // all four warps go on, or leave, together
+      if (!named_and(128, got)) {
+        ctl.bad = 1;
+        break;
       }
-    }
-  }
-  cp_async_commit();
-
-  const float scale = to_f32<T>(reinterpret_cast<const T*>(a.scales)[t.adapter]);
-  const int row = warp * 32 + lane;
-  const bool live = row < t.n;
-  T* yrow = reinterpret_cast<T*>(pick3(a.y, p)) + (t.first + (live ? row : 0)) * pick3(a.y_stride, p);
-  bool ok = true;
-  for (int ch = 0; ch < nch; ++ch) {
-    if (ch + 1 < nch) load_b_chunk(ch + 1);
-    cp_async_commit();
-    const int o0 = o_begin + ch * kMmaOutChunk;
-    const int ncols = min(kMmaOutChunk, o_end - o0);  // a multiple of 8
-    const int npad = (ncols + 15) & ~15;
-    // this token's 128 outputs of y, fetched while the operands land and the MMA runs
-    uint4 yv[16];
-#pragma unroll
-    for (int q = 0; q < 16; ++q) {
-      yv[q] = make_uint4(0, 0, 0, 0);
-      if (live && q * 8 < ncols) yv[q] = *reinterpret_cast<const uint4*>(yrow + o0 + q * 8);
-    }
-    cp_async_wait<1>();
-    fence_proxy_async();
-    __syncthreads();
-    if (tid == 0) {
       tc_fence_after();
-      const uint32_t idesc = umma_idesc<T>(npad);
-      const uint32_t bs = b_smem + (ch & 1) * kMmaOperandBytes;
-      for (int ks = 0; ks < kpad / 16; ++ks) {
-        const uint64_t da = umma_smem_desc(d_smem + ks * 2 * kLbo, kLbo, 128);
-        const uint64_t db = umma_smem_desc(bs + ks * 2 * kLbo, kLbo, 128);
-        umma_f16(tmem, da, db, idesc, ks > 0 ? 1u : 0u);
-      }
-      umma_commit(&acc_done);
-    }
-    ok = mbar_wait_timed(&acc_done, ch & 1);
-    ok = __syncthreads_and(ok);
-    if (!ok) break;
-    tc_fence_after();
+      const uint32_t out_tile = out_smem;
 #pragma unroll
-    for (int g = 0; g < kMmaOutChunk / 16; ++g) {
-      if (g * 16 < npad) {  // uniform over the CTA
-        uint32_t v[16];
-        tmem_ld16(tmem + (static_cast<uint32_t>(warp * 32) << 16) + g * 16, v);
-        tmem_ld_wait();
+      for (int g = 0; g < kMmaOutChunk / 16; ++g) {
+        if (g * 16 < npad) {  // uniform over the warps
+          uint32_t v[16];
+          tmem_ld16(tmem + (static_cast<uint32_t>(warp * 32) << 16) + ab * kMmaOutChunk + g * 16, v);
+          tmem_ld_wait();
 #pragma unroll
-        for (int h = 0; h < 2; ++h) {
-          const int q = g * 2 + h;
-          if (live && q * 8 < ncols) {
+          for (int h = 0; h < 2; ++h) {
             union {
               uint4 q4;
               T e[8];
             } pk;
-            pk.q4 = yv[q];
 #pragma unroll
             for (int e = 0; e < 8; ++e)
-              pk.e[e] = from_f32<T>(fmaf(scale, __uint_as_float(v[h * 8 + e]), to_f32<T>(pk.e[e])));
-            *reinterpret_cast<uint4*>(yrow + o0 + q * 8) = pk.q4;
+              pk.e[e] = from_f32<T>(live ? scale * __uint_as_float(v[h * 8 + e]) : 0.f);
+            const int col = g * 16 + h * 8;  // column of the 128-wide tile; half = col / 64
+            const uint32_t cc = static_cast<uint32_t>((col & 63) >> 3);
+            const uint32_t dst = out_tile + (col >> 6) * (kMmaTokens * 128) + row * 128 + ((cc ^ (row & 7)) << 4);
+            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(pk.q4.x), "r"(pk.q4.y),
+                         "r"(pk.q4.z), "r"(pk.q4.w)
+                         : "memory");
           }
         }
       }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&ctl.acc_empty[ab]);
+      fence_proxy_async();
+      named_sync(128);
+      if (tid == 0) {
+        for (int half = 0; half * 64 < ncols; ++half)
+          tma_reduce_add_2d(ymap, o0 + half * 64, t.first, out_tile + half * (kMmaTokens * 128));
+        bulk_commit();
+      }
     }
-    // all warps have read the accumulator before the next chunk's MMA overwrites it
-    tc_fence_before();
-    __syncthreads();
+    if (tid == 0) bulk_wait<0>();
+  } else if (warp < 4 + kMmaExLoaderWarps) {
+    // ---- loader warps: the delta tile once, then B chunks lw, lw + 2, ... ----
+    const int lw = warp - 4;
+    const T* wsrc = reinterpret_cast<const T*>(a.w);
+    const int n_items = kMmaTokens * cpr;
+    if (kpad != R) {
+      // the chunk that pads K to a multiple of 16 is zero in all operand tiles and never overwritten
+      for (int i = lw * 32 + lane; i < 3 * kMmaTokens; i += kMmaExLoaderWarps * 32) {
+        const int which = i / kMmaTokens, rr = i - which * kMmaTokens;
+        asm volatile("st.shared.v4.b32 [%0], {%1, %1, %1, %1};" ::"r"(d_smem + which * tile_bytes + cpr * kLbo + rr * 16),
+                     "r"(0u)
+                     : "memory");
+      }
+    }
+    for (int ch = lw, first = 1; ch < nch || first; ch += kMmaExLoaderWarps, first = 0) {
+      if (ch < nch) {
+        const int s = ch % kMmaExStages, use = ch / kMmaExStages;
+        if (use > 0 && !mbar_wait_timed(&ctl.b_empty[s], (use - 1) & 1)) {
+          ctl.bad = 1;
+          break;
+        }
+        const int o0 = o_begin + ch * kMmaOutChunk;
+        const uint32_t dst = b_smem + s * tile_bytes;
+        for (int q = lane; q < n_items; q += 32) {
+          const int row = q / cpr, c = q - row * cpr;
+          const uint32_t o = static_cast<uint32_t>(min(o0 + row, h_out - 1));
+          const uint32_t f = o * R + c * 8;
+          const uint32_t pr = f / S, col = f - pr * S;
+          cp_async16(dst + c * kLbo + row * 16, wsrc + s_row_off[pr - pr_first] + col);
+        }
+      }
+      if (first) {
+        pdl_wait();  // delta comes from the kernel before this one
+        const T* dsrc = reinterpret_cast<const T*>(pick3(a.delta, p));
+        for (int q = lw * 32 + lane; q < n_items; q += kMmaExLoaderWarps * 32) {
+          const int row = q / cpr, c = q - row * cpr;
+          const int64_t tok = t.first + min(row, t.n - 1);
+          cp_async16(d_smem + c * kLbo + row * 16, dsrc + tok * a.delta_stride + c * 8);
+        }
+      }
+      cp_async_wait_all();
+      fence_proxy_async();
+      __syncwarp();
+      if (lane == 0) {
+        if (first) mbar_arrive(&ctl.d_full);
+        if (ch < nch) mbar_arrive(&ctl.b_full[ch % kMmaExStages]);
+      }
+    }
+  } else {
+    // ---- MMA issue ----
+    if (lane == 0) {
+      bool ok = mbar_wait_timed(&ctl.d_full, 0);
+      for (int ch = 0; ch < nch && ok; ++ch) {
+        const int s = ch % kMmaExStages, use = ch / kMmaExStages, ab = ch & 1;
+        ok = mbar_wait_timed(&ctl.b_full[s], use & 1);
+        if (ok && ch >= 2) ok = mbar_wait_timed(&ctl.acc_empty[ab], ((ch >> 1) - 1) & 1);
+        if (!ok) break;
+        tc_fence_after();
+        const int ncols = min(kMmaOutChunk, o_end - (o_begin + ch * kMmaOutChunk));
+        const uint32_t idesc = umma_idesc<T>((ncols + 15) & ~15);
+        const uint32_t bs = b_smem + s * tile_bytes;
+        for (int ks = 0; ks < kpad / 16; ++ks) {
+          const uint64_t da = umma_smem_desc(d_smem + ks * 2 * kLbo, kLbo, 128);
+          const uint64_t db = umma_smem_desc(bs + ks * 2 * kLbo, kLbo, 128);
+          umma_f16(tmem + ab * kMmaOutChunk, da, db, idesc, ks > 0 ? 1u : 0u);
+        }
+        umma_commit(&ctl.b_empty[s]);
+        umma_commit(&ctl.acc_full[ab]);
+      }
+      if (!ok) ctl.bad = 1;
+    }
   }
-  cp_async_wait<0>();
-  if (!ok && tid == 0) set_status(a.status, SLORA_STATUS_TIMEOUT);
+
   tc_fence_before();
   __syncthreads();
+  if (ctl.bad != 0 && tid == 0) set_status(a.status, SLORA_STATUS_TIMEOUT);
   if (warp == 0) tmem_dealloc(tmem, kMmaExpandCols);
 }
 
