@@ -51,6 +51,12 @@ def parse_args():
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--cpu-seconds", type=float, default=10.0)
     ap.add_argument("--pool-rows", type=int, default=None)
+    ap.add_argument("--layers", type=int, default=None,
+                    help="override the model's layer count (small cases for profiling; not a benchmark number)")
+    ap.add_argument("--prefill", action="store_true",
+                    help="secondary line: the segment (prefill) API on long sequences, served by the tensor-core kernels")
+    ap.add_argument("--prefill-seqs", type=int, default=8)
+    ap.add_argument("--prefill-len", type=int, default=512)
     return ap.parse_args()
 
 
@@ -197,7 +203,7 @@ class Runner:
             ids, seg = build_batch(wl.spec, g)
             wl.ids, wl.segments = ids.to(device), seg
         self.wl = wl
-        self.L = wl.spec.layers
+        self.L = args.layers or wl.spec.layers
         self.P = args.phys_layers
         H, K = wl.spec.hidden, wl.spec.h_kv
         dt = wl.dtype
@@ -208,7 +214,7 @@ class Runner:
         self.ops = sl.LoraBatchOps(wl.a_start, wl.a_len, wl.a_loc, wl.a_scaling, wl.pools_a, wl.pools_b, wl.max_rank,
                                    use_pdl=not args.no_pdl)
         self.ops.prepare(wl.ids, use_plan=not args.no_plan)
-        self.launches_per_step = 4 * self.L
+        self.launches_per_step = 4 * self.L  # replaced by the library's own count of the first eager step
         self.graph = None
 
     def zero_outputs(self):
@@ -343,6 +349,85 @@ def e2e_measure(run, steps, warmup):
     return sum(times), h2d, d2h
 
 
+def prefill_bench(args, device, peak_gbs):
+    """Secondary workload: the reference's prefill entry points (lora_get_qkvo_fwd_shrink / _expand) over long
+    same-adapter sequences, S2-shaped (hidden 4096, ranks 8..64).  Sequences of 32 tokens or more run on the tensor
+    cores.  A step is q, k, v, o shrink + expand of every layer; prints its own JSON line."""
+    import slora_b200 as sl
+    from slora_b200.workloads import build_workload
+    peak, peak_kind = peak_gbs
+    P = args.phys_layers
+    wl = build_workload(3, device=device, phys_layers=P, pool_rows=args.pool_rows or 65536, decode_tokens=0,
+                        prefill=("seqs", args.prefill_seqs, args.prefill_len, args.prefill_len))
+    L, H, R = args.layers or wl.spec.layers, wl.spec.hidden, wl.max_rank
+    seg = wl.segments
+    b_start = torch.tensor([s for s, _, _ in seg], dtype=torch.int32, device=device)
+    b_len = torch.tensor([n for _, n, _ in seg], dtype=torch.int32, device=device)
+    req = torch.tensor([a for _, _, a in seg], dtype=torch.int64, device=device)
+    max_len = max(n for _, n, _ in seg)
+    delta = torch.zeros((wl.T, R), dtype=wl.dtype, device=device)
+    ys = [[torch.zeros((wl.T, H), dtype=wl.dtype, device=device) for _ in range(4)] for _ in range(P)]
+
+    def step():
+        for l in range(L):
+            p = l % P
+            for proj in range(4):
+                x = wl.x_o[p] if proj == 3 else wl.x_qkv[p]
+                sl.lora_get_qkvo_fwd_shrink(x, wl.pools_a[p], delta, wl.a_loc, wl.a_start, wl.a_len, b_start, b_len,
+                                            req, H, proj, R, max_len)
+                sl.lora_get_qkvo_fwd_expand(delta, wl.pools_b[p], ys[p][proj], wl.a_scaling, wl.a_loc, wl.a_start,
+                                            wl.a_len, b_start, b_len, req, H, proj, R, max_len)
+
+    before = sl.launch_counts()
+    step()
+    torch.cuda.synchronize()
+    after = sl.launch_counts()
+    per_step = {k: after[k] - before[k] for k in after}
+    graph = None
+    if not args.no_graph:
+        s = torch.cuda.Stream()
+        s.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(s):
+            step()
+        torch.cuda.current_stream().wait_stream(s)
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=s):
+            step()
+    run = graph.replay if graph is not None else step
+    for _ in range(max(args.warmup, 3)):
+        run()
+    torch.cuda.synchronize()
+    with ClockSampler(physical_gpu_index(device.index or 0)) as clocks:
+        t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        t0.record()
+        for _ in range(args.steps):
+            run()
+        t1.record()
+        torch.cuda.synchronize()
+    elapsed = t0.elapsed_time(t1) * 1e-3
+    es = 2
+    distinct = sorted(set(a for _, _, a in seg))
+    w_bytes = sum(wl.ranks[a] * 2 * H * es for a in distinct) * 4
+    act_bytes = wl.T * H * es * (2 + 8)  # x read for q/k/v and for o; y read and written for four projections
+    step_bytes = (w_bytes + act_bytes) * L
+    flops = sum(2 * n * wl.ranks[a] * 2 * H for _, n, a in seg) * 4 * L
+    gbs = step_bytes / (elapsed / args.steps) / 1e9
+    line = {"metric": "lora_prefill_tokens_per_s", "value": wl.T * args.steps / elapsed, "unit": "tokens/s",
+            "n_gpus": 1, "steps": args.steps, "warmup": max(args.warmup, 3),
+            "ms_per_step": elapsed / args.steps * 1e3, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "f16 in, f32 accumulate (tcgen05)", "data": "synthetic",
+            "config": {"workload": "cfg3-S2-prefill-segments", "sequences": len(seg), "tokens": wl.T, "layers": L,
+                       "hidden": H, "ranks": sorted(set(wl.ranks[a] for a in distinct)), "phys_layers": P,
+                       "graph": graph is not None},
+            "roofline": {"bound": "hbm", "achieved": gbs, "peak": peak, "unit": "GB/s", "frac": gbs / peak,
+                         "traffic": None, "peak_kind": peak_kind, "tflops": flops / (elapsed / args.steps) / 1e12,
+                         "kernel": "whole step (lora_shrink_mma_kernel + lora_expand_mma_kernel per projection)"},
+            "gpu_launches": sum(per_step.values()) * args.steps, "launches_per_step": per_step,
+            "clocks": clocks.summary()}
+    print(json.dumps(line), flush=True)
+
+
 def main():
     args = parse_args()
     if args.impl == "reference":
@@ -368,10 +453,15 @@ def main():
         return
 
     peak_gbs, peak_kind = load_peaks()
+    if args.prefill:
+        prefill_bench(args, device, peak_gbs=load_peaks())
+        return
     run = Runner(args, args.config, device, seed_shift=rank)
     wl = run.wl
+    before = sum(run.sl.launch_counts().values())
     run.step_eager()
     torch.cuda.synchronize()
+    run.launches_per_step = sum(run.sl.launch_counts().values()) - before
     run.ops.plan and run.ops.plan.check()
     if not args.no_graph:
         run.capture()
