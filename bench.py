@@ -100,7 +100,7 @@ class ClockSampler:
                         self.reasons.add(k)
             except Exception:
                 pass
-            time.sleep(0.02)
+            time.sleep(0.002)
 
     def __enter__(self):
         if self.nv is not None:
@@ -270,6 +270,12 @@ def _graph_time(fn, launches, iters=5):
     return e0.elapsed_time(e1) * 1e3 / iters / launches
 
 
+# dram__bytes_read.sum + dram__bytes_write.sum per launch from the ncu capture summarised in
+# profiles/lora_pipe_kernels_cfg2_decode.md (same batch and per-launch work as the benchmark's; y stays in L2 there)
+NCU_TRAFFIC = {(2, "lora_pipe_kernel<expand>(qkv)"): 32.76e6 + 0.016e6,
+               (2, "lora_pipe_kernel<shrink>(qkv)"): 28.54e6 + 0.002e6}
+
+
 def kernel_roofline(run, peak_gbs, peak_kind):
     """Average duration of the q/k/v expand launch (the largest kernel of the step) and of the q/k/v shrink launch:
     a CUDA graph holding one launch per layer of that kernel alone, CUDA-event timed."""
@@ -303,7 +309,8 @@ def kernel_roofline(run, peak_gbs, peak_kind):
     for name, t, nbytes in (("lora_pipe_kernel<expand>(qkv)", t_expand, b_bytes + y_bytes),
                             ("lora_pipe_kernel<shrink>(qkv)", t_shrink, a_bytes + x_bytes)):
         out[name] = {"bound": "hbm", "achieved": nbytes / t / 1e9, "peak": peak_gbs, "unit": "GB/s",
-                     "frac": nbytes / t / 1e9 / peak_gbs, "traffic": None, "kernel": name,
+                     "frac": nbytes / t / 1e9 / peak_gbs, "traffic": NCU_TRAFFIC.get((wl.spec.cfg, name)),
+                     "kernel": name,
                      "us_per_launch": t * 1e6, "algorithmic_bytes_per_launch": nbytes, "peak_kind": peak_kind,
                      "how": "CUDA graph of one launch per layer of this kernel alone, CUDA events around the replay"}
     return out

@@ -336,6 +336,9 @@ int run_shrink(const TileSrc& src, const Tables& tb, const void* w, const void* 
     }
     if (rc) return rc;
     a.src.seg_split = src.seg_split;
+    // the CUDA-core launch of the same call may start while the tensor-core kernel runs: neither writes what the
+    // other reads before its grid-dependency wait, and their outputs are disjoint
+    flags |= SLORA_FLAG_PDL;
   }
   const bool can_pipe = (S % h_in == 0);
   const KernelChoice choice = kernel_choice();
@@ -345,7 +348,7 @@ int run_shrink(const TileSrc& src, const Tables& tb, const void* w, const void* 
     a.rows_per_cta = kMaxRows;
     a.max_rb = (delta_width + kMaxRows - 1) / kMaxRows;
     const int64_t items = static_cast<int64_t>(src.slots) * nproj * a.max_rb;
-    const int64_t grid = items < sm_count() ? items : sm_count();
+    const int64_t grid = items < sm_count() * kPipeCtasPerSm ? items : sm_count() * kPipeCtasPerSm;
     const size_t smem = kRingBytes;
     if (dtype == SLORA_F16) {
       auto k = lora_shrink_pipe_kernel<__half>;
@@ -459,6 +462,7 @@ int run_expand(const TileSrc& src, const Tables& tb, const void* w, const void* 
     }
     if (rc) return rc;
     a.src.seg_split = src.seg_split;
+    flags |= SLORA_FLAG_PDL;  // as in the shrink: overlap the CUDA-core launch with the tensor-core kernel
   }
   const int pipe_piece = pow2_divisor(tb.pool_stride, kPipeChunk);
   bool can_pipe = delta_parts == 1 && delta_stride % 8 == 0 && pipe_piece * kMaxPieces >= kPipeChunk &&
@@ -472,7 +476,7 @@ int run_expand(const TileSrc& src, const Tables& tb, const void* w, const void* 
     a.piece = pipe_piece;
     set_chunks(kPipeChunk);
     const int64_t items = static_cast<int64_t>(src.slots) * a.chunk_begin[nproj];
-    const int64_t grid = items < sm_count() ? items : sm_count();
+    const int64_t grid = items < sm_count() * kPipeCtasPerSm ? items : sm_count() * kPipeCtasPerSm;
     const size_t smem = kRingBytes;
     if (dtype == SLORA_F16) {
       auto k = lora_expand_pipe_kernel<__half>;
