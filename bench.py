@@ -333,6 +333,12 @@ def e2e_measure(run, steps, warmup):
                           use_pdl=not run.args.no_pdl)
     h2d = x_host.numel() * x_host.element_size() + ids_host.numel() * 8
     d2h = y_host.numel() * y_host.element_size()
+    # Three streams: activations of layer l+1.. upload and deltas of layer l-1.. download while layer l computes
+    # (PCIe is full duplex), the way a serving loop would feed a layer-by-layer model.
+    cur = torch.cuda.current_stream()
+    s_in, s_out = torch.cuda.Stream(), torch.cuda.Stream()
+    ev_in = [torch.cuda.Event() for _ in range(L)]
+    ev_done = [torch.cuda.Event() for _ in range(L)]
     times = []
     for it in range(warmup + steps):
         y_dev.zero_()
@@ -340,15 +346,25 @@ def e2e_measure(run, steps, warmup):
         t0 = torch.cuda.Event(enable_timing=True)
         t1 = torch.cuda.Event(enable_timing=True)
         t0.record()
-        x_dev.copy_(x_host, non_blocking=True)
+        s_in.wait_stream(cur)
+        s_out.wait_stream(cur)
+        with torch.cuda.stream(s_in):
+            for l in range(L):
+                x_dev[l].copy_(x_host[l], non_blocking=True)
+                ev_in[l].record(s_in)
         ids_dev.copy_(ids_host, non_blocking=True)
         ops.prepare(ids_dev, use_plan=not run.args.no_plan)
         for l in range(L):
             p = l % run.P
             yl = y_dev[l]
+            cur.wait_event(ev_in[l])
             ops.lora_get_qkv(p, x_dev[l, 0], yl[:, :H], yl[:, H:H + K], yl[:, H + K:H + 2 * K])
             ops.lora_get_o(p, x_dev[l, 1], yl[:, H + 2 * K:])
-        y_host.copy_(y_dev, non_blocking=True)
+            ev_done[l].record(cur)
+            with torch.cuda.stream(s_out):
+                s_out.wait_event(ev_done[l])
+                y_host[l].copy_(yl, non_blocking=True)
+        cur.wait_stream(s_out)
         t1.record()
         torch.cuda.synchronize()
         if it >= warmup:

@@ -52,6 +52,15 @@ extern "C" {
                              kernel.  Safe whenever the previous kernels on the stream do not write the pool
                              buffers or the tables that this call reads. */
 
+#define SLORA_FLAG_BIG_GROUPS 2u /* planned calls (slora_batch_lora_*, slora_lora_*_multi with a plan): some adapter
+                                   has 128 or more tokens in the batch (slora_plan_big_tiles > 0, or the caller's
+                                   scheduler knows): such groups are computed on the tensor cores (tcgen05) in
+                                   tiles of 128 tokens by a second launch, the rest stays on the CUDA-core kernels.
+                                   Without the flag everything stays on the CUDA-core kernels.  Results of the two
+                                   paths differ in summation order and in the expand's rounding (the tensor-core
+                                   path rounds scale * sum to the I/O type and adds it to y in that type, as the
+                                   reference's kernels do). */
+
 /* Bits of the device status word (plan header / status argument). */
 #define SLORA_STATUS_BAD_ID 1      /* a token's adapter id was outside [0, n_adapters) - token skipped   */
 #define SLORA_STATUS_BAD_TABLE 2   /* start/ranks4/loc entry out of range - work item skipped            */
@@ -127,6 +136,13 @@ int slora_sgmv_expand(void* y, const void* delta, const void* w, const int64_t* 
 size_t slora_plan_workspace_bytes(int64_t T, int64_t n_adapters);
 int slora_plan_build(void* workspace, size_t workspace_bytes, const int64_t* ids, int64_t T, const int64_t* start,
                      const int64_t* ranks4, int64_t n_adapters, int64_t loc_len, void* stream);
+/*
+ * Number of 128-token tiles of big same-adapter groups in a plan (0: SLORA_FLAG_BIG_GROUPS would only add empty
+ * launches).  Reads the plan header back: synchronises `stream`.  No counterpart in the reference, which picks its
+ * prefill kernels on the host from the request lengths (lora_unordered_batch_infer.py:127-130).
+ */
+int slora_plan_big_tiles(const void* workspace, int* n_big_out, void* stream);
+
 int slora_plan_status(const void* workspace, int* status_out, int* n_tiles_out, void* stream);
 
 /*

@@ -15,6 +15,7 @@ LIB_PATH = os.path.join(_HERE, "libslora_b200.so")
 
 F16, BF16 = 0, 1
 FLAG_PDL = 1
+FLAG_BIG_GROUPS = 2
 
 STATUS_BITS = {1: "bad adapter id", 2: "bad table entry", 4: "unsupported rank", 8: "bulk-copy wait timed out"}
 
@@ -64,6 +65,7 @@ _SIGS = {
                                            _P, _P, c_int64, c_int64, c_int, c_int64, c_int, c_uint, _P]),
     "slora_validate_tables": (c_int, [_P, _P, _P, _P, c_int64, c_int64, c_int64, c_int64, _P, _P]),
     "slora_launch_counts": (None, [_P]),
+    "slora_plan_big_tiles": (c_int, [_P, _P, _P]),
 }
 
 EXPORTS = tuple(_SIGS)

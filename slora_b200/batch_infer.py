@@ -53,6 +53,12 @@ class BatchPlan:
                                               _lib.current_stream_ptr()))
         return st.value, nt.value
 
+    def big_tiles(self) -> int:
+        """Number of 128-token tiles of adapters with 128 or more tokens in the batch -- synchronises the stream."""
+        n = ctypes.c_int(0)
+        _lib.check(_lib.lib.slora_plan_big_tiles(self.ptr, ctypes.byref(n), _lib.current_stream_ptr()))
+        return n.value
+
     def check(self):
         st, _ = self.status()
         if st:
@@ -73,7 +79,8 @@ class LoraBatchOps:
         self.a_start, self.a_len, self.a_loc, self.a_scaling = a_start, a_len, a_loc, a_scaling
         self.key_buffer, self.value_buffer = key_buffer, value_buffer
         self.max_lora_dim = int(max_lora_dim)
-        self.flags = _lib.FLAG_PDL if use_pdl else 0
+        self.base_flags = _lib.FLAG_PDL if use_pdl else 0
+        self.flags = self.base_flags
         self.plan = None
         self.delta = None
 
@@ -83,17 +90,28 @@ class LoraBatchOps:
         return cls(infer_adapter.a_start, infer_adapter.a_len, infer_adapter.a_loc, infer_adapter.a_scaling,
                    mm.key_buffer, mm.value_buffer, max_lora_dim, use_pdl)
 
-    def prepare(self, token_adapter_ids, use_plan=True):
+    def prepare(self, token_adapter_ids, use_plan=True, big_groups=None):
         """Start a forward: ``token_adapter_ids`` is ``req_bins`` (decode) or ``batch_req_bins`` (prefill).
 
         Allocates the three delta buffers the reference allocates in ``forward`` (``:68-69,75-76``) and builds the
         plan.  ``use_plan=False`` keeps every token its own group (the reference's behaviour).
+
+        ``big_groups``: does some adapter have 128 or more tokens in this batch (a prefill batch)?  Such groups run
+        on the tensor cores.  The reference decides the same way on the host (``:127-130``: Triton kernels when
+        ``max_len_in_batch >= 200``).  ``None`` asks the plan (one 64-byte read-back and a stream synchronisation,
+        only for batches of 128 tokens or more); a scheduler that knows its batch passes ``True`` / ``False``.
         """
         self.ids = token_adapter_ids.contiguous()
         T = self.ids.numel()
         dtype = self.key_buffer[0].dtype
         self.delta = [torch.zeros((T, self.max_lora_dim), dtype=dtype, device=self.ids.device) for _ in range(3)]
         self.plan = BatchPlan(self.ids, self.a_start, self.a_len, self.a_loc.numel()) if use_plan else None
+        self.flags = self.base_flags
+        if self.plan is not None and T >= 128:
+            if big_groups is None:
+                big_groups = self.plan.big_tiles() > 0
+            if big_groups:
+                self.flags |= _lib.FLAG_BIG_GROUPS
         return self
 
     def _common(self, layer_id):

@@ -18,12 +18,19 @@ constexpr int kChunk = 8192;    // flat B elements per expand work item (16 KB)
 constexpr uint32_t kSpinLimit = 1u << 18;
 
 // ---- batch plan workspace (int32 words) --------------------------------------------------------------------
-//   [header PH_WORDS][tile records 8 * max_tiles][perm T][pos T][cnt n_adapters]
-// tile record: {adapter, first slot in perm, tokens (0 = skip), slot_rows r, first loc entry, 0, 0, 0}
-constexpr int PH_MAGIC = 0, PH_NTILES = 1, PH_STATUS = 2, PH_MAXTILES = 3, PH_T = 4, PH_NADAPTERS = 5;
+//   [header PH_WORDS][tile records 8 * max_tiles][perm T][pos T][cnt n_adapters][big-tile records 8 * max_big]
+// tile record: {adapter, first slot in perm, tokens (0 = skip), slot_rows r, first loc entry, big, 0, 0}
+//   big = 1 when the tile's adapter has kBigGroupTokens tokens or more in the batch and 8..128 slot rows (a multiple
+//   of 8): such groups are also listed as big tiles of up to 128 tokens for the tensor-core kernels
+// big-tile record: {adapter, first slot in perm, tokens, slot_rows r, first loc entry, 0, 0, 0}
+constexpr int PH_MAGIC = 0, PH_NTILES = 1, PH_STATUS = 2, PH_MAXTILES = 3, PH_T = 4, PH_NADAPTERS = 5, PH_NBIG = 6,
+              PH_BIGOFF = 7, PH_MAXBIG = 8;
+constexpr int kBigGroupTokens = 128;  // planned batches: same-adapter groups at least this long go to the tensor cores
+constexpr int kBigSegmentTokens = 32;  // segment calls: segments at least this long do
+constexpr int kBigTileTokens = 128;
 constexpr int PH_WORDS = 16;
 constexpr int kTileWords = 8;
-constexpr int32_t kPlanMagic = 0x534c5032;  // "SLP2"
+constexpr int32_t kPlanMagic = 0x534c5033;  // "SLP3"
 
 enum TileMode { MODE_TOKEN = 0, MODE_PLAN = 1, MODE_SEGMENT = 2 };
 
@@ -36,8 +43,9 @@ struct TileSrc {
   int n_seg;
   int tiles_per_seg;
   int slots;  // tile slots the launch enumerates (upper bound of the number of tiles)
-  int seg_split;          // SEGMENT: > 0 when segments at least this long go to the tensor-core kernels
+  int seg_split;          // > 0 when segments (SEGMENT) / groups (PLAN) at least this long go to the tensor-core kernels
   int mma_tiles_per_seg;  // SEGMENT: 128-token tiles enumerated per segment by the tensor-core kernels
+  int big_slots;          // PLAN: big-tile slots the tensor-core launch enumerates
   int64_t T;
 };
 
@@ -251,6 +259,8 @@ __device__ __forceinline__ bool lookup_tile(const TileSrc& s, const Tables& tb, 
     t.r = r0.w;
     t.loc_base = r1.x;
     t.perm = s.plan + PH_WORDS + kTileWords * hdr[PH_MAXTILES];
+    // big groups an eligible layout lets the tensor-core kernels serve are theirs (same predicate as mma_serves)
+    if (s.seg_split > 0 && r1.y != 0 && tb.pool_stride % t.r == 0) return false;
     return t.n > 0 && t.r > 0;
   }
   int64_t adapter;

@@ -89,15 +89,20 @@ int max_tiles_for(int64_t T, int64_t n_adapters) {
   return static_cast<int>((T + kTileTokens - 1) / kTileTokens + groups);
 }
 
+// Big-tile slots a plan can need: a big group has c >= kBigGroupTokens tokens and ceil(c / 128) <= 2c / 128 tiles.
+int max_big_for(int64_t T) { return static_cast<int>(2 * T / kBigGroupTokens + 1); }
+
 struct PlanLayout {
   int max_tiles;
+  int max_big;
   size_t words;
 };
 PlanLayout plan_layout(int64_t T, int64_t n_adapters) {
   PlanLayout l;
   l.max_tiles = max_tiles_for(T, n_adapters);
+  l.max_big = max_big_for(T);
   l.words = static_cast<size_t>(PH_WORDS) + static_cast<size_t>(kTileWords) * l.max_tiles + 2u * static_cast<size_t>(T) +
-            static_cast<size_t>(n_adapters) + 4;
+            static_cast<size_t>(n_adapters) + 4 + static_cast<size_t>(kTileWords) * l.max_big;
   return l;
 }
 
@@ -306,8 +311,8 @@ int run_shrink(const TileSrc& src, const Tables& tb, const void* w, const void* 
   a.status = status;
   // long segments first go to the tensor-core kernel; the launch below then skips them
   a.src.seg_split = 0;
-  if (src.mode == MODE_SEGMENT && src.seg_split > 0 && mma_enabled() && S == h_in && h_in % kMmaKBlock == 0 &&
-      src.T < 0x7fffffff) {
+  if ((src.mode == MODE_SEGMENT || src.mode == MODE_PLAN) && src.seg_split > 0 && mma_enabled() && S == h_in &&
+      h_in % kMmaKBlock == 0 && src.T < 0x7fffffff) {
     bool consecutive = true;
     for (int p = 1; p < nproj; ++p) consecutive = consecutive && qkvo[p] == qkvo[0] + p;
     const int wmax = delta_width < kMmaMaxRank ? delta_width : kMmaMaxRank;
@@ -321,7 +326,8 @@ int run_shrink(const TileSrc& src, const Tables& tb, const void* w, const void* 
     m.mma_stages = (kMmaSmemBudget - 1024) / m.mma_stage_bytes;
     if (m.mma_stages > kMmaMaxStages) m.mma_stages = kMmaMaxStages;
     const size_t smem = static_cast<size_t>(m.mma_stages) * m.mma_stage_bytes + 1024;
-    const int64_t grid = static_cast<int64_t>(src.n_seg) * src.mma_tiles_per_seg * m.max_rb;
+    const int64_t mma_tiles = src.mode == MODE_PLAN ? src.big_slots : static_cast<int64_t>(src.n_seg) * src.mma_tiles_per_seg;
+    const int64_t grid = mma_tiles * m.max_rb;
     CUtensorMap x_map;
     rc = make_tmap(&x_map, dtype, x, h_in, src.T, x_stride, kMmaTokens);
     if (rc) return rc;
@@ -430,8 +436,8 @@ int run_expand(const TileSrc& src, const Tables& tb, const void* w, const void* 
   a.rank_mult = rank_mult;
   a.status = status;
   a.src.seg_split = 0;
-  bool can_mma = src.mode == MODE_SEGMENT && src.seg_split > 0 && mma_enabled() && delta_parts == 1 &&
-                 rank_mult == 1 && delta_stride % 8 == 0;
+  bool can_mma = (src.mode == MODE_SEGMENT || src.mode == MODE_PLAN) && src.seg_split > 0 && mma_enabled() &&
+                 delta_parts == 1 && rank_mult == 1 && delta_stride % 8 == 0;
   for (int p = 0; p < nproj; ++p)
     can_mma = can_mma && aligned16(y[p]) && y_stride[p] % 8 == 0 && aligned16(delta[p]);
   for (int p = 0; p < nproj; ++p) can_mma = can_mma && h_out[p] >= 64;
@@ -445,7 +451,8 @@ int run_expand(const TileSrc& src, const Tables& tb, const void* w, const void* 
     const int wmax = delta_width < kMmaMaxRank ? delta_width : kMmaMaxRank;
     m.mma_stage_bytes = kMmaTokens * ((wmax + 15) & ~15) * 2;
     const size_t smem = kMmaOutTileBytes + static_cast<size_t>(1 + kMmaExStages) * m.mma_stage_bytes + 1024;
-    const int64_t grid = static_cast<int64_t>(src.n_seg) * src.mma_tiles_per_seg * m.chunk_begin[nproj];
+    const int64_t mma_tiles = src.mode == MODE_PLAN ? src.big_slots : static_cast<int64_t>(src.n_seg) * src.mma_tiles_per_seg;
+    const int64_t grid = mma_tiles * m.chunk_begin[nproj];
     TmapSet y_maps;
     memset(&y_maps, 0, sizeof(y_maps));
     for (int p = 0; p < nproj && !rc; ++p)
@@ -494,7 +501,8 @@ int run_expand(const TileSrc& src, const Tables& tb, const void* w, const void* 
   return launch(lora_expand_kernel<__nv_bfloat16>, grid, kThreads, 0, flags, stream, a, "expand");
 }
 
-int make_src(const void* plan, const int64_t* ids, int64_t T, int64_t n_adapters, TileSrc* src, int32_t** status) {
+int make_src(const void* plan, const int64_t* ids, int64_t T, int64_t n_adapters, unsigned flags, TileSrc* src,
+             int32_t** status) {
   memset(src, 0, sizeof(*src));
   src->T = T;
   *status = nullptr;
@@ -504,6 +512,8 @@ int make_src(const void* plan, const int64_t* ids, int64_t T, int64_t n_adapters
     src->mode = MODE_PLAN;
     src->plan = reinterpret_cast<const int32_t*>(plan);
     src->slots = max_tiles_for(T, n_adapters);
+    src->big_slots = max_big_for(T);
+    src->seg_split = ((flags & SLORA_FLAG_BIG_GROUPS) && T >= kBigGroupTokens) ? kBigGroupTokens : 0;
     *status = const_cast<int32_t*>(src->plan) + PH_STATUS;
   } else {
     if (!ids && T > 0) return fail(SLORA_ERR_NULL, "neither plan nor ids given");
@@ -568,7 +578,7 @@ int slora_bgmv_shrink(void* delta, const void* x, const void* w, const int64_t* 
                       int64_t n_adapters, int64_t loc_len, int dtype, void* stream) {
   TileSrc src;
   int32_t* status;
-  int rc = make_src(nullptr, ids, T, n_adapters, &src, &status);
+  int rc = make_src(nullptr, ids, T, n_adapters, 0, &src, &status);
   if (rc) return rc;
   void* d[1] = {delta};
   const int q[1] = {qkvo};
@@ -583,7 +593,7 @@ int slora_bgmv_expand(void* y, const void* delta, const void* w, const int64_t* 
                       int64_t pool_stride, int64_t n_adapters, int64_t loc_len, int dtype, void* stream) {
   TileSrc src;
   int32_t* status;
-  int rc = make_src(nullptr, ids, T, n_adapters, &src, &status);
+  int rc = make_src(nullptr, ids, T, n_adapters, 0, &src, &status);
   if (rc) return rc;
   void* yy[1] = {y};
   const void* d[1] = {delta};
@@ -661,9 +671,20 @@ int slora_plan_build(void* workspace, size_t workspace_bytes, const int64_t* ids
                 l.words * sizeof(int32_t));
   plan_build_kernel<<<1, 1024, 0, static_cast<cudaStream_t>(stream)>>>(
       reinterpret_cast<int32_t*>(workspace), ids, start, ranks4, loc_len, static_cast<int>(T),
-      static_cast<int>(n_adapters), l.max_tiles);
+      static_cast<int>(n_adapters), l.max_tiles, l.max_big);
   plan_fence_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>();
   return check_launch("plan_build", 2);
+}
+
+int slora_plan_big_tiles(const void* workspace, int* n_big_out, void* stream) {
+  if (!workspace || !n_big_out) return fail(SLORA_ERR_NULL, "workspace or n_big_out is null");
+  int32_t hdr[PH_WORDS];
+  cudaError_t e = cudaMemcpyAsync(hdr, workspace, sizeof(hdr), cudaMemcpyDeviceToHost, static_cast<cudaStream_t>(stream));
+  if (e == cudaSuccess) e = cudaStreamSynchronize(static_cast<cudaStream_t>(stream));
+  if (e != cudaSuccess) return fail(SLORA_ERR_LAUNCH, "plan_big_tiles: %s", cudaGetErrorString(e));
+  if (hdr[PH_MAGIC] != kPlanMagic) return fail(SLORA_ERR_WORKSPACE, "workspace does not hold a plan");
+  *n_big_out = hdr[PH_NBIG];
+  return SLORA_OK;
 }
 
 int slora_plan_status(const void* workspace, int* status_out, int* n_tiles_out, void* stream) {
@@ -686,7 +707,7 @@ int slora_lora_shrink_multi(const void* plan, const int64_t* ids, int nproj, con
   if (!qkvo || !delta) return fail(SLORA_ERR_NULL, "qkvo or delta array is null");
   TileSrc src;
   int32_t* status;
-  int rc = make_src(plan, ids, T, n_adapters, &src, &status);
+  int rc = make_src(plan, ids, T, n_adapters, flags, &src, &status);
   if (rc) return rc;
   return run_shrink(src, make_tables(start, ranks4, loc, n_adapters, loc_len, pool_rows, pool_stride), pool_a, x,
                     x_stride, h_in, nproj, qkvo, delta, delta_stride, delta_width, dtype, flags, status,
@@ -703,7 +724,7 @@ int slora_lora_expand_multi(const void* plan, const int64_t* ids, int nproj, con
   if (!qkvo || !y || !y_stride || !h_out || !delta) return fail(SLORA_ERR_NULL, "null argument array");
   TileSrc src;
   int32_t* status;
-  int rc = make_src(plan, ids, T, n_adapters, &src, &status);
+  int rc = make_src(plan, ids, T, n_adapters, flags, &src, &status);
   if (rc) return rc;
   return run_expand(src, make_tables(start, ranks4, loc, n_adapters, loc_len, pool_rows, pool_stride), pool_b,
                     scales, nproj, qkvo, y, y_stride, h_out, delta, delta_stride, delta_width, delta_parts,

@@ -34,7 +34,7 @@ namespace slora {
 
 constexpr int kMmaTokens = 128;    // tokens per tile = M of one tcgen05.mma
 constexpr int kMmaKBlock = 64;     // K elements per pipeline stage of the shrink (one 128-byte swizzle span)
-constexpr int kMmaMinTokens = 32;  // segments at least this long are served here
+constexpr int kMmaMinTokens = kBigSegmentTokens;  // segments at least this long are served here
 constexpr int kMmaMaxRows = 256;   // adapter rows one shrink CTA multiplies by (N of the instruction)
 constexpr int kMmaMaxRank = 128;
 constexpr int kMmaMaxStages = 8;
@@ -47,7 +47,8 @@ constexpr int kMmaOutPerCta = 512;  // outputs one expand CTA walks through
 constexpr int kMmaExLoaderWarps = 2;
 constexpr int kMmaExStages = 2;
 constexpr int kMmaExpandThreads = (4 + kMmaExLoaderWarps + 1) * 32;
-constexpr int kMmaOutTileBytes = kMmaTokens * kMmaOutChunk * 2;  // 32 KB: two swizzled halves of 64 columns
+constexpr int kMmaOutRowPitch = kMmaOutChunk * 2 + 16;  // gathered tokens: one padded row per token (no bank conflicts)
+constexpr int kMmaOutTileBytes = 35 * 1024;  // two swizzled 16 KB halves of 64 columns, or 128 rows of kMmaOutRowPitch
 constexpr int kMmaExpandCols = 256;                              // two accumulators of 128 columns
 
 // Tensor maps of the y buffers of one expand call.
@@ -140,6 +141,22 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map
       "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar)), "r"(x), "r"(y)
       : "memory");
 }
+// Bulk reduce of one contiguous run: global[i] += shared[i] for `bytes` bytes of T elements (both addresses 16-byte
+// aligned, bytes a multiple of 16); completion is tracked by the issuing thread's bulk group.
+template <typename T>
+__device__ __forceinline__ void bulk_reduce_add(void* dst, uint32_t src, uint32_t bytes);
+template <>
+__device__ __forceinline__ void bulk_reduce_add<__half>(void* dst, uint32_t src, uint32_t bytes) {
+  asm volatile("cp.reduce.async.bulk.global.shared::cta.bulk_group.add.noftz.f16 [%0], [%1], %2;" ::"l"(dst), "r"(src),
+               "r"(bytes)
+               : "memory");
+}
+template <>
+__device__ __forceinline__ void bulk_reduce_add<__nv_bfloat16>(void* dst, uint32_t src, uint32_t bytes) {
+  asm volatile("cp.reduce.async.bulk.global.shared::cta.bulk_group.add.noftz.bf16 [%0], [%1], %2;" ::"l"(dst), "r"(src),
+               "r"(bytes)
+               : "memory");
+}
 // TMA tile reduce: global[tile] += shared[tile], element-wise in the tensor map's type.
 __device__ __forceinline__ void tma_reduce_add_2d(const CUtensorMap* map, int x, int y, uint32_t src) {
   asm volatile("cp.reduce.async.bulk.tensor.2d.global.shared::cta.add.bulk_group [%0, {%2, %3}], [%1];" ::"l"(
@@ -187,11 +204,18 @@ __device__ __forceinline__ uint64_t umma_smem_desc_sw128(uint32_t addr) {
 // ---- tiles ----------------------------------------------------------------------------------------------------
 struct MmaTile {
   int adapter;
-  int first;  // first token of the tile
+  int first;  // first token of the tile (segments) or first slot in perm (plan)
   int n;      // tokens, 1..kMmaTokens
   int r;      // slot rows of the adapter
   int64_t loc_base;
+  const int32_t* perm;  // plan only: token of slot i is perm[first + i]; null when the tile's tokens are consecutive
 };
+
+// Token index of row `i` of a tile (rows beyond the tile's tokens repeat its last token).
+__device__ __forceinline__ int64_t mma_token(const MmaTile& t, int i) {
+  const int j = t.first + min(i, t.n - 1);
+  return t.perm ? t.perm[j] : j;
+}
 
 // May the tensor-core kernels take a segment of `len` tokens whose adapter has `r` slot rows?  The CUDA-core kernels
 // skip exactly the segments for which this holds (TileSrc::seg_split > 0), so the two launches partition the work.
@@ -201,6 +225,22 @@ __device__ __forceinline__ bool mma_serves(const TileSrc& s, const Tables& tb, i
 
 __device__ __forceinline__ bool lookup_mma_tile(const TileSrc& s, const Tables& tb, int tile_idx, MmaTile& t,
                                                 int32_t* status) {
+  if (s.mode == MODE_PLAN) {
+    // big-tile records were validated by the plan builder
+    const int32_t* hdr = s.plan;
+    if (s.seg_split <= 0 || tile_idx >= hdr[PH_NBIG]) return false;
+    const int4* rec = reinterpret_cast<const int4*>(s.plan + hdr[PH_BIGOFF] + kTileWords * tile_idx);
+    const int4 r0 = rec[0];
+    const int4 r1 = rec[1];
+    t.adapter = r0.x;
+    t.first = r0.y;
+    t.n = r0.z;
+    t.r = r0.w;
+    t.loc_base = r1.x;
+    t.perm = s.plan + PH_WORDS + kTileWords * hdr[PH_MAXTILES];
+    return t.n > 0 && t.r > 0 && tb.pool_stride % t.r == 0;
+  }
+  t.perm = nullptr;
   const int seg = tile_idx / s.mma_tiles_per_seg;
   const int sub = tile_idx - seg * s.mma_tiles_per_seg;
   if (seg >= s.n_seg) return false;
@@ -234,12 +274,14 @@ __device__ __forceinline__ bool lookup_mma_tile(const TileSrc& s, const Tables& 
 //   [x tile 128 x 64, swizzled][adapter rows npad_max x 64, core-matrix layout]
 // ------------------------------------------------------------------------------------------------------------
 struct ShrinkMmaCtl {
-  uint64_t full[kMmaMaxStages];   // 2 arrivals: the stage's loader warp, the activation TMA (with its bytes)
+  uint64_t full[kMmaMaxStages];   // arrivals: the stage's loader warp and, for consecutive tokens, the activation
+                                  // TMA (with its bytes); gathered tokens are copied by the loader warp itself
   uint64_t empty[kMmaMaxStages];  // 1 arrival: tcgen05.commit after the stage's MMAs
   uint64_t acc_done;
   uint32_t tmem;
   int bad;
   int64_t row_off[kMmaMaxRows];  // element offset of each adapter row in the pool
+  int64_t tok_off[kMmaTokens];   // gathered tokens: element offset of each token row in x
 };
 
 template <typename T>
@@ -273,6 +315,10 @@ __global__ void __launch_bounds__(kMmaShrinkThreads, 1)
     if (e < 0 || e >= a.tb.pool_rows) rows_ok = false;
     ctl.row_off[j] = e * S;
   }
+  const bool gather = t.perm != nullptr;
+  if (gather) {
+    for (int i = tid; i < kMmaTokens; i += kMmaShrinkThreads) ctl.tok_off[i] = mma_token(t, i) * a.x_stride;
+  }
   if (!__syncthreads_and(rows_ok)) {
     if (tid == 0) set_status(a.status, SLORA_STATUS_BAD_TABLE);
     return;
@@ -284,7 +330,7 @@ __global__ void __launch_bounds__(kMmaShrinkThreads, 1)
   const int nkb = a.h_in / kMmaKBlock;
   if (tid == 0) {
     for (int s = 0; s < nst; ++s) {
-      mbar_init(&ctl.full[s], 2);
+      mbar_init(&ctl.full[s], gather ? 1 : 2);
       mbar_init(&ctl.empty[s], 1);
     }
     mbar_init(&ctl.acc_done, 1);
@@ -308,13 +354,29 @@ __global__ void __launch_bounds__(kMmaShrinkThreads, 1)
     if (warp < nst) {
       const int row_lo = lane & 7, c_lo = lane >> 3;
       const T* w = reinterpret_cast<const T*>(a.w);
+      const T* x = reinterpret_cast<const T*>(a.x);
       const uint32_t dst0 = smem0 + warp * stage_bytes + kMmaXTileBytes + row_lo * 16;
+      if (gather) pdl_wait();  // this warp reads the activations itself
       for (int kb = warp, use = 0; kb < nkb; kb += nst, ++use) {
         if (use > 0 && !mbar_wait_timed(&ctl.empty[warp], (use - 1) & 1)) {
           ctl.bad = 1;
           break;
         }
         const int k0 = kb * kMmaKBlock;
+        if (gather) {
+          // token rows into the 128-byte swizzled layout the TMA would have produced: chunk c of row i at
+          // i * 128 + ((c ^ (i & 7)) << 4)
+          const uint32_t xdst = smem0 + warp * stage_bytes;
+          for (int rg = 0; rg < kMmaTokens; rg += 8) {
+            const int row = rg + row_lo;
+            const T* src = x + ctl.tok_off[row] + k0;
+#pragma unroll
+            for (int ch = 0; ch < 2; ++ch) {
+              const int c = ch * 4 + c_lo;
+              cp_async16(xdst + row * 128 + ((c ^ row_lo) << 4), src + c * 8);
+            }
+          }
+        }
         for (int rg = 0; rg < npad; rg += 8) {
           const T* src = w + ctl.row_off[rg + row_lo] + k0;
 #pragma unroll
@@ -330,8 +392,8 @@ __global__ void __launch_bounds__(kMmaShrinkThreads, 1)
       }
     }
   } else if (warp == kMmaLoaderWarps) {
-    // ---- activation tiles by TMA ----
-    if (lane == 0) {
+    // ---- activation tiles by TMA (consecutive tokens only) ----
+    if (lane == 0 && !gather) {
       pdl_wait();  // activations come from the kernel before this one
       for (int kb = 0; kb < nkb; ++kb) {
         const int s = kb % nst, use = kb / nst;
@@ -377,7 +439,7 @@ __global__ void __launch_bounds__(kMmaShrinkThreads, 1)
   if (ok && warp < 4) {
     const int row = warp * 32 + lane;
     const bool live = row < t.n;
-    const int64_t tok = t.first + (live ? row : 0);
+    const int64_t tok = mma_token(t, live ? row : 0);
     bool vec = (a.delta_stride % 8 == 0);
     for (int q = 0; q < gp; ++q) vec = vec && ((reinterpret_cast<uintptr_t>(pick3(a.delta, p0 + q)) & 15) == 0);
     int p = 0, jj = 0;  // column j = p * r + jj; r is a multiple of 8
@@ -516,11 +578,14 @@ __global__ void __launch_bounds__(kMmaExpandThreads)
   const uint32_t tmem = ctl.tmem;
 
   if (warp < 4) {
-    // ---- epilogue: scale, round, stage in shared memory, add into y with a TMA reduce ----
+    // ---- epilogue: scale, round, stage in shared memory, add into y with a TMA reduce (consecutive tokens: one
+    // tile reduce per 64 columns; gathered tokens: one bulk reduce per token row, issued by the row's own thread) ----
     const float scale = to_f32<T>(reinterpret_cast<const T*>(a.scales)[t.adapter]);
     const int row = warp * 32 + lane;
     const bool live = row < t.n;
+    const bool gather = t.perm != nullptr;
     const CUtensorMap* ymap = &y_maps.m[p];
+    T* yrow = reinterpret_cast<T*>(pick3(a.y, p)) + mma_token(t, live ? row : 0) * pick3(a.y_stride, p);
     pdl_wait();  // y is also written by the kernel before this one
     for (int ch = 0; ch < nch; ++ch) {
       const int ab = ch & 1;
@@ -528,7 +593,7 @@ __global__ void __launch_bounds__(kMmaExpandThreads)
       const int ncols = min(kMmaOutChunk, o_end - o0);  // a multiple of 8
       const int npad = (ncols + 15) & ~15;
       // the previous chunk's reduce must have finished reading the out tile
-      if (tid == 0) bulk_wait_read<0>();
+      if (gather || tid == 0) bulk_wait_read<0>();
       const bool got = mbar_wait_timed(&ctl.acc_full[ab], (ch >> 1) & 1);
       // all four warps go on, or leave, together
       if (!named_and(128, got)) {
@@ -554,7 +619,9 @@ __global__ void __launch_bounds__(kMmaExpandThreads)
               pk.e[e] = from_f32<T>(live ? scale * __uint_as_float(v[h * 8 + e]) : 0.f);
             const int col = g * 16 + h * 8;  // column of the 128-wide tile; half = col / 64
             const uint32_t cc = static_cast<uint32_t>((col & 63) >> 3);
-            const uint32_t dst = out_tile + (col >> 6) * (kMmaTokens * 128) + row * 128 + ((cc ^ (row & 7)) << 4);
+            const uint32_t dst =
+                gather ? out_tile + row * kMmaOutRowPitch + col * 2
+                       : out_tile + (col >> 6) * (kMmaTokens * 128) + row * 128 + ((cc ^ (row & 7)) << 4);
             asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(pk.q4.x), "r"(pk.q4.y),
                          "r"(pk.q4.z), "r"(pk.q4.w)
                          : "memory");
@@ -565,14 +632,20 @@ __global__ void __launch_bounds__(kMmaExpandThreads)
       __syncwarp();
       if (lane == 0) mbar_arrive(&ctl.acc_empty[ab]);
       fence_proxy_async();
-      named_sync(128);
-      if (tid == 0) {
-        for (int half = 0; half * 64 < ncols; ++half)
-          tma_reduce_add_2d(ymap, o0 + half * 64, t.first, out_tile + half * (kMmaTokens * 128));
+      if (gather) {
+        // each thread adds the row it wrote itself: no barrier needed
+        if (live) bulk_reduce_add<T>(yrow + o0, out_tile + row * kMmaOutRowPitch, static_cast<uint32_t>(ncols) * 2);
         bulk_commit();
+      } else {
+        named_sync(128);
+        if (tid == 0) {
+          for (int half = 0; half * 64 < ncols; ++half)
+            tma_reduce_add_2d(ymap, o0 + half * 64, t.first, out_tile + half * (kMmaTokens * 128));
+          bulk_commit();
+        }
       }
     }
-    if (tid == 0) bulk_wait<0>();
+    if (gather || tid == 0) bulk_wait<0>();
   } else if (warp < 4 + kMmaExLoaderWarps) {
     // ---- loader warps: the delta tile once, then B chunks lw, lw + 2, ... ----
     const int lw = warp - 4;
@@ -609,8 +682,7 @@ __global__ void __launch_bounds__(kMmaExpandThreads)
         const T* dsrc = reinterpret_cast<const T*>(pick3(a.delta, p));
         for (int q = lw * 32 + lane; q < n_items; q += kMmaExLoaderWarps * 32) {
           const int row = q / cpr, c = q - row * cpr;
-          const int64_t tok = t.first + min(row, t.n - 1);
-          cp_async16(d_smem + c * kLbo + row * 16, dsrc + tok * a.delta_stride + c * 8);
+          cp_async16(d_smem + c * kLbo + row * 16, dsrc + mma_token(t, row) * a.delta_stride + c * 8);
         }
       }
       cp_async_wait_all();

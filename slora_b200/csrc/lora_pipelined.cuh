@@ -36,13 +36,19 @@
 namespace slora {
 
 constexpr int kSlots = 8;  // stage descriptors (barrier pairs) in flight
-constexpr int kRingBytes = 96 * 1024;  // ring + control block stay below half an SM's shared memory
+#ifndef SLORA_RING_KB
+#define SLORA_RING_KB 96
+#endif
+#ifndef SLORA_STAGE_KB
+#define SLORA_STAGE_KB 48
+#endif
+constexpr int kRingBytes = SLORA_RING_KB * 1024;  // ring + control block stay below half an SM's shared memory
 constexpr int kPipeCtasPerSm = 2;      // persistent CTAs per SM
 constexpr int kPendSlots = 4;           // stages that may be issued before the grid-dependency wait
 constexpr int kProducerWarps = 1;  // stage g is fed by producer warp g % kProducerWarps
 constexpr int kConsumerWarps = 8;
 constexpr int kPipeThreads = 32 * (kProducerWarps + kConsumerWarps);
-constexpr int kMaxStageBytes = 48 * 1024;  // a shrink item is cut into K-chunks no larger than this
+constexpr int kMaxStageBytes = SLORA_STAGE_KB * 1024;  // a shrink item is cut into K-chunks no larger than this
 constexpr int kPipeChunk = 16384;          // flat B elements per expand item (32 KB)
 constexpr int kMaxPieces = 16;  // B copies per expand stage (lanes 0..15); y copies use lanes 16..23, delta 24..31
 constexpr int kSpanRows = 6;    // pool rows a B chunk may touch

@@ -6,19 +6,22 @@
 namespace slora {
 
 // workspace words: [header PH_WORDS][tile records kTileWords * max_tiles][perm T][pos T][cnt n_adapters]
+//                  [big-tile records kTileWords * max_big]
 // Counting sort by adapter id: histogram, exclusive scan over adapters (tokens and tiles at once), scatter.
 // Tokens whose id is outside [0, n_adapters) are left out and SLORA_STATUS_BAD_ID is recorded; adapters whose
 // table entries are out of range get tiles of zero tokens and SLORA_STATUS_BAD_TABLE.
 __global__ void __launch_bounds__(1024) plan_build_kernel(int32_t* ws, const int64_t* __restrict__ ids,
                                                           const int64_t* __restrict__ start,
                                                           const int64_t* __restrict__ ranks4, int64_t loc_len, int T,
-                                                          int n_adapters, int max_tiles) {
+                                                          int n_adapters, int max_tiles, int max_big) {
   int32_t* hdr = ws;
   int32_t* tiles = ws + PH_WORDS;
   int32_t* perm = tiles + kTileWords * max_tiles;
   int32_t* pos = perm + T;
   int32_t* cnt = pos + T;
-  __shared__ int s_tok[32], s_tile[32];
+  const int big_off = (PH_WORDS + kTileWords * max_tiles + 2 * T + n_adapters + 3) & ~3;  // 16-byte aligned records
+  int32_t* big = ws + big_off;
+  __shared__ int s_tok[32], s_tile[32], s_big[32];
   __shared__ int s_status;
   const int tid = threadIdx.x, nthr = blockDim.x, lane = tid & 31, warp = tid >> 5;
 
@@ -38,47 +41,64 @@ __global__ void __launch_bounds__(1024) plan_build_kernel(int32_t* ws, const int
   // exclusive scan over adapters of (tokens, tiles); each thread owns a contiguous run of adapters
   const int per = (n_adapters + nthr - 1) / nthr;
   const int lo = min(tid * per, n_adapters), hi = min(lo + per, n_adapters);
-  int tok_sum = 0, tile_sum = 0;
+  // a group is big when it has kBigGroupTokens tokens or more and a rank the tensor-core kernels take
+  auto is_big = [&](int a, int c) {
+    if (c < kBigGroupTokens) return false;
+    const int64_t r = ranks4[a] >> 2;
+    return r >= 8 && r <= 128 && r % 8 == 0;
+  };
+  int tok_sum = 0, tile_sum = 0, big_sum = 0;
   for (int a = lo; a < hi; ++a) {
     const int c = cnt[a];
     tok_sum += c;
     tile_sum += (c + kTileTokens - 1) / kTileTokens;
+    if (is_big(a, c)) big_sum += (c + kBigTileTokens - 1) / kBigTileTokens;
   }
-  int tok_inc = tok_sum, tile_inc = tile_sum;
+  int tok_inc = tok_sum, tile_inc = tile_sum, big_inc = big_sum;
 #pragma unroll
   for (int off = 1; off < 32; off <<= 1) {
     const int a = __shfl_up_sync(0xffffffffu, tok_inc, off);
     const int b = __shfl_up_sync(0xffffffffu, tile_inc, off);
+    const int g = __shfl_up_sync(0xffffffffu, big_inc, off);
     if (lane >= off) {
       tok_inc += a;
       tile_inc += b;
+      big_inc += g;
     }
   }
   if (lane == 31) {
     s_tok[warp] = tok_inc;
     s_tile[warp] = tile_inc;
+    s_big[warp] = big_inc;
   }
   __syncthreads();
   if (warp == 0) {
     const int nw = nthr >> 5;
-    const int a = lane < nw ? s_tok[lane] : 0, b = lane < nw ? s_tile[lane] : 0;
-    int ai = a, bi = b;
+    const int a = lane < nw ? s_tok[lane] : 0, b = lane < nw ? s_tile[lane] : 0, g = lane < nw ? s_big[lane] : 0;
+    int ai = a, bi = b, gi = g;
 #pragma unroll
     for (int off = 1; off < 32; off <<= 1) {
       const int a2 = __shfl_up_sync(0xffffffffu, ai, off);
       const int b2 = __shfl_up_sync(0xffffffffu, bi, off);
+      const int g2 = __shfl_up_sync(0xffffffffu, gi, off);
       if (lane >= off) {
         ai += a2;
         bi += b2;
+        gi += g2;
       }
     }
     s_tok[lane] = ai - a;  // exclusive
     s_tile[lane] = bi - b;
-    if (lane == 31) hdr[PH_NTILES] = min(bi, max_tiles);
+    s_big[lane] = gi - g;
+    if (lane == 31) {
+      hdr[PH_NTILES] = min(bi, max_tiles);
+      hdr[PH_NBIG] = min(gi, max_big);
+    }
   }
   __syncthreads();
   int tok_off = s_tok[warp] + tok_inc - tok_sum;
   int tile_off = s_tile[warp] + tile_inc - tile_sum;
+  int bigt_off = s_big[warp] + big_inc - big_sum;
   for (int a = lo; a < hi; ++a) {
     const int c = cnt[a];
     cnt[a] = tok_off;  // becomes the group's first slot in perm
@@ -86,14 +106,26 @@ __global__ void __launch_bounds__(1024) plan_build_kernel(int32_t* ws, const int
       const int64_t r4 = ranks4[a], st = start[a];
       const bool good = r4 >= 0 && st >= 0 && st + r4 <= loc_len && r4 <= (int64_t(1) << 20) && st < 0x7fffffffLL;
       if (!good) atomicOr(&s_status, SLORA_STATUS_BAD_TABLE);
+      const bool bigg = good && is_big(a, c);
       for (int i = 0; i * kTileTokens < c; ++i) {
         if (tile_off < max_tiles) {
           int4* rec = reinterpret_cast<int4*>(tiles + kTileWords * tile_off);
           rec[0] = make_int4(a, tok_off + i * kTileTokens, good ? min(kTileTokens, c - i * kTileTokens) : 0,
                              good ? static_cast<int>(r4 >> 2) : 0);
-          rec[1] = make_int4(good ? static_cast<int>(st) : 0, 0, 0, 0);
+          rec[1] = make_int4(good ? static_cast<int>(st) : 0, bigg ? 1 : 0, 0, 0);
         }
         ++tile_off;
+      }
+      if (bigg) {
+        for (int i = 0; i * kBigTileTokens < c; ++i) {
+          if (bigt_off < max_big) {
+            int4* rec = reinterpret_cast<int4*>(big + kTileWords * bigt_off);
+            rec[0] = make_int4(a, tok_off + i * kBigTileTokens, min(kBigTileTokens, c - i * kBigTileTokens),
+                               static_cast<int>(r4 >> 2));
+            rec[1] = make_int4(static_cast<int>(st), 0, 0, 0);
+          }
+          ++bigt_off;
+        }
       }
     }
     tok_off += c;
@@ -109,6 +141,8 @@ __global__ void __launch_bounds__(1024) plan_build_kernel(int32_t* ws, const int
     hdr[PH_MAXTILES] = max_tiles;
     hdr[PH_T] = T;
     hdr[PH_NADAPTERS] = n_adapters;
+    hdr[PH_BIGOFF] = big_off;
+    hdr[PH_MAXBIG] = max_big;
   }
 }
 

@@ -122,3 +122,52 @@ def test_out_of_range_pool_row_skips_the_tile():
     w.a_loc = bad
     _, y = _run_segments(wl, w, 0)
     assert float(y.abs().max()) == 0.0
+
+
+def _planned_layer(wl, w, use_pdl=True):
+    ops = sl.LoraBatchOps(w.a_start, w.a_len, w.a_loc, w.a_scaling, w.pools_a, w.pools_b, w.max_rank, use_pdl)
+    ops.prepare(w.ids)
+    H, K = wl.spec.hidden, wl.spec.h_kv
+    outs = [torch.zeros((wl.T, n), dtype=wl.dtype, device=DEV) for n in (H, K, K, H)]
+    ops.lora_get_qkv(0, w.x_qkv[0], outs[0], outs[1], outs[2])
+    ops.lora_get_o(0, w.x_o[0], outs[3])
+    torch.cuda.synchronize()
+    ops.plan.check()
+    return outs
+
+
+@pytest.mark.parametrize("use_pdl", [True, False])
+def test_planned_batch_routes_big_groups_to_the_tensor_cores(use_pdl):
+    """A mixed batch through LoraBatchOps: sequences of 130..400 tokens (same-adapter groups of 128 tokens or more,
+    gathered through the plan's permutation) run on the tensor cores, the decode tokens and short sequences on the
+    CUDA cores, in the same calls."""
+    wl = build_workload(3, pool_rows=8192, n_adapters=16, decode_tokens=40, prefill=("seqs", 5, 20, 400), hidden=1024)
+    assert max(n for _, n, _ in wl.segments) >= 128
+    w = wl.to(DEV)
+    before = sl.launch_counts()
+    outs = _planned_layer(wl, w, use_pdl)
+    after = sl.launch_counts()
+    assert after["tensor_core"] - before["tensor_core"] == 4    # q,k,v shrink, q,k,v expand, o shrink, o expand
+    cuda_core = sum(after[k] - before[k] for k in ("pipelined", "simple"))
+    assert cuda_core == 4                                       # the rest of the batch, same four calls
+    for p in range(4):
+        assert_parity(outs[p], _oracle(wl, p), what=f"planned big groups proj {p}")
+
+
+def test_planned_batch_bf16_rank_128():
+    wl = build_workload(3, dtype=torch.bfloat16, pool_rows=4096, n_adapters=3, decode_tokens=10,
+                        prefill=("seqs", 2, 200, 300), hidden=1024, rank_choices=(128,))
+    w = wl.to(DEV)
+    outs = _planned_layer(wl, w)
+    for p in range(4):
+        assert_parity(outs[p], _oracle(wl, p), torch.bfloat16, what=f"planned rank 128 proj {p}")
+
+
+def test_small_batch_below_one_tile():
+    """One 40-token sequence: the whole batch is smaller than the 128-row box of the tensor maps."""
+    wl = build_workload(3, pool_rows=4096, n_adapters=2, decode_tokens=0, prefill=("seqs", 1, 40, 40), hidden=1024,
+                        rank_choices=(16,))
+    w = wl.to(DEV)
+    for p in (0, 3):
+        _, y = _run_segments(wl, w, p)
+        assert_parity(y, _oracle(wl, p), what=f"40 tokens proj {p}")
