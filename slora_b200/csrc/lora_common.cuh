@@ -87,6 +87,7 @@ struct ShrinkArgs {
   int piece;         // simple kernel: elements per bulk copy
   int mma_stage_bytes;  // tensor-core kernel: bytes of one pipeline stage
   int mma_stages;       // tensor-core kernel: pipeline stages
+  int mma_ksplit;       // tensor-core kernel: CTAs (one cluster) that split K of one tile
   int32_t* status;
 };
 

@@ -193,7 +193,7 @@ int launch(K kernel, int64_t grid, int threads, size_t smem, unsigned flags, cud
 // The same with a second kernel argument (a tensor map or a set of them).
 template <typename K, typename A, typename B>
 int launch2(K kernel, int64_t grid, int threads, size_t smem, unsigned flags, cudaStream_t stream, const A& args,
-            const B& extra, const char* what) {
+            const B& extra, const char* what, int cluster = 1) {
   if (grid <= 0) return SLORA_OK;
   if (grid > 0x7fffffffLL) return fail(SLORA_ERR_SHAPE, "%s: grid of %lld CTAs is too large", what, (long long)grid);
   cudaLaunchConfig_t cfg;
@@ -202,11 +202,18 @@ int launch2(K kernel, int64_t grid, int threads, size_t smem, unsigned flags, cu
   cfg.blockDim = dim3(static_cast<unsigned>(threads), 1, 1);
   cfg.dynamicSmemBytes = smem;
   cfg.stream = stream;
-  cudaLaunchAttribute attr[1];
+  cudaLaunchAttribute attr[2];
   int nattr = 0;
   if (flags & SLORA_FLAG_PDL) {
     attr[nattr].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[nattr].val.programmaticStreamSerializationAllowed = 1;
+    ++nattr;
+  }
+  if (cluster > 1) {
+    attr[nattr].id = cudaLaunchAttributeClusterDimension;
+    attr[nattr].val.clusterDim.x = static_cast<unsigned>(cluster);
+    attr[nattr].val.clusterDim.y = 1;
+    attr[nattr].val.clusterDim.z = 1;
     ++nattr;
   }
   cfg.attrs = attr;
@@ -323,22 +330,33 @@ int run_shrink(const TileSrc& src, const Tables& tb, const void* w, const void* 
     m.rows_per_cta = gp;
     m.max_rb = nproj / gp;
     m.mma_stage_bytes = kMmaXTileBytes + npad_max * kMmaKBlock * 2;
+    const int64_t mma_tiles = src.mode == MODE_PLAN ? src.big_slots : static_cast<int64_t>(src.n_seg) * src.mma_tiles_per_seg;
+    // split K over a cluster of up to 8 CTAs while the launch would otherwise leave SMs idle (a tile alone streams
+    // 128 x h_in activations through one SM); a plan enumerates about twice the tiles it can hold
+    const int64_t likely_units = (src.mode == MODE_PLAN ? src.T / kBigTileTokens + 1 : mma_tiles) * m.max_rb;
+    const int nkb_total = h_in / kMmaKBlock;
+    int ks = 8;
+    while (ks > 1 && (nkb_total % ks != 0 || likely_units * ks > sm_count() + sm_count() / 8)) ks >>= 1;
+    m.mma_ksplit = ks;
     m.mma_stages = (kMmaSmemBudget - 1024) / m.mma_stage_bytes;
     if (m.mma_stages > kMmaMaxStages) m.mma_stages = kMmaMaxStages;
-    const size_t smem = static_cast<size_t>(m.mma_stages) * m.mma_stage_bytes + 1024;
-    const int64_t mma_tiles = src.mode == MODE_PLAN ? src.big_slots : static_cast<int64_t>(src.n_seg) * src.mma_tiles_per_seg;
-    const int64_t grid = mma_tiles * m.max_rb;
+    if (m.mma_stages > nkb_total / ks) m.mma_stages = nkb_total / ks;
+    size_t smem = static_cast<size_t>(m.mma_stages) * m.mma_stage_bytes;
+    const size_t red_bytes = static_cast<size_t>(kMmaTokens) * (npad_max + 4) * 4;  // split-K partial sums
+    if (ks > 1 && smem < red_bytes) smem = red_bytes;
+    smem += 1024;
+    const int64_t grid = mma_tiles * m.max_rb * ks;
     CUtensorMap x_map;
     rc = make_tmap(&x_map, dtype, x, h_in, src.T, x_stride, kMmaTokens);
     if (rc) return rc;
     if (dtype == SLORA_F16) {
       auto k = lora_shrink_mma_kernel<__half>;
       rc = ensure_dyn_smem(k, 4, smem, 4096);
-      if (!rc) rc = launch2(k, grid, kMmaShrinkThreads, smem, flags, stream, m, x_map, "shrink(tensor core)");
+      if (!rc) rc = launch2(k, grid, kMmaShrinkThreads, smem, flags, stream, m, x_map, "shrink(tensor core)", ks);
     } else {
       auto k = lora_shrink_mma_kernel<__nv_bfloat16>;
       rc = ensure_dyn_smem(k, 5, smem, 4096);
-      if (!rc) rc = launch2(k, grid, kMmaShrinkThreads, smem, flags, stream, m, x_map, "shrink(tensor core)");
+      if (!rc) rc = launch2(k, grid, kMmaShrinkThreads, smem, flags, stream, m, x_map, "shrink(tensor core)", ks);
     }
     if (rc) return rc;
     a.src.seg_split = src.seg_split;

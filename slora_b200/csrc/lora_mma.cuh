@@ -173,6 +173,34 @@ template <int N>
 __device__ __forceinline__ void bulk_wait() {
   asm volatile("cp.async.bulk.wait_group %0;" ::"n"(N) : "memory");
 }
+// Thread-block cluster helpers (split-K shrink): this CTA's rank, a barrier over all threads of the cluster, the
+// address of a peer CTA's copy of a shared-memory location, and a 16-byte load from it.
+__device__ __forceinline__ uint32_t cluster_rank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\nbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ uint32_t peer_smem(uint32_t addr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ float4 ld_peer_f4(uint32_t addr) {
+  float4 v;
+  asm volatile("ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [%4];"
+               : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w)
+               : "r"(addr)
+               : "memory");
+  return v;
+}
+__device__ __forceinline__ int ld_peer_i32(uint32_t addr) {
+  int v;
+  asm volatile("ld.shared::cluster.b32 %0, [%1];" : "=r"(v) : "r"(addr) : "memory");
+  return v;
+}
 __device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_all;" ::: "memory"); }
 // Barrier among `threads` threads of the CTA (hardware barrier 1; barrier 0 is __syncthreads), and the same with an
 // AND-reduction of a predicate.
@@ -292,8 +320,13 @@ __global__ void __launch_bounds__(kMmaShrinkThreads, 1)
 
   pdl_launch_dependents();
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  const int pg = blockIdx.x % a.max_rb;
-  const int tile_idx = blockIdx.x / a.max_rb;
+  // split-K: the `ks` CTAs of a cluster share one (tile, projection group) and take consecutive K ranges; every
+  // early return below depends on the tile only, so the CTAs of a cluster take it together
+  const int ks = a.mma_ksplit;
+  const int kq = ks > 1 ? static_cast<int>(cluster_rank()) : 0;
+  const int unit = blockIdx.x / ks;
+  const int pg = unit % a.max_rb;
+  const int tile_idx = unit / a.max_rb;
   MmaTile t;
   if (!lookup_mma_tile(a.src, a.tb, tile_idx, t, nullptr)) return;
   const int r = t.r;
@@ -327,7 +360,8 @@ __global__ void __launch_bounds__(kMmaShrinkThreads, 1)
   const int nst = a.mma_stages;
   const uint32_t smem0 = (smem_u32(mma_smem) + 1023u) & ~1023u;
   const uint32_t stage_bytes = static_cast<uint32_t>(a.mma_stage_bytes);
-  const int nkb = a.h_in / kMmaKBlock;
+  const int nkb = a.h_in / kMmaKBlock / ks;  // K-blocks of this CTA
+  const int kb_base = kq * nkb;
   if (tid == 0) {
     for (int s = 0; s < nst; ++s) {
       mbar_init(&ctl.full[s], gather ? 1 : 2);
@@ -362,7 +396,7 @@ __global__ void __launch_bounds__(kMmaShrinkThreads, 1)
           ctl.bad = 1;
           break;
         }
-        const int k0 = kb * kMmaKBlock;
+        const int k0 = (kb_base + kb) * kMmaKBlock;
         if (gather) {
           // token rows into the 128-byte swizzled layout the TMA would have produced: chunk c of row i at
           // i * 128 + ((c ^ (i & 7)) << 4)
@@ -402,7 +436,7 @@ __global__ void __launch_bounds__(kMmaShrinkThreads, 1)
           break;
         }
         mbar_expect_tx(&ctl.full[s], kMmaXTileBytes);
-        tma_load_2d(smem0 + s * stage_bytes, &x_map, kb * kMmaKBlock, t.first, &ctl.full[s]);
+        tma_load_2d(smem0 + s * stage_bytes, &x_map, (kb_base + kb) * kMmaKBlock, t.first, &ctl.full[s]);
       }
     }
   } else {
@@ -436,46 +470,94 @@ __global__ void __launch_bounds__(kMmaShrinkThreads, 1)
   if (warp < 4) ok = mbar_wait_timed(&ctl.acc_done, 0);
   ok = __syncthreads_and(ok) && ctl.bad == 0;
   tc_fence_after();
-  if (ok && warp < 4) {
-    const int row = warp * 32 + lane;
-    const bool live = row < t.n;
-    const int64_t tok = mma_token(t, live ? row : 0);
-    bool vec = (a.delta_stride % 8 == 0);
-    for (int q = 0; q < gp; ++q) vec = vec && ((reinterpret_cast<uintptr_t>(pick3(a.delta, p0 + q)) & 15) == 0);
-    int p = 0, jj = 0;  // column j = p * r + jj; r is a multiple of 8
-    for (int c0 = 0; c0 < npad; c0 += 16) {
-      uint32_t v[16];
-      tmem_ld16(tmem + (static_cast<uint32_t>(warp * 32) << 16) + c0, v);
-      tmem_ld_wait();
+  bool vec = (a.delta_stride % 8 == 0);
+  for (int q = 0; q < gp; ++q) vec = vec && ((reinterpret_cast<uintptr_t>(pick3(a.delta, p0 + q)) & 15) == 0);
+  // eight consecutive columns [j0, j0 + 8) of row `tok` (j0 a multiple of 8, so they lie in one projection)
+  auto store8 = [&](int64_t tok, int j0, const float (&f)[8]) {
+    const int p = j0 / r, jj = j0 - p * r;
+    T* drow = reinterpret_cast<T*>(pick3(a.delta, p0 + p)) + tok * a.delta_stride;
+    if (vec && jj + 8 <= a.delta_width) {
+      union {
+        uint4 q;
+        T e[8];
+      } pk;
 #pragma unroll
-      for (int h = 0; h < 2; ++h) {
-        if (c0 + h * 8 < rows) {
-          T* drow = reinterpret_cast<T*>(pick3(a.delta, p0 + p)) + tok * a.delta_stride;
-          if (live && vec && jj + 8 <= a.delta_width) {
-            union {
-              uint4 q;
-              T e[8];
-            } pk;
+      for (int e = 0; e < 8; ++e) pk.e[e] = from_f32<T>(f[e]);
+      *reinterpret_cast<uint4*>(drow + jj) = pk.q;
+    } else {
 #pragma unroll
-            for (int e = 0; e < 8; ++e) pk.e[e] = from_f32<T>(__uint_as_float(v[h * 8 + e]));
-            *reinterpret_cast<uint4*>(drow + jj) = pk.q;
-          } else if (live) {
+      for (int e = 0; e < 8; ++e) {
+        if (jj + e < a.delta_width) drow[jj + e] = from_f32<T>(f[e]);
+      }
+    }
+  };
+  if (ks == 1) {
+    if (ok && warp < 4) {
+      const int row = warp * 32 + lane;
+      const bool live = row < t.n;
+      const int64_t tok = mma_token(t, live ? row : 0);
+      for (int c0 = 0; c0 < npad; c0 += 16) {
+        uint32_t v[16];
+        tmem_ld16(tmem + (static_cast<uint32_t>(warp * 32) << 16) + c0, v);
+        tmem_ld_wait();
 #pragma unroll
-            for (int e = 0; e < 8; ++e) {
-              if (jj + e < a.delta_width) drow[jj + e] = from_f32<T>(__uint_as_float(v[h * 8 + e]));
-            }
-          }
-          jj += 8;
-          if (jj >= r) {
-            jj = 0;
-            ++p;
+        for (int h = 0; h < 2; ++h) {
+          if (live && c0 + h * 8 < rows) {
+            float f[8];
+#pragma unroll
+            for (int e = 0; e < 8; ++e) f[e] = __uint_as_float(v[h * 8 + e]);
+            store8(tok, c0 + h * 8, f);
           }
         }
       }
     }
-  } else if (!ok && tid == 0) {
-    set_status(a.status, SLORA_STATUS_TIMEOUT);
+  } else {
+    // partial sums to shared memory (the pipeline stages are idle now): [128 rows][npad + 4] floats
+    const uint32_t pitch = static_cast<uint32_t>(npad + 4) * 4;
+    if (ok && warp < 4) {
+      const int row = warp * 32 + lane;
+      for (int c0 = 0; c0 < npad; c0 += 16) {
+        uint32_t v[16];
+        tmem_ld16(tmem + (static_cast<uint32_t>(warp * 32) << 16) + c0, v);
+        tmem_ld_wait();
+#pragma unroll
+        for (int h = 0; h < 4; ++h)
+          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(smem0 + row * pitch + (c0 + h * 4) * 4),
+                       "r"(v[h * 4]), "r"(v[h * 4 + 1]), "r"(v[h * 4 + 2]), "r"(v[h * 4 + 3])
+                       : "memory");
+      }
+    }
+    if (tid == 0 && !ok) ctl.bad = 1;
+    cluster_sync_all();
+    // CTA kq adds the ks partial tiles for its share of the rows, in rank order, and stores them
+    bool all_ok = true;
+    for (int q = 0; q < ks; ++q) all_ok = all_ok && ld_peer_i32(peer_smem(smem_u32(&ctl.bad), q)) == 0;
+    if (all_ok && tid < 128) {
+      const int rows_per = kMmaTokens / ks;
+      const int groups = npad >> 3;
+      for (int u = tid; u < rows_per * groups; u += 128) {
+        const int row = kq * rows_per + u / groups;
+        const int j0 = (u % groups) * 8;
+        if (row < t.n && j0 < rows) {
+          float f[8];
+#pragma unroll
+          for (int e = 0; e < 8; ++e) f[e] = 0.f;
+          const uint32_t local = smem0 + row * pitch + j0 * 4;
+          for (int q = 0; q < ks; ++q) {
+            const uint32_t pa = peer_smem(local, q);
+            const float4 lo4 = ld_peer_f4(pa), hi4 = ld_peer_f4(pa + 16);
+            f[0] += lo4.x, f[1] += lo4.y, f[2] += lo4.z, f[3] += lo4.w;
+            f[4] += hi4.x, f[5] += hi4.y, f[6] += hi4.z, f[7] += hi4.w;
+          }
+          store8(mma_token(t, row), j0, f);
+        }
+      }
+    }
+    ok = all_ok;
+    // no CTA of the cluster may leave while a peer still reads its shared memory
+    cluster_sync_all();
   }
+  if (!ok && tid == 0) set_status(a.status, SLORA_STATUS_TIMEOUT);
   tc_fence_before();
   __syncthreads();
   if (warp == 0) tmem_dealloc(tmem, cols);
