@@ -288,7 +288,7 @@ def kernel_roofline(run, peak_gbs, peak_kind):
     y_bytes = wl.T * sum(2 * dims[p][1] * es for p in range(3))
     a_bytes = sum(wl.ranks[a] * dims[p][0] * es for a in distinct for p in range(3))
     x_bytes = wl.T * dims[0][0] * es
-    flags = 0 if run.args.no_pdl else _lib.FLAG_PDL
+    flags = ops.flags  # programmatic launch and tensor-core routing as the step itself uses them
 
     def shrinks():
         for l in range(run.L):

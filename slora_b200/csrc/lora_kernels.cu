@@ -190,6 +190,64 @@ int launch(K kernel, int64_t grid, int threads, size_t smem, unsigned flags, cud
   return SLORA_OK;
 }
 
+// A call that launches a tensor-core kernel and a CUDA-core kernel runs the two side by side: they work on disjoint
+// tokens, so the tensor-core kernel goes to a library-owned side stream that forks from the caller's stream before
+// the launch and joins it again after the CUDA-core launch (also under stream capture, where the pair becomes two
+// parallel branches of the graph).  One side stream and two events per device, created at first use and kept.
+// SLORA_SIDE_STREAM=0 keeps everything on the caller's stream.
+struct SideStream {
+  cudaStream_t stream;
+  cudaEvent_t fork, join;
+  int state;  // 0 = not created yet, 1 = usable, -1 = creation failed or switched off
+};
+SideStream* side_stream() {
+  static SideStream sides[64];
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) {
+    cudaGetLastError();
+    return nullptr;
+  }
+  SideStream& sd = sides[dev];
+  if (sd.state == 0) {
+    const char* e = getenv("SLORA_SIDE_STREAM");
+    sd.state = -1;
+    if (!(e && strcmp(e, "0") == 0) &&
+        cudaStreamCreateWithFlags(&sd.stream, cudaStreamNonBlocking) == cudaSuccess &&
+        cudaEventCreateWithFlags(&sd.fork, cudaEventDisableTiming) == cudaSuccess &&
+        cudaEventCreateWithFlags(&sd.join, cudaEventDisableTiming) == cudaSuccess) {
+      sd.state = 1;
+    } else {
+      cudaGetLastError();
+    }
+  }
+  return sd.state == 1 ? &sd : nullptr;
+}
+// Fork: returns the stream the tensor-core kernel should use (the side stream, or `main` when there is none).
+cudaStream_t fork_side(SideStream* sd, cudaStream_t main) {
+  if (!sd) return main;
+  if (cudaEventRecord(sd->fork, main) != cudaSuccess || cudaStreamWaitEvent(sd->stream, sd->fork, 0) != cudaSuccess) {
+    cudaGetLastError();
+    return main;
+  }
+  return sd->stream;
+}
+// Join on scope exit: whatever the caller's stream does next waits for the side stream's work of this call.
+struct SideJoin {
+  SideStream* sd = nullptr;
+  cudaStream_t main = nullptr;
+  void arm(SideStream* s, cudaStream_t m) {
+    if (cudaEventRecord(s->join, s->stream) == cudaSuccess) {
+      sd = s;
+      main = m;
+    } else {
+      cudaGetLastError();
+    }
+  }
+  ~SideJoin() {
+    if (sd && cudaStreamWaitEvent(main, sd->join, 0) != cudaSuccess) cudaGetLastError();
+  }
+};
+
 // The same with a second kernel argument (a tensor map or a set of them).
 template <typename K, typename A, typename B>
 int launch2(K kernel, int64_t grid, int threads, size_t smem, unsigned flags, cudaStream_t stream, const A& args,
@@ -318,6 +376,7 @@ int run_shrink(const TileSrc& src, const Tables& tb, const void* w, const void* 
   a.status = status;
   // long segments first go to the tensor-core kernel; the launch below then skips them
   a.src.seg_split = 0;
+  SideJoin side_join;
   if ((src.mode == MODE_SEGMENT || src.mode == MODE_PLAN) && src.seg_split > 0 && mma_enabled() && S == h_in &&
       h_in % kMmaKBlock == 0 && src.T < 0x7fffffff) {
     bool consecutive = true;
@@ -349,20 +408,25 @@ int run_shrink(const TileSrc& src, const Tables& tb, const void* w, const void* 
     CUtensorMap x_map;
     rc = make_tmap(&x_map, dtype, x, h_in, src.T, x_stride, kMmaTokens);
     if (rc) return rc;
+    // (calls chained with programmatic dependent launch stay on one stream: measured, the chain's overlap is worth
+    // more than running the pair side by side)
+    SideStream* sd = (flags & SLORA_FLAG_PDL) ? nullptr : side_stream();
+    const cudaStream_t mma_stream = fork_side(sd, stream);
     if (dtype == SLORA_F16) {
       auto k = lora_shrink_mma_kernel<__half>;
       rc = ensure_dyn_smem(k, 4, smem, 4096);
-      if (!rc) rc = launch2(k, grid, kMmaShrinkThreads, smem, flags, stream, m, x_map, "shrink(tensor core)", ks);
+      if (!rc) rc = launch2(k, grid, kMmaShrinkThreads, smem, flags, mma_stream, m, x_map, "shrink(tensor core)", ks);
     } else {
       auto k = lora_shrink_mma_kernel<__nv_bfloat16>;
       rc = ensure_dyn_smem(k, 5, smem, 4096);
-      if (!rc) rc = launch2(k, grid, kMmaShrinkThreads, smem, flags, stream, m, x_map, "shrink(tensor core)", ks);
+      if (!rc) rc = launch2(k, grid, kMmaShrinkThreads, smem, flags, mma_stream, m, x_map, "shrink(tensor core)", ks);
     }
+    if (mma_stream != stream) side_join.arm(sd, stream);
     if (rc) return rc;
     a.src.seg_split = src.seg_split;
-    // the CUDA-core launch of the same call may start while the tensor-core kernel runs: neither writes what the
-    // other reads before its grid-dependency wait, and their outputs are disjoint
-    flags |= SLORA_FLAG_PDL;
+    // without a side stream the CUDA-core launch of the same call may still start while the tensor-core kernel
+    // runs: neither writes what the other reads before its grid-dependency wait, and their outputs are disjoint
+    if (mma_stream == stream) flags |= SLORA_FLAG_PDL;
   }
   const bool can_pipe = (S % h_in == 0);
   const KernelChoice choice = kernel_choice();
@@ -454,6 +518,7 @@ int run_expand(const TileSrc& src, const Tables& tb, const void* w, const void* 
   a.rank_mult = rank_mult;
   a.status = status;
   a.src.seg_split = 0;
+  SideJoin side_join;
   bool can_mma = (src.mode == MODE_SEGMENT || src.mode == MODE_PLAN) && src.seg_split > 0 && mma_enabled() &&
                  delta_parts == 1 && rank_mult == 1 && delta_stride % 8 == 0;
   for (int p = 0; p < nproj; ++p)
@@ -476,18 +541,23 @@ int run_expand(const TileSrc& src, const Tables& tb, const void* w, const void* 
     for (int p = 0; p < nproj && !rc; ++p)
       rc = make_tmap(&y_maps.m[p], dtype, y[p], h_out[p], src.T, y_stride[p], kMmaTokens);
     if (rc) return rc;
+    // (calls chained with programmatic dependent launch stay on one stream: measured, the chain's overlap is worth
+    // more than running the pair side by side)
+    SideStream* sd = (flags & SLORA_FLAG_PDL) ? nullptr : side_stream();
+    const cudaStream_t mma_stream = fork_side(sd, stream);
     if (dtype == SLORA_F16) {
       auto k = lora_expand_mma_kernel<__half>;
       rc = ensure_dyn_smem(k, 6, smem, 12288);
-      if (!rc) rc = launch2(k, grid, kMmaExpandThreads, smem, flags, stream, m, y_maps, "expand(tensor core)");
+      if (!rc) rc = launch2(k, grid, kMmaExpandThreads, smem, flags, mma_stream, m, y_maps, "expand(tensor core)");
     } else {
       auto k = lora_expand_mma_kernel<__nv_bfloat16>;
       rc = ensure_dyn_smem(k, 7, smem, 12288);
-      if (!rc) rc = launch2(k, grid, kMmaExpandThreads, smem, flags, stream, m, y_maps, "expand(tensor core)");
+      if (!rc) rc = launch2(k, grid, kMmaExpandThreads, smem, flags, mma_stream, m, y_maps, "expand(tensor core)");
     }
+    if (mma_stream != stream) side_join.arm(sd, stream);
     if (rc) return rc;
     a.src.seg_split = src.seg_split;
-    flags |= SLORA_FLAG_PDL;  // as in the shrink: overlap the CUDA-core launch with the tensor-core kernel
+    if (mma_stream == stream) flags |= SLORA_FLAG_PDL;  // as in the shrink
   }
   const int pipe_piece = pow2_divisor(tb.pool_stride, kPipeChunk);
   bool can_pipe = delta_parts == 1 && delta_stride % 8 == 0 && pipe_piece * kMaxPieces >= kPipeChunk &&
