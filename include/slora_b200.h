@@ -218,6 +218,18 @@ int slora_validate_tables(const int64_t* start, const int64_t* ranks4, const int
                           int64_t n_adapters, int64_t loc_len, int64_t T, int64_t pool_rows, int32_t* report,
                           void* stream);
 
+/*
+ * Tensor parallelism (no reference code: lora_adapter.py:24 asserts world_size 1; the scheme is figures/slora_tp.png):
+ * after the all-gather of the rank-sharded intermediates, `gathered` holds [n_parts][nproj][T][part_width] (part g
+ * starts at element g * part_stride; its row (p, t) holds rank rows [g * rs, (g + 1) * rs) of token t's adapter,
+ * rs = ranks4[ids[t]] / 4 slot rows per part).  Writes plain delta rows out[p][t][g * rs + j], out being
+ * [nproj][T][n_parts * part_width], the layout slora_lora_expand_multi reads with delta_parts = 1 and
+ * rank_mult = n_parts.  Columns at and beyond an adapter's rank are not written.
+ */
+int slora_tp_regroup(void* out, const void* gathered, const int64_t* ids, const int64_t* ranks4, int n_parts,
+                     int nproj, int64_t T, int part_width, int64_t part_stride, int64_t n_adapters, int dtype,
+                     void* stream);
+
 /* Kernels this process has launched through the library so far, per family:
  * out[0] simple (one CTA per work item), out[1] pipelined (persistent, warp-specialised), out[2] tensor core
  * (tcgen05, long segments), out[3] plan building and table validation.  The counters only ever grow; a caller

@@ -49,6 +49,28 @@ __global__ void validate_tables_kernel(const int64_t* start, const int64_t* rank
     if (loc[i] < 0 || loc[i] >= pool_rows) report_bad(report, 3, i);
   }
 }
+// Tensor parallelism: turn the all-gathered intermediates [N][nproj][T][Rl] (rank g's columns are rank rows
+// [g * rs, (g + 1) * rs) of the token's adapter, rs = its per-rank slot rows) into plain delta rows
+// out[p][t][g * rs + j].  One CTA per (token, projection); columns at and beyond the adapter's rank are left alone.
+template <typename T>
+__global__ void tp_regroup_kernel(T* __restrict__ out, const T* __restrict__ in, const int64_t* __restrict__ ids,
+                                  const int64_t* __restrict__ ranks4, int N, int Rl, int64_t tokens,
+                                  int64_t part_stride, int64_t n_adapters) {
+  const int64_t t = blockIdx.x;
+  const int p = blockIdx.y;
+  const int64_t a = ids[t];
+  if (a < 0 || a >= n_adapters) return;
+  int64_t rs = ranks4[a] >> 2;
+  if (rs <= 0) return;
+  if (rs > Rl) rs = Rl;
+  const int R = N * Rl;
+  const int64_t row = static_cast<int64_t>(p) * tokens + t;
+  for (int idx = threadIdx.x; idx < N * Rl; idx += blockDim.x) {
+    const int g = idx / Rl, j = idx - g * Rl;
+    if (j < rs) out[row * R + g * rs + j] = in[g * part_stride + row * Rl + j];
+  }
+}
+
 __global__ void zero_report_kernel(int32_t* report) {
   if (threadIdx.x < 4) report[threadIdx.x] = 0;
 }
@@ -920,6 +942,27 @@ int slora_batch_lora_o_noalloc(const int64_t* ids, void* o, int64_t o_stride, in
   return slora_batch_lora_o(scratch, ids, o, o_stride, h_out, x, x_stride, h_in, pool_a, pool_b, pool_rows, pool_stride,
                             start, ranks4, loc, scales, n_adapters, loc_len, scratch + kNoAllocPlanBytes, max_rank,
                             max_rank, T, dtype, flags, stream);
+}
+
+int slora_tp_regroup(void* out, const void* gathered, const int64_t* ids, const int64_t* ranks4, int n_parts,
+                     int nproj, int64_t T, int part_width, int64_t part_stride, int64_t n_adapters, int dtype,
+                     void* stream) {
+  if (T == 0) return SLORA_OK;
+  if (!out || !gathered || !ids || !ranks4) return fail(SLORA_ERR_NULL, "null buffer or table pointer");
+  if (dtype != SLORA_F16 && dtype != SLORA_BF16) return fail(SLORA_ERR_DTYPE, "unsupported dtype %d", dtype);
+  if (n_parts < 1 || nproj < 1 || nproj > 3 || part_width < 1 || T < 0 || T > 0x7fffffff || part_stride < 0)
+    return fail(SLORA_ERR_SHAPE, "tp_regroup: bad shape");
+  const dim3 grid(static_cast<unsigned>(T), static_cast<unsigned>(nproj));
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (dtype == SLORA_F16) {
+    tp_regroup_kernel<__half><<<grid, 128, 0, s>>>(static_cast<__half*>(out), static_cast<const __half*>(gathered), ids,
+                                                  ranks4, n_parts, part_width, T, part_stride, n_adapters);
+  } else {
+    tp_regroup_kernel<__nv_bfloat16><<<grid, 128, 0, s>>>(static_cast<__nv_bfloat16*>(out),
+                                                         static_cast<const __nv_bfloat16*>(gathered), ids, ranks4,
+                                                         n_parts, part_width, T, part_stride, n_adapters);
+  }
+  return check_launch("tp_regroup", 1);
 }
 
 int slora_validate_tables(const int64_t* start, const int64_t* ranks4, const int64_t* loc, const int64_t* ids,

@@ -87,6 +87,8 @@ class TpLoraOps:
         dev, dt = self.ids.device, self.pools_a[0].dtype
         self.local = torch.zeros((3, T, self.Rl), dtype=dt, device=dev)
         self.gathered = torch.zeros((self.N, 3, T, self.Rl), dtype=dt, device=dev)
+        # plain [nproj, T, R] delta rows for backends that regroup the gathered intermediates (see lora_qkv)
+        self.full = torch.zeros((3, T, self.R), dtype=dt, device=dev) if hasattr(self.backend, "regroup") else None
         self.plan = self.backend.make_plan(self.ids, self.t)
         return self
 
@@ -108,7 +110,13 @@ class TpLoraOps:
         self.backend.shrink(self.plan, self.ids, [0, 1, 2], [self.local[0], self.local[1], self.local[2]], x,
                             self.pools_a[layer], t)
         gathered, part_stride = self._exchange(3)
-        T = self.ids.numel()
+        if self.full is not None:
+            # regroup once, then the expand reads ordinary delta rows (and may use the pipelined kernels)
+            self.backend.regroup(self.full, gathered, self.ids, t, self.N, 3, self.Rl, part_stride)
+            self.backend.expand(self.plan, self.ids, [0, 1, 2], [q_g, k_g, v_g], [self.full[p] for p in range(3)],
+                                self.pools_b[layer], t, delta_stride=self.R, delta_width=self.R, delta_parts=1,
+                                delta_part_stride=0, rank_mult=self.N)
+            return
         deltas = [gathered[0, p] for p in range(3)]
         self.backend.expand(self.plan, self.ids, [0, 1, 2], [q_g, k_g, v_g], deltas, self.pools_b[layer], t,
                             delta_stride=self.Rl, delta_width=self.Rl, delta_parts=self.N,
@@ -118,6 +126,12 @@ class TpLoraOps:
         t = self.t
         self.backend.shrink(self.plan, self.ids, [3], [self.local[0]], x, self.pools_a[layer], t)
         stage, part_stride = self._exchange(1)
+        if self.full is not None:
+            self.backend.regroup(self.full, stage, self.ids, t, self.N, 1, self.Rl, part_stride)
+            self.backend.expand(self.plan, self.ids, [3], [o_g], [self.full[0]], self.pools_b[layer], t,
+                                delta_stride=self.R, delta_width=self.R, delta_parts=1, delta_part_stride=0,
+                                rank_mult=self.N)
+            return
         self.backend.expand(self.plan, self.ids, [3], [o_g], [stage[0]], self.pools_b[layer], t,
                             delta_stride=self.Rl, delta_width=self.Rl, delta_parts=self.N,
                             delta_part_stride=part_stride, rank_mult=self.N)
@@ -137,6 +151,13 @@ class CudaBackend:
     def shrink(self, plan, ids, qkvo, deltas, x, pool_a, t):
         from .batch_infer import shrink_multi
         shrink_multi(plan, ids, qkvo, deltas, x, pool_a, t.a_start, t.a_len, t.a_loc, self.flags)
+
+    def regroup(self, out, gathered, ids, t, n_parts, nproj, part_width, part_stride):
+        """``out[p, t, g*rs + j] = gathered[g, p, t, j]`` (C entry ``slora_tp_regroup``)."""
+        from . import _lib
+        _lib.check(_lib.lib.slora_tp_regroup(out.data_ptr(), gathered.data_ptr(), ids.data_ptr(), t.a_len.data_ptr(),
+                                             n_parts, nproj, ids.numel(), part_width, part_stride, t.a_start.numel(),
+                                             _lib.dtype_code(out.dtype), _lib.current_stream_ptr()))
 
     def expand(self, plan, ids, qkvo, ys, deltas, pool_b, t, **kw):
         from .batch_infer import expand_multi

@@ -22,7 +22,8 @@ def run(args, dist, rank, world, device):
     spec = wl.spec
     H, K, T, L, P = spec.hidden, spec.h_kv, wl.T, spec.layers, args.phys_layers
     tables = tp.TpTables(wl.a_start, wl.a_len, wl.a_loc, wl.a_scaling)
-    ops = tp.TpLoraOps(tables, wl.pools_a, wl.pools_b, wl.max_rank, world, rank, tp.CudaBackend()).prepare(wl.ids)
+    ops = tp.TpLoraOps(tables, wl.pools_a, wl.pools_b, wl.max_rank, world, rank,
+                       tp.CudaBackend(use_pdl=not args.no_pdl)).prepare(wl.ids)
     dt = wl.dtype
     q = [torch.zeros((T, H // world), dtype=dt, device=device) for _ in range(P)]
     k = [torch.zeros((T, K // world), dtype=dt, device=device) for _ in range(P)]
@@ -35,15 +36,22 @@ def run(args, dist, rank, world, device):
             ops.lora_qkv(p, wl.x_qkv[p], q[p], k[p], v[p])
             ops.lora_o(p, wl.x_o[p], o[p])
 
+    import slora_b200 as sl
+    before = sum(sl.launch_counts().values())
+    step()
+    torch.cuda.synchronize()
+    launches_per_step = sum(sl.launch_counts().values()) - before
+    # (eager on purpose: replaying the step, NCCL all-gathers included, from a CUDA graph measured the same time)
+    run = step
     for _ in range(max(args.warmup, 3)):
-        step()
+        run()
     torch.cuda.synchronize()
     dist.barrier()
     torch.cuda.synchronize()
     t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     t0.record()
     for _ in range(args.steps):
-        step()
+        run()
     t1.record()
     torch.cuda.synchronize()
     dist.barrier()
@@ -68,11 +76,12 @@ def run(args, dist, rank, world, device):
                        "adapters": spec.n_adapters, "max_rank": wl.max_rank, "phys_layers": P,
                        "parallelism": f"slora-tp{world}: A rank-sharded, B output-sharded, NCCL all-gather of "
                                       f"[T, 3R/N] and [T, R/N] per layer",
-                       "l2": "inputs larger than L2"},
+                       "l2": "inputs larger than L2", "graph": False, "pdl": not args.no_pdl},
             "per_rank_hbm": {"algorithmic_bytes_per_step": per_rank_bytes,
                              "achieved": per_rank_bytes / (elapsed / args.steps) / 1e9, "unit": "GB/s"},
             "exchange_bytes_per_step_per_rank": exch,
-            "gpu_launches": args.steps * L * 4, "e2e": None, "cpu_baseline": None,
+            "gpu_launches": args.steps * launches_per_step, "collectives_per_step": 2 * L, "e2e": None,
+            "cpu_baseline": None,
         }
         print(json.dumps(line), flush=True)
     dist.barrier()
