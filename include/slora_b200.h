@@ -230,6 +230,29 @@ int slora_tp_regroup(void* out, const void* gathered, const int64_t* ids, const 
                      int nproj, int64_t T, int part_width, int64_t part_stride, int64_t n_adapters, int dtype,
                      void* stream);
 
+/*
+ * Tensor parallelism, the exchange over peer memory (NVLink loads/stores; no reference code, see slora_tp_regroup).
+ * One launch per rank replaces all-gather + slora_tp_regroup: rank `my_part` writes its [nproj][T][part_width]
+ * intermediates `local` into every rank's delta buffer peer_full[g] ([2][3][full_tokens][n_parts * part_width]; the
+ * caller names the half: 0 for q,k,v calls, 1 for o calls, strictly alternating) at the regrouped columns, raises
+ * its flag on every rank (peer_flags[g]: int32 [2][n_parts]) and waits until the flags of all ranks for this exchange
+ * have arrived on this rank.  The expand then reads peer_full[my_part] + half * 3 * full_tokens * R with
+ * delta_parts = 1, rank_mult = n_parts.
+ *   peer_full / peer_flags: host arrays of n_parts device pointers valid on this GPU (symmetric memory, or
+ *   cudaIpc / cudaMalloc with peer access); flags start at zero.  seq_state: int32 [2] in this GPU's memory, zero at
+ *   the start: exchanges completed per half, maintained by the kernel (so a captured graph can be replayed).
+ *   counter: one zero-initialised int32 in this GPU's memory.  status: device status word or NULL.
+ *   mode: 1 = write and signal, 2 = wait (and count the exchange as done), 3 = both (the normal call).
+ *   flags: SLORA_FLAG_PDL lets the expand that follows fetch its adapter rows while the exchange is in flight.
+ * The wait is bounded (about 2 s of SM clock); when it runs out SLORA_STATUS_TIMEOUT is set in *status and the
+ * kernel returns, so a missing rank never hangs the GPU.  Ranks must run on different GPUs (a rank waiting for
+ * another rank's launch on the same GPU may wait for a kernel that cannot start).
+ */
+int slora_tp_exchange(const void* local, void* const* peer_full, int32_t* const* peer_flags, int32_t* counter,
+                      int32_t* status, const int64_t* ids, const int64_t* ranks4, int my_part, int n_parts, int nproj,
+                      int64_t T, int64_t full_tokens, int part_width, int64_t n_adapters, int half, int32_t* seq_state,
+                      int mode, int dtype, unsigned flags, void* stream);
+
 /* Kernels this process has launched through the library so far, per family:
  * out[0] simple (one CTA per work item), out[1] pipelined (persistent, warp-specialised), out[2] tensor core
  * (tcgen05, long segments), out[3] plan building and table validation.  The counters only ever grow; a caller

@@ -65,6 +65,8 @@ _SIGS = {
                                            _P, _P, c_int64, c_int64, c_int, c_int64, c_int, c_uint, _P]),
     "slora_validate_tables": (c_int, [_P, _P, _P, _P, c_int64, c_int64, c_int64, c_int64, _P, _P]),
     "slora_tp_regroup": (c_int, [_P, _P, _P, _P, c_int, c_int, c_int64, c_int, c_int64, c_int64, c_int, _P]),
+    "slora_tp_exchange": (c_int, [_P, _P, _P, _P, _P, _P, _P, c_int, c_int, c_int, c_int64, c_int64, c_int, c_int64,
+                                  c_int, _P, c_int, c_int, c_uint, _P]),
     "slora_launch_counts": (None, [_P]),
     "slora_plan_big_tiles": (c_int, [_P, _P, _P]),
 }

@@ -71,6 +71,102 @@ __global__ void tp_regroup_kernel(T* __restrict__ out, const T* __restrict__ in,
   }
 }
 
+// Tensor parallelism, exchange over peer memory: every rank writes its columns of the intermediates straight into
+// every rank's delta buffer (its own included) in the regrouped layout of tp_regroup_kernel, then tells every rank so
+// with a flag; the last CTA of the launch then waits (for a bounded time) until every rank's flag for this exchange
+// has arrived.  Replaces all-gather + regroup by one small kernel whose traffic is NVLink stores.
+//   full[g]  : rank g's buffer [2][3][T][R], R = n_parts * part_width; the caller names the half (q,k,v calls use
+//              half 0, o calls half 1)
+//   flags[g] : rank g's int32 [2][n_parts]; flags[g][half][r] = n once rank r's columns of the n-th exchange on
+//              that half have landed on rank g
+//   seq_state: this rank's int32 [2]: exchanges completed per half; the kernel reads it, works on number
+//              seq_state[half] + 1 and, when its wait is over, stores that number back.  Keeping the count on the
+//              device lets a captured CUDA graph be replayed (a count passed as a kernel argument would be frozen).
+// Two alternating halves suffice: a rank reaches its next exchange on half h only after every peer signalled the
+// exchange on the other half in between, which a peer does after the kernels that read half h on it (its expand)
+// have completed.
+constexpr int kTpMaxParts = 8;
+constexpr int kTpTokensPerCta = 16;
+constexpr long long kTpWaitCycles = 4000000000ll;  // about 2 s: ranks drift by host-side jitter, not more
+struct TpExchangeArgs {
+  const void* local;  // [nproj][T][part_width], this rank's shrink output
+  void* full[kTpMaxParts];
+  int32_t* flags[kTpMaxParts];
+  int32_t* counter;  // one zero-initialised int32 of this rank's memory (CTA arrival counter)
+  int32_t* status;
+  const int64_t* ids;
+  const int64_t* ranks4;
+  int my_part, n_parts, nproj, part_width;
+  int64_t T, n_adapters;
+  int64_t full_tokens;  // token rows per projection in a delta buffer (>= T)
+  int32_t* seq_state;
+  int half;
+  int mode;  // bit 0: write and signal, bit 1: wait for every rank's signal
+};
+
+template <typename T>
+__global__ void __launch_bounds__(128) tp_exchange_kernel(const TpExchangeArgs a) {
+  __shared__ int s_last;
+  const int tid = threadIdx.x;
+  const int half = a.half;
+  // under programmatic dependent launch the next kernel (the expand) may start now and fetch its adapter rows while
+  // this exchange is in flight; this kernel itself needs the shrink's output, so it waits for the kernel before it
+  pdl_launch_dependents();
+  pdl_wait();
+  // every CTA reads the count before the last one (which alone stores to it, at the very end) can get that far
+  const int seq = a.seq_state[half] + 1;
+  const int N = a.n_parts, pw = a.part_width;
+  const int64_t R = static_cast<int64_t>(N) * pw;
+  if (a.mode & 1) {
+    const int p = blockIdx.x % a.nproj;
+    const int64_t t0 = static_cast<int64_t>(blockIdx.x / a.nproj) * kTpTokensPerCta;
+    const T* local = reinterpret_cast<const T*>(a.local);
+    for (int idx = tid; idx < kTpTokensPerCta * N * pw; idx += blockDim.x) {
+      const int tt = idx / (N * pw);
+      const int rem = idx - tt * (N * pw);
+      const int g = rem / pw, j = rem - g * pw;
+      const int64_t t = t0 + tt;
+      if (t >= a.T) continue;
+      const int64_t ad = a.ids[t];
+      if (ad < 0 || ad >= a.n_adapters) continue;
+      int64_t rs = a.ranks4[ad] >> 2;
+      if (rs > pw) rs = pw;
+      if (j >= rs) continue;
+      T* dst = reinterpret_cast<T*>(a.full[g]) + ((static_cast<int64_t>(half) * 3 + p) * a.full_tokens + t) * R;
+      dst[a.my_part * rs + j] = local[(static_cast<int64_t>(p) * a.T + t) * pw + j];
+    }
+  }
+  // the last CTA to get here speaks for the launch
+  __threadfence_system();
+  __syncthreads();
+  if (tid == 0) {
+    const int total = static_cast<int>(gridDim.x);
+    s_last = atomicAdd(a.counter, 1) == total - 1;
+  }
+  __syncthreads();
+  if (!s_last) return;
+  if (tid == 0) *a.counter = 0;
+  __threadfence_system();
+  if ((a.mode & 1) && tid < N) {
+    asm volatile("st.release.sys.global.b32 [%0], %1;" ::"l"(a.flags[tid] + half * N + a.my_part), "r"(seq) : "memory");
+  }
+  if ((a.mode & 2) && tid < N) {
+    const int32_t* mine = a.flags[a.my_part] + half * N + tid;
+    const long long t_start = clock64();
+    bool seen = false;
+    while (!seen) {
+      int v;
+      asm volatile("ld.acquire.sys.global.b32 %0, [%1];" : "=r"(v) : "l"(mine) : "memory");
+      seen = v >= seq;
+      if (!seen && clock64() - t_start > kTpWaitCycles) break;
+    }
+    if (!seen) set_status(a.status, SLORA_STATUS_TIMEOUT);
+  }
+  __threadfence_system();
+  __syncthreads();
+  if ((a.mode & 2) && tid == 0) a.seq_state[half] = seq;
+}
+
 __global__ void zero_report_kernel(int32_t* report) {
   if (threadIdx.x < 4) report[threadIdx.x] = 0;
 }
@@ -178,6 +274,7 @@ int sm_count() {
 }
 
 int family_of(const char* what) {
+  if (strstr(what, "tp_exchange")) return 3;
   if (strstr(what, "tensor core")) return 2;
   if (strstr(what, "pipelined")) return 1;
   return 0;
@@ -963,6 +1060,53 @@ int slora_tp_regroup(void* out, const void* gathered, const int64_t* ids, const 
                                                          n_parts, part_width, T, part_stride, n_adapters);
   }
   return check_launch("tp_regroup", 1);
+}
+
+int slora_tp_exchange(const void* local, void* const* peer_full, int32_t* const* peer_flags, int32_t* counter,
+                      int32_t* status, const int64_t* ids, const int64_t* ranks4, int my_part, int n_parts, int nproj,
+                      int64_t T, int64_t full_tokens, int part_width, int64_t n_adapters, int half, int32_t* seq_state,
+                      int mode, int dtype, unsigned flags, void* stream) {
+  if (full_tokens < T) return fail(SLORA_ERR_SHAPE, "tp_exchange: delta buffers hold %lld token rows, batch has %lld",
+                                   (long long)full_tokens, (long long)T);
+  if (dtype != SLORA_F16 && dtype != SLORA_BF16) return fail(SLORA_ERR_DTYPE, "unsupported dtype %d", dtype);
+  if (!peer_full || !peer_flags || !counter || !seq_state) return fail(SLORA_ERR_NULL, "null peer table or counter");
+  if (n_parts < 1 || n_parts > kTpMaxParts || my_part < 0 || my_part >= n_parts)
+    return fail(SLORA_ERR_SHAPE, "tp_exchange: n_parts=%d (max %d), my_part=%d", n_parts, kTpMaxParts, my_part);
+  if (nproj < 1 || nproj > 3 || part_width < 1 || T < 0 || T > 0x7fffffff || half < 0 || half > 1 || (mode & 3) == 0)
+    return fail(SLORA_ERR_SHAPE, "tp_exchange: bad shape, half or mode");
+  if ((mode & 1) && T > 0 && (!local || !ids || !ranks4)) return fail(SLORA_ERR_NULL, "null buffer or table pointer");
+  TpExchangeArgs a;
+  memset(&a, 0, sizeof(a));
+  a.local = local;
+  for (int g = 0; g < n_parts; ++g) {
+    if (!peer_full[g] || !peer_flags[g]) return fail(SLORA_ERR_NULL, "tp_exchange: null peer pointer %d", g);
+    a.full[g] = peer_full[g];
+    a.flags[g] = peer_flags[g];
+  }
+  a.counter = counter;
+  a.status = status;
+  a.ids = ids;
+  a.ranks4 = ranks4;
+  a.my_part = my_part;
+  a.n_parts = n_parts;
+  a.nproj = nproj;
+  a.part_width = part_width;
+  a.T = T;
+  a.full_tokens = full_tokens;
+  a.n_adapters = n_adapters;
+  a.seq_state = seq_state;
+  a.half = half;
+  a.mode = mode;
+  const bool push = (mode & 1) && T > 0;
+  const int64_t grid = push ? (T + kTpTokensPerCta - 1) / kTpTokensPerCta * nproj : 1;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  int rc;
+  if (dtype == SLORA_F16) {
+    rc = launch(tp_exchange_kernel<__half>, grid, 128, 0, flags, s, a, "tp_exchange");
+  } else {
+    rc = launch(tp_exchange_kernel<__nv_bfloat16>, grid, 128, 0, flags, s, a, "tp_exchange");
+  }
+  return rc;
 }
 
 int slora_validate_tables(const int64_t* start, const int64_t* ranks4, const int64_t* loc, const int64_t* ids,

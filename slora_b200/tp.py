@@ -63,6 +63,36 @@ class TpTables:
     a_scaling: torch.Tensor
 
 
+class PeerExchange:
+    """Symmetric-memory buffers of the exchange over peer memory (C entry ``slora_tp_exchange``).
+
+    Every rank owns a delta buffer ``[2, 3, T, R]`` and a flag array ``[2, N]`` that all ranks can address over
+    NVLink (``torch.distributed._symmetric_memory``).  One small kernel per exchange writes this rank's columns into
+    every rank's buffer, raises its flag everywhere and waits for everybody's flag: it stands where
+    ``all_gather_into_tensor`` + regroup stand otherwise.
+    """
+
+    def __init__(self, T, R, world, rank, dtype, device, group=None):
+        import ctypes
+        import torch.distributed as dist
+        import torch.distributed._symmetric_memory as symm_mem
+        group = group or dist.group.WORLD
+        self.world, self.rank = world, rank
+        self.full = symm_mem.empty((2, 3, max(T, 1), R), dtype=dtype, device=device)
+        self.flags = symm_mem.empty((2, world), dtype=torch.int32, device=device)
+        self.full.zero_()
+        self.flags.zero_()
+        h_full = symm_mem.rendezvous(self.full, group.group_name)
+        h_flags = symm_mem.rendezvous(self.flags, group.group_name)
+        self.full_ptrs = (ctypes.c_void_p * world)(*[int(p) for p in h_full.buffer_ptrs])
+        self.flag_ptrs = (ctypes.c_void_p * world)(*[int(p) for p in h_flags.buffer_ptrs])
+        self._handles = (h_full, h_flags)
+        self.counter = torch.zeros(1, dtype=torch.int32, device=device)
+        self.seq_state = torch.zeros(2, dtype=torch.int32, device=device)   # exchanges done per half (device-kept)
+        torch.cuda.synchronize(device)
+        dist.barrier(group=group)   # nobody signals before everybody's flags are zero
+
+
 class TpLoraOps:
     """Per-rank LoRA operator under S-LoRA tensor parallelism.
 
@@ -72,13 +102,15 @@ class TpLoraOps:
     """
 
     def __init__(self, tables: TpTables, pools_a: List[torch.Tensor], pools_b: List[torch.Tensor], max_rank: int,
-                 world: int, rank: int, backend, group=None):
+                 world: int, rank: int, backend, group=None, peer_exchange: bool = False):
         if max_rank % world != 0:
             raise ValueError("max_rank must be divisible by the tensor-parallel size")
         self.t, self.pools_a, self.pools_b = tables, pools_a, pools_b
         self.R, self.N, self.rank = max_rank, world, rank
         self.Rl = max_rank // world
         self.backend, self.group = backend, group
+        self.peer_exchange = peer_exchange and world > 1 and hasattr(backend, "exchange")
+        self.px = None
         self.ids = None
 
     def prepare(self, token_adapter_ids: torch.Tensor):
@@ -90,6 +122,8 @@ class TpLoraOps:
         # plain [nproj, T, R] delta rows for backends that regroup the gathered intermediates (see lora_qkv)
         self.full = torch.zeros((3, T, self.R), dtype=dt, device=dev) if hasattr(self.backend, "regroup") else None
         self.plan = self.backend.make_plan(self.ids, self.t)
+        if self.peer_exchange and (self.px is None or self.px.full.shape[2] < T):
+            self.px = PeerExchange(T, self.R, self.N, self.rank, dt, dev, self.group)
         return self
 
     def _exchange(self, nproj):
@@ -109,6 +143,12 @@ class TpLoraOps:
         t = self.t
         self.backend.shrink(self.plan, self.ids, [0, 1, 2], [self.local[0], self.local[1], self.local[2]], x,
                             self.pools_a[layer], t)
+        if self.px is not None:
+            full = self.backend.exchange(self.px, self.plan, self.local, self.ids, t, 3, self.Rl, half=0)
+            self.backend.expand(self.plan, self.ids, [0, 1, 2], [q_g, k_g, v_g], [full[p] for p in range(3)],
+                                self.pools_b[layer], t, delta_stride=self.R, delta_width=self.R, delta_parts=1,
+                                delta_part_stride=0, rank_mult=self.N)
+            return
         gathered, part_stride = self._exchange(3)
         if self.full is not None:
             # regroup once, then the expand reads ordinary delta rows (and may use the pipelined kernels)
@@ -125,6 +165,12 @@ class TpLoraOps:
     def lora_o(self, layer, x, o_g):
         t = self.t
         self.backend.shrink(self.plan, self.ids, [3], [self.local[0]], x, self.pools_a[layer], t)
+        if self.px is not None:
+            full = self.backend.exchange(self.px, self.plan, self.local, self.ids, t, 1, self.Rl, half=1)
+            self.backend.expand(self.plan, self.ids, [3], [o_g], [full[0]], self.pools_b[layer], t,
+                                delta_stride=self.R, delta_width=self.R, delta_parts=1, delta_part_stride=0,
+                                rank_mult=self.N)
+            return
         stage, part_stride = self._exchange(1)
         if self.full is not None:
             self.backend.regroup(self.full, stage, self.ids, t, self.N, 1, self.Rl, part_stride)
@@ -158,6 +204,18 @@ class CudaBackend:
         _lib.check(_lib.lib.slora_tp_regroup(out.data_ptr(), gathered.data_ptr(), ids.data_ptr(), t.a_len.data_ptr(),
                                              n_parts, nproj, ids.numel(), part_width, part_stride, t.a_start.numel(),
                                              _lib.dtype_code(out.dtype), _lib.current_stream_ptr()))
+
+    def exchange(self, px, plan, local, ids, t, nproj, part_width, half, mode=3):
+        """Write ``local[:nproj]`` into half ``half`` of every rank's delta buffer, signal, wait; returns this rank's
+        ``[3, T, R]`` view of that half.  q,k,v calls use half 0 and o calls half 1, strictly alternating."""
+        from . import _lib
+        status = 0 if plan is None else plan.ptr + 8      # the plan header's status word
+        _lib.check(_lib.lib.slora_tp_exchange(local.data_ptr(), px.full_ptrs, px.flag_ptrs, px.counter.data_ptr(),
+                                              status, ids.data_ptr(), t.a_len.data_ptr(), px.rank, px.world, nproj,
+                                              ids.numel(), px.full.shape[2], part_width, t.a_start.numel(), half,
+                                              px.seq_state.data_ptr(), mode, _lib.dtype_code(local.dtype),
+                                              self.flags, _lib.current_stream_ptr()))
+        return px.full[half][:, :ids.numel()]
 
     def expand(self, plan, ids, qkvo, ys, deltas, pool_b, t, **kw):
         from .batch_infer import expand_multi

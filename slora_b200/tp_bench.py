@@ -23,7 +23,7 @@ def run(args, dist, rank, world, device):
     H, K, T, L, P = spec.hidden, spec.h_kv, wl.T, spec.layers, args.phys_layers
     tables = tp.TpTables(wl.a_start, wl.a_len, wl.a_loc, wl.a_scaling)
     ops = tp.TpLoraOps(tables, wl.pools_a, wl.pools_b, wl.max_rank, world, rank,
-                       tp.CudaBackend(use_pdl=not args.no_pdl)).prepare(wl.ids)
+                       tp.CudaBackend(use_pdl=not args.no_pdl), peer_exchange=args.tp_exchange == "p2p").prepare(wl.ids)
     dt = wl.dtype
     q = [torch.zeros((T, H // world), dtype=dt, device=device) for _ in range(P)]
     k = [torch.zeros((T, K // world), dtype=dt, device=device) for _ in range(P)]
@@ -41,8 +41,23 @@ def run(args, dist, rank, world, device):
     step()
     torch.cuda.synchronize()
     launches_per_step = sum(sl.launch_counts().values()) - before
-    # (eager on purpose: replaying the step, NCCL all-gathers included, from a CUDA graph measured the same time)
-    run = step
+    graph = None
+    if ops.px is not None and not args.no_graph:
+        # with the exchange over peer memory the step holds no library collective and replays from a CUDA graph
+        # (the exchange kernels keep their sequence numbers on the device); with NCCL all-gathers it runs eagerly
+        s = torch.cuda.Stream()
+        s.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(s):
+            step()
+        torch.cuda.current_stream().wait_stream(s)
+        torch.cuda.synchronize()
+        dist.barrier()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=s):
+            step()
+        torch.cuda.synchronize()
+        dist.barrier()
+    run = graph.replay if graph is not None else step
     for _ in range(max(args.warmup, 3)):
         run()
     torch.cuda.synchronize()
@@ -74,9 +89,10 @@ def run(args, dist, rank, world, device):
             "vs_baseline": None, "dtype": "f16 in, f32 accumulate", "data": "synthetic",
             "config": {"workload": spec.name, "tokens": T, "layers": L, "hidden": H, "kv_width": K,
                        "adapters": spec.n_adapters, "max_rank": wl.max_rank, "phys_layers": P,
-                       "parallelism": f"slora-tp{world}: A rank-sharded, B output-sharded, NCCL all-gather of "
-                                      f"[T, 3R/N] and [T, R/N] per layer",
-                       "l2": "inputs larger than L2", "graph": False, "pdl": not args.no_pdl},
+                       "parallelism": f"slora-tp{world}: A rank-sharded, B output-sharded, [T, 3R/N] and [T, R/N] "
+                                      f"exchanged per layer by " + ("one kernel over peer memory (NVLink stores + flags)"
+                                                                    if ops.px is not None else "NCCL all-gather + regroup"),
+                       "l2": "inputs larger than L2", "graph": graph is not None, "pdl": not args.no_pdl},
             "per_rank_hbm": {"algorithmic_bytes_per_step": per_rank_bytes,
                              "achieved": per_rank_bytes / (elapsed / args.steps) / 1e9, "unit": "GB/s"},
             "exchange_bytes_per_step_per_rank": exch,
@@ -84,5 +100,7 @@ def run(args, dist, rank, world, device):
             "cpu_baseline": None,
         }
         print(json.dumps(line), flush=True)
+    del graph
+    torch.cuda.synchronize()
     dist.barrier()
     dist.destroy_process_group()

@@ -1,0 +1,173 @@
+"""The tensor-parallel exchange of the rank-r intermediates: ``slora_tp_regroup`` (after an all-gather) and
+``slora_tp_exchange`` (one kernel over peer memory), against the plain formula.
+
+On one GPU the N ranks are emulated inside one process: every rank's buffers are ordinary device tensors (addresses all
+valid on the one GPU), the ranks' launches follow each other on one stream, and a rank only waits for flags that
+earlier launches have already raised.  With two or more GPUs the real thing runs as one process per GPU over symmetric
+memory and is compared with the single-GPU operator.
+"""
+import ctypes
+import os
+import socket
+
+import numpy as np
+import pytest
+import torch
+
+import slora_b200 as sl
+from slora_b200 import _lib, tp
+from slora_b200.workloads import make_tables
+from tests.helpers import assert_parity
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+def _expected_full(locals_, ids, slot_rows, N, Rl, nproj):
+    """out[p, t, g*rs + j] = locals_[g][p, t, j] for j < rs."""
+    T = ids.numel()
+    out = torch.zeros((3, T, N * Rl), dtype=locals_[0].dtype)
+    for t in range(T):
+        rs = slot_rows[int(ids[t])]
+        for g in range(N):
+            out[:nproj, t, g * rs:(g + 1) * rs] = locals_[g][:nproj, t, :rs].cpu()
+    return out
+
+
+@pytest.mark.parametrize("nproj", [3, 1])
+def test_regroup_and_exchange_emulated_on_one_gpu(nproj):
+    N, T, Rl = 4, 37, 16
+    ranks = [16, 64, 32, 64, 8 * N]            # full ranks; a rank's slot holds r / N rows
+    slot_rows = [r // N for r in ranks]
+    g = torch.Generator().manual_seed(5)
+    ids = torch.randint(0, len(ranks), (T,), generator=g).to(DEV)
+    a_len = torch.tensor([4 * s for s in slot_rows], dtype=torch.int64, device=DEV)
+    locals_ = [torch.randn((3, T, Rl), generator=g).to(torch.float16).to(DEV) for _ in range(N)]
+    want = _expected_full(locals_, ids.cpu(), slot_rows, N, Rl, nproj)
+
+    # all-gather layout + regroup
+    gathered = torch.stack(locals_)            # [N, 3, T, Rl]
+    out = torch.zeros((3, T, N * Rl), dtype=torch.float16, device=DEV)
+    _lib.check(_lib.lib.slora_tp_regroup(out.data_ptr(), gathered.data_ptr(), ids.data_ptr(), a_len.data_ptr(), N,
+                                         nproj, T, Rl, 3 * T * Rl, len(ranks), _lib.F16, _lib.current_stream_ptr()))
+    torch.cuda.synchronize()
+    assert torch.equal(out.cpu()[:nproj], want[:nproj])
+
+    # exchange: every emulated rank owns a buffer [2, 3, cap, R] and flags [2, N]
+    cap = T + 3
+    fulls = [torch.zeros((2, 3, cap, N * Rl), dtype=torch.float16, device=DEV) for _ in range(N)]
+    flags = [torch.zeros((2, N), dtype=torch.int32, device=DEV) for _ in range(N)]
+    counters = [torch.zeros(1, dtype=torch.int32, device=DEV) for _ in range(N)]
+    seq_states = [torch.zeros(2, dtype=torch.int32, device=DEV) for _ in range(N)]
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    full_ptrs = (ctypes.c_void_p * N)(*[f.data_ptr() for f in fulls])
+    flag_ptrs = (ctypes.c_void_p * N)(*[f.data_ptr() for f in flags])
+
+    def call(rank, half, mode):
+        _lib.check(_lib.lib.slora_tp_exchange(locals_[rank].data_ptr(), full_ptrs, flag_ptrs,
+                                              counters[rank].data_ptr(), status.data_ptr(), ids.data_ptr(),
+                                              a_len.data_ptr(), rank, N, nproj, T, cap, Rl, len(ranks), half,
+                                              seq_states[rank].data_ptr(), mode, _lib.F16, 0,
+                                              _lib.current_stream_ptr()))
+
+    for n, half in enumerate((0, 1, 0), start=1):   # three exchanges: both halves, and a half used a second time
+        for f in fulls:
+            f[half].zero_()
+        for rank in range(N - 1):
+            call(rank, half, 1)                # write + signal; its wait comes later
+        call(N - 1, half, 3)                   # the last rank finds every flag raised
+        for rank in range(N - 1):
+            call(rank, half, 2)
+        torch.cuda.synchronize()
+        assert int(status.item()) == 0
+        done = (n + 1) // 2 if half == 0 else 1
+        for rank in range(N):
+            got = fulls[rank][half][:nproj, :T].cpu()
+            assert torch.equal(got, want[:nproj]), f"rank {rank} exchange {n}"
+            assert flags[rank][half].cpu().tolist() == [done] * N
+            assert int(seq_states[rank][half]) == done
+
+
+def test_exchange_wait_runs_out_without_hanging():
+    """A flag that nobody raises: the bounded wait gives up, the status word says so, the context stays usable."""
+    N, T, Rl = 2, 8, 8
+    ids = torch.zeros(T, dtype=torch.int64, device=DEV)
+    a_len = torch.tensor([4 * Rl], dtype=torch.int64, device=DEV)
+    local = torch.ones((3, T, Rl), dtype=torch.float16, device=DEV)
+    fulls = [torch.zeros((2, 3, T, N * Rl), dtype=torch.float16, device=DEV) for _ in range(N)]
+    flags = [torch.zeros((2, N), dtype=torch.int32, device=DEV) for _ in range(N)]
+    counter = torch.zeros(1, dtype=torch.int32, device=DEV)
+    seq_state = torch.zeros(2, dtype=torch.int32, device=DEV)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    full_ptrs = (ctypes.c_void_p * N)(*[f.data_ptr() for f in fulls])
+    flag_ptrs = (ctypes.c_void_p * N)(*[f.data_ptr() for f in flags])
+    _lib.check(_lib.lib.slora_tp_exchange(local.data_ptr(), full_ptrs, flag_ptrs, counter.data_ptr(),
+                                          status.data_ptr(), ids.data_ptr(), a_len.data_ptr(), 0, N, 1, T, T, Rl, 1, 1,
+                                          seq_state.data_ptr(), 3, _lib.F16, 0, _lib.current_stream_ptr()))  # rank 1 is silent
+    torch.cuda.synchronize()
+    assert int(status.item()) & 8              # SLORA_STATUS_TIMEOUT
+    assert float(fulls[1][1, 0, 0, 0]) == 1.0  # the writes went out all the same
+    assert int((local + 1).sum().item()) == 2 * local.numel()
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _worker(rank, world, port, result_dir):
+    import torch.distributed as dist
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world),
+                      NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", device_id=dev)
+    H, T = 1024, 48
+    ranks = [8, 16, 32, 16]
+    g = torch.Generator().manual_seed(33)
+    ads = [([torch.randn((r, H), generator=g) / 32 for _ in range(4)],
+            [torch.randn((H, r), generator=g) * 0.02 for _ in range(4)]) for r in ranks]
+    x = torch.randn((T, H), generator=g).to(torch.float16)
+    ids = torch.randint(0, len(ranks), (T,), generator=g)
+    a_start, a_len, a_loc = make_tables([r // world for r in ranks], 512, 300 + rank, True)
+    pa = torch.zeros((512, H), dtype=torch.float16)
+    pb = torch.zeros((512, H), dtype=torch.float16)
+    for i, (A, B) in enumerate(ads):
+        ra, rb = tp.shard_adapter(A, B, rank, world, H)
+        loc = a_loc[a_start[i]: a_start[i] + a_len[i]]
+        pa[loc] = ra.to(torch.float16)
+        pb[loc] = rb.to(torch.float16)
+    t = tp.TpTables(a_start.to(dev), a_len.to(dev), a_loc.to(dev),
+                    torch.tensor([16.0 / r for r in ranks], dtype=torch.float16, device=dev))
+    outs = {}
+    for peer in (True, False):                  # the exchange over peer memory, then NCCL all-gather + regroup
+        ops = tp.TpLoraOps(t, [pa.to(dev)], [pb.to(dev)], max(ranks), world, rank, tp.CudaBackend(),
+                           peer_exchange=peer).prepare(ids.to(dev))
+        for rep in range(3):                    # several layers' worth of exchanges on both buffer halves
+            q, k, v, o = (torch.zeros((T, H // world), dtype=torch.float16, device=dev) for _ in range(4))
+            ops.lora_qkv(0, x.to(dev), q, k, v)
+            ops.lora_o(0, x.to(dev), o)
+        torch.cuda.synchronize()
+        ops.plan.check()
+        outs[peer] = torch.stack([q, k, v, o]).cpu()
+    assert torch.equal(outs[True], outs[False])
+    np.save(os.path.join(result_dir, f"rank{rank}.npy"), outs[True].float().numpy())
+    if rank == 0:
+        want = [torch.stack([(x[i].float() @ ads[int(ids[i])][0][p].half().float().T)
+                             @ ads[int(ids[i])][1][p].half().float().T * (16.0 / ranks[int(ids[i])])
+                             for i in range(T)]).numpy() for p in range(4)]
+        np.save(os.path.join(result_dir, "want.npy"), np.stack(want))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_exchange_over_symmetric_memory_on_two_gpus(tmp_path):
+    import torch.multiprocessing as mp
+    world = 2
+    mp.spawn(_worker, args=(world, _free_port(), str(tmp_path)), nprocs=world, join=True)
+    want = np.load(tmp_path / "want.npy")
+    got = np.concatenate([np.load(tmp_path / f"rank{r}.npy") for r in range(world)], axis=2)
+    for p in range(4):
+        assert_parity(got[p], want[p], what=f"tp2 proj {p}")
