@@ -53,8 +53,9 @@ def parse_args():
     ap.add_argument("--pool-rows", type=int, default=None)
     ap.add_argument("--layers", type=int, default=None,
                     help="override the model's layer count (small cases for profiling; not a benchmark number)")
-    ap.add_argument("--tp-exchange", default="p2p", choices=["p2p", "nccl"],
-                    help="tensor-parallel runs: exchange the intermediates over peer memory or with NCCL all-gather")
+    ap.add_argument("--tp-exchange", default="fused", choices=["fused", "p2p", "nccl"],
+                    help="tensor-parallel runs: exchange the intermediates over peer memory from inside the shrink and "
+                         "expand kernels (fused), by one kernel over peer memory (p2p), or with NCCL all-gather")
     ap.add_argument("--prefill", action="store_true",
                     help="secondary line: the segment (prefill) API on long sequences, served by the tensor-core kernels")
     ap.add_argument("--prefill-seqs", type=int, default=8)

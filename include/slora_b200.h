@@ -253,6 +253,33 @@ int slora_tp_exchange(const void* local, void* const* peer_full, int32_t* const*
                       int64_t T, int64_t full_tokens, int part_width, int64_t n_adapters, int half, int32_t* seq_state,
                       int mode, int dtype, unsigned flags, void* stream);
 
+/*
+ * The same exchange without a launch of its own (the pipelined kernels only; SLORA_ERR_SHAPE / SLORA_ERR_ALIGN with
+ * "No suitable kernel" when the layout needs another kernel family - then use slora_lora_shrink_multi +
+ * slora_tp_exchange + slora_lora_expand_multi).
+ *   slora_tp_shrink_push: the planned shrink of slora_lora_shrink_multi whose reduction epilogue stores each result
+ *     into every rank's delta buffer (regrouped columns) instead of a local buffer; the launch's last CTA raises this
+ *     rank's flag on every rank.  part_width = columns per rank (R / n_parts).
+ *   slora_tp_expand_wait: the planned expand of slora_lora_expand_multi reading this rank's delta buffer half; its
+ *     producer warps wait (bounded, ~2 s) for every rank's flag after the grid-dependency wait and before the first
+ *     delta row is copied - adapter rows are already streaming by then; the launch's last CTA counts the exchange
+ *     as done in seq_state.
+ * Buffers, flags, seq_state, half: as for slora_tp_exchange; counter: one zero-initialised int32 per entry point.
+ * The two calls of one exchange must both be made (a rank that pushes must also wait).  T == 0 returns at once.
+ */
+int slora_tp_shrink_push(const void* plan, const int64_t* ids, int nproj, const int* qkvo, int part_width,
+                         const void* x, int64_t x_stride, int h_in, const void* pool_a, int64_t pool_rows,
+                         int64_t pool_stride, const int64_t* start, const int64_t* ranks4, const int64_t* loc,
+                         int64_t n_adapters, int64_t loc_len, int64_t T, void* const* peer_full,
+                         int32_t* const* peer_flags, int32_t* counter, int32_t* seq_state, int my_part, int n_parts,
+                         int half, int64_t full_tokens, int dtype, unsigned flags, void* stream);
+int slora_tp_expand_wait(const void* plan, const int64_t* ids, int nproj, const int* qkvo, void* const* y,
+                         const int64_t* y_stride, const int* h_out, const void* pool_b, int64_t pool_rows,
+                         int64_t pool_stride, const int64_t* start, const int64_t* ranks4, const int64_t* loc,
+                         const void* scales, int64_t n_adapters, int64_t loc_len, int64_t T, void* my_full,
+                         int32_t* my_flags, int32_t* counter, int32_t* seq_state, int my_part, int n_parts, int half,
+                         int64_t full_tokens, int part_width, int dtype, unsigned flags, void* stream);
+
 /* Kernels this process has launched through the library so far, per family:
  * out[0] simple (one CTA per work item), out[1] pipelined (persistent, warp-specialised), out[2] tensor core
  * (tcgen05, long segments), out[3] plan building and table validation.  The counters only ever grow; a caller

@@ -69,6 +69,19 @@ struct TileInfo {
   const int32_t* perm;  // PLAN only
 };
 
+// Tensor-parallel link of a pipelined shrink (writes its result into every rank's delta buffer and signals) or expand
+// (waits for every rank's signal before it reads its delta buffer).  See tp_exchange_kernel for the buffers.
+constexpr int kTpMaxParts = 8;
+struct TpLink {
+  void* full[kTpMaxParts];       // shrink: every rank's delta buffer [2][3][full_tokens][R]
+  int32_t* flags[kTpMaxParts];   // shrink: every rank's flags [2][n_parts]; expand: only flags[my_part] is used
+  int32_t* counter;              // CTA arrival counter of this launch (zero between launches)
+  int32_t* seq_state;            // this rank's exchanges completed per half
+  int64_t full_tokens;
+  int my_part, n_parts, half;
+  int enabled;
+};
+
 struct ShrinkArgs {
   TileSrc src;
   Tables tb;
@@ -88,6 +101,7 @@ struct ShrinkArgs {
   int mma_stage_bytes;  // tensor-core kernel: bytes of one pipeline stage
   int mma_stages;       // tensor-core kernel: pipeline stages
   int mma_ksplit;       // tensor-core kernel: CTAs (one cluster) that split K of one tile
+  TpLink tp;
   int32_t* status;
 };
 
@@ -109,6 +123,7 @@ struct ExpandArgs {
   int rank_mult;
   int piece;  // elements per bulk copy (power of two dividing pool_stride, <= kChunk)
   int mma_stage_bytes;  // tensor-core kernel: bytes of one operand tile [128 x kpad_max]
+  TpLink tp;
   int32_t* status;
 };
 

@@ -85,7 +85,6 @@ __global__ void tp_regroup_kernel(T* __restrict__ out, const T* __restrict__ in,
 // Two alternating halves suffice: a rank reaches its next exchange on half h only after every peer signalled the
 // exchange on the other half in between, which a peer does after the kernels that read half h on it (its expand)
 // have completed.
-constexpr int kTpMaxParts = 8;
 constexpr int kTpTokensPerCta = 16;
 constexpr long long kTpWaitCycles = 4000000000ll;  // about 2 s: ranks drift by host-side jitter, not more
 struct TpExchangeArgs {
@@ -456,7 +455,7 @@ int ensure_dyn_smem(K kernel, int which, size_t smem, size_t static_bytes = 0) {
 
 int run_shrink(const TileSrc& src, const Tables& tb, const void* w, const void* x, int64_t x_stride, int h_in,
                int nproj, const int* qkvo, void* const* delta, int64_t delta_stride, int delta_width, int dtype,
-               unsigned flags, int32_t* status, cudaStream_t stream) {
+               unsigned flags, int32_t* status, cudaStream_t stream, const TpLink* tp = nullptr) {
   int rc = check_common(dtype, tb, w);
   if (rc) return rc;
   if (!x) return fail(SLORA_ERR_NULL, "x is null");
@@ -496,7 +495,11 @@ int run_shrink(const TileSrc& src, const Tables& tb, const void* w, const void* 
   // long segments first go to the tensor-core kernel; the launch below then skips them
   a.src.seg_split = 0;
   SideJoin side_join;
-  if ((src.mode == MODE_SEGMENT || src.mode == MODE_PLAN) && src.seg_split > 0 && mma_enabled() && S == h_in &&
+  if (tp) {
+    a.tp = *tp;
+    a.tp.enabled = 1;
+  }
+  if (!tp && (src.mode == MODE_SEGMENT || src.mode == MODE_PLAN) && src.seg_split > 0 && mma_enabled() && S == h_in &&
       h_in % kMmaKBlock == 0 && src.T < 0x7fffffff) {
     bool consecutive = true;
     for (int p = 1; p < nproj; ++p) consecutive = consecutive && qkvo[p] == qkvo[0] + p;
@@ -549,8 +552,9 @@ int run_shrink(const TileSrc& src, const Tables& tb, const void* w, const void* 
   }
   const bool can_pipe = (S % h_in == 0);
   const KernelChoice choice = kernel_choice();
-  if (choice == CHOOSE_PIPELINED && !can_pipe)
-    return fail(SLORA_ERR_SHAPE, "pipelined shrink needs pool_stride %% h_in == 0");
+  if ((choice == CHOOSE_PIPELINED || tp) && !can_pipe)
+    return fail(SLORA_ERR_SHAPE, "No suitable kernel. pipelined shrink needs pool_stride %% h_in == 0");
+  if (tp && choice == CHOOSE_SIMPLE) return fail(SLORA_ERR_SHAPE, "No suitable kernel. the linked shrink is pipelined only");
   if (can_pipe && choice != CHOOSE_SIMPLE) {
     a.rows_per_cta = kMaxRows;
     a.max_rb = (delta_width + kMaxRows - 1) / kMaxRows;
@@ -593,7 +597,7 @@ int run_shrink(const TileSrc& src, const Tables& tb, const void* w, const void* 
 int run_expand(const TileSrc& src, const Tables& tb, const void* w, const void* scales, int nproj, const int* qkvo,
                void* const* y, const int64_t* y_stride, const int* h_out, const void* const* delta,
                int64_t delta_stride, int delta_width, int delta_parts, int64_t delta_part_stride, int rank_mult,
-               int dtype, unsigned flags, int32_t* status, cudaStream_t stream) {
+               int dtype, unsigned flags, int32_t* status, cudaStream_t stream, const TpLink* tp = nullptr) {
   int rc = check_common(dtype, tb, w);
   if (rc) return rc;
   if (!scales) return fail(SLORA_ERR_NULL, "scales is null");
@@ -638,7 +642,11 @@ int run_expand(const TileSrc& src, const Tables& tb, const void* w, const void* 
   a.status = status;
   a.src.seg_split = 0;
   SideJoin side_join;
-  bool can_mma = (src.mode == MODE_SEGMENT || src.mode == MODE_PLAN) && src.seg_split > 0 && mma_enabled() &&
+  if (tp) {
+    a.tp = *tp;
+    a.tp.enabled = 1;
+  }
+  bool can_mma = !tp && (src.mode == MODE_SEGMENT || src.mode == MODE_PLAN) && src.seg_split > 0 && mma_enabled() &&
                  delta_parts == 1 && rank_mult == 1 && delta_stride % 8 == 0;
   for (int p = 0; p < nproj; ++p)
     can_mma = can_mma && aligned16(y[p]) && y_stride[p] % 8 == 0 && aligned16(delta[p]);
@@ -684,8 +692,10 @@ int run_expand(const TileSrc& src, const Tables& tb, const void* w, const void* 
   for (int p = 0; p < nproj; ++p)
     can_pipe = can_pipe && aligned16(y[p]) && y_stride[p] % 8 == 0 && aligned16(delta[p]);
   const KernelChoice choice = kernel_choice();
-  if (choice == CHOOSE_PIPELINED && !can_pipe)
-    return fail(SLORA_ERR_ALIGN, "pipelined expand needs 16-byte aligned y and delta rows and a plain delta layout");
+  if ((choice == CHOOSE_PIPELINED || tp) && !can_pipe)
+    return fail(SLORA_ERR_ALIGN, "No suitable kernel. pipelined expand needs 16-byte aligned y and delta rows and a "
+                                 "plain delta layout");
+  if (tp && choice == CHOOSE_SIMPLE) return fail(SLORA_ERR_SHAPE, "No suitable kernel. the linked expand is pipelined only");
   if (can_pipe && choice != CHOOSE_SIMPLE) {
     a.piece = pipe_piece;
     set_chunks(kPipeChunk);
@@ -936,6 +946,100 @@ int slora_lora_expand_multi(const void* plan, const int64_t* ids, int nproj, con
   return run_expand(src, make_tables(start, ranks4, loc, n_adapters, loc_len, pool_rows, pool_stride), pool_b,
                     scales, nproj, qkvo, y, y_stride, h_out, delta, delta_stride, delta_width, delta_parts,
                     delta_part_stride, rank_mult, dtype, flags, status, static_cast<cudaStream_t>(stream));
+}
+
+int slora_tp_shrink_push(const void* plan, const int64_t* ids, int nproj, const int* qkvo, int part_width,
+                         const void* x, int64_t x_stride, int h_in, const void* pool_a, int64_t pool_rows,
+                         int64_t pool_stride, const int64_t* start, const int64_t* ranks4, const int64_t* loc,
+                         int64_t n_adapters, int64_t loc_len, int64_t T, void* const* peer_full,
+                         int32_t* const* peer_flags, int32_t* counter, int32_t* seq_state, int my_part, int n_parts,
+                         int half, int64_t full_tokens, int dtype, unsigned flags, void* stream) {
+  if (!qkvo || !peer_full || !peer_flags || !counter || !seq_state) return fail(SLORA_ERR_NULL, "null argument");
+  if (n_parts < 1 || n_parts > kTpMaxParts || my_part < 0 || my_part >= n_parts || half < 0 || half > 1 ||
+      full_tokens < T || part_width < 1)
+    return fail(SLORA_ERR_SHAPE, "tp_shrink_push: bad part, half or buffer size");
+  TpLink tp;
+  memset(&tp, 0, sizeof(tp));
+  for (int g = 0; g < n_parts; ++g) {
+    if (!peer_full[g] || !peer_flags[g]) return fail(SLORA_ERR_NULL, "tp_shrink_push: null peer pointer %d", g);
+    tp.full[g] = peer_full[g];
+    tp.flags[g] = peer_flags[g];
+  }
+  tp.counter = counter;
+  tp.seq_state = seq_state;
+  tp.full_tokens = full_tokens;
+  tp.my_part = my_part;
+  tp.n_parts = n_parts;
+  tp.half = half;
+  TileSrc src;
+  int32_t* status;
+  int rc = make_src(plan, ids, T, n_adapters, 0, &src, &status);
+  if (rc) return rc;
+  if (T == 0) return SLORA_OK;  // every rank sees the same empty batch and skips the exchange
+  void* d[3] = {peer_full[my_part], peer_full[my_part], peer_full[my_part]};  // unused: results go to every rank
+  return run_shrink(src, make_tables(start, ranks4, loc, n_adapters, loc_len, pool_rows, pool_stride), pool_a, x,
+                    x_stride, h_in, nproj, qkvo, d, part_width, part_width, dtype, flags, status,
+                    static_cast<cudaStream_t>(stream), &tp);
+}
+
+int slora_tp_expand_wait(const void* plan, const int64_t* ids, int nproj, const int* qkvo, void* const* y,
+                         const int64_t* y_stride, const int* h_out, const void* pool_b, int64_t pool_rows,
+                         int64_t pool_stride, const int64_t* start, const int64_t* ranks4, const int64_t* loc,
+                         const void* scales, int64_t n_adapters, int64_t loc_len, int64_t T, void* my_full,
+                         int32_t* my_flags, int32_t* counter, int32_t* seq_state, int my_part, int n_parts, int half,
+                         int64_t full_tokens, int part_width, int dtype, unsigned flags, void* stream) {
+  if (!qkvo || !y || !y_stride || !h_out || !my_full || !my_flags || !counter || !seq_state)
+    return fail(SLORA_ERR_NULL, "null argument");
+  if (n_parts < 1 || n_parts > kTpMaxParts || my_part < 0 || my_part >= n_parts || half < 0 || half > 1 ||
+      full_tokens < T || part_width < 1 || nproj < 1 || nproj > 3)
+    return fail(SLORA_ERR_SHAPE, "tp_expand_wait: bad part, half or buffer size");
+  TpLink tp;
+  memset(&tp, 0, sizeof(tp));
+  tp.flags[my_part] = my_flags;
+  tp.counter = counter;
+  tp.seq_state = seq_state;
+  tp.full_tokens = full_tokens;
+  tp.my_part = my_part;
+  tp.n_parts = n_parts;
+  tp.half = half;
+  const int R = n_parts * part_width;
+  const void* d[3];
+  for (int p = 0; p < 3; ++p)
+    d[p] = static_cast<const char*>(my_full) + ((static_cast<int64_t>(half) * 3 + p) * full_tokens) * R * 2;
+  TileSrc src;
+  int32_t* status;
+  int rc = make_src(plan, ids, T, n_adapters, 0, &src, &status);
+  if (rc) return rc;
+  if (T == 0) return SLORA_OK;
+  const Tables tb = make_tables(start, ranks4, loc, n_adapters, loc_len, pool_rows, pool_stride);
+  rc = run_expand(src, tb, pool_b, scales, nproj, qkvo, y, y_stride, h_out, d, R, R, 1, 0, n_parts, dtype, flags,
+                  status, static_cast<cudaStream_t>(stream), &tp);
+  if ((rc == SLORA_ERR_ALIGN || rc == SLORA_ERR_SHAPE) && strstr(g_err, "No suitable kernel")) {
+    // a layout the pipelined expand does not take: nothing has been launched yet; wait for the flags with a
+    // one-CTA launch of the exchange kernel (mode 2), then expand with whatever kernel family fits
+    TpExchangeArgs w;
+    memset(&w, 0, sizeof(w));
+    w.flags[my_part] = my_flags;
+    w.counter = counter;
+    w.status = status;
+    w.my_part = my_part;
+    w.n_parts = n_parts;
+    w.nproj = 1;
+    w.part_width = part_width;
+    w.T = T;
+    w.full_tokens = full_tokens;
+    w.n_adapters = n_adapters;
+    w.seq_state = seq_state;
+    w.half = half;
+    w.mode = 2;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    rc = dtype == SLORA_F16 ? launch(tp_exchange_kernel<__half>, 1, 128, 0, flags, s, w, "tp_exchange")
+                            : launch(tp_exchange_kernel<__nv_bfloat16>, 1, 128, 0, flags, s, w, "tp_exchange");
+    if (rc) return rc;
+    rc = run_expand(src, tb, pool_b, scales, nproj, qkvo, y, y_stride, h_out, d, R, R, 1, 0, n_parts, dtype, flags,
+                    status, s);
+  }
+  return rc;
 }
 
 int slora_batch_lora_qkv(const void* plan, const int64_t* ids, void* q, void* k, void* v, int64_t q_stride,

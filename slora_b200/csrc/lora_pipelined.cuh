@@ -101,10 +101,60 @@ struct Ring {
   bool pre = true;    // still before the grid-dependency wait
   int npend = 0;      // stages with stashed activation copies
   bool dead = false;  // a bounded wait ran out
+  const TpLink* tp = nullptr;  // expand under tensor parallelism: flags to wait for before activations are read
+  int32_t* status = nullptr;
 };
+
+constexpr long long kTpLinkWaitCycles = 4000000000ll;  // about 2 s: ranks drift by host-side jitter, not more
+
+// Expand side of the tensor-parallel link: lanes 0..n_parts-1 wait until every rank's columns of this exchange have
+// landed in this rank's delta buffer.  Bounded; false when the wait ran out.
+__device__ __forceinline__ bool tp_link_wait(const TpLink& tp, int lane) {
+  bool seen = true;
+  if (lane < tp.n_parts) {
+    const int seq = tp.seq_state[tp.half] + 1;
+    const int32_t* flag = tp.flags[tp.my_part] + tp.half * tp.n_parts + lane;
+    const long long t0 = clock64();
+    seen = false;
+    while (!seen) {
+      int v;
+      asm volatile("ld.acquire.sys.global.b32 %0, [%1];" : "=r"(v) : "l"(flag) : "memory");
+      seen = v >= seq;
+      if (!seen && clock64() - t0 > kTpLinkWaitCycles) break;
+    }
+  }
+  return __all_sync(0xffffffffu, seen);
+}
+
+// End of a linked launch: the last CTA to get here either raises this rank's flag on every rank (shrink: all its
+// columns have been written and fenced) or counts the exchange as done (expand: every CTA has read its number).
+__device__ __forceinline__ void tp_link_finish(const TpLink& tp, bool is_shrink) {
+  __shared__ int s_last;
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x == 0) s_last = atomicAdd(tp.counter, 1) == static_cast<int>(gridDim.x) - 1;
+  __syncthreads();
+  if (!s_last) return;
+  const int seq = tp.seq_state[tp.half] + 1;
+  if (threadIdx.x == 0) *tp.counter = 0;
+  __threadfence_system();
+  if (is_shrink) {
+    if (static_cast<int>(threadIdx.x) < tp.n_parts) {
+      asm volatile("st.release.sys.global.b32 [%0], %1;" ::"l"(tp.flags[threadIdx.x] + tp.half * tp.n_parts + tp.my_part),
+                   "r"(seq)
+                   : "memory");
+    }
+  } else if (threadIdx.x == 0) {
+    tp.seq_state[tp.half] = seq;
+  }
+}
 
 __device__ __forceinline__ void ring_flush(Ring& r, PipeCtl& c, int lane) {
   pdl_wait();
+  if (r.tp != nullptr && !tp_link_wait(*r.tp, lane)) {
+    // the copies still go out (the consumers' barriers expect them); the result is flagged as not to be trusted
+    if (lane == 0) set_status(r.status, SLORA_STATUS_TIMEOUT);
+  }
   PipeCtl::Prod& pp = c.prod[r.role];
   for (int i = 0; i < r.npend; ++i) {
     const uint32_t slot = (r.g - r.npend + i) % kSlots;
@@ -266,6 +316,7 @@ __device__ __forceinline__ void shrink_producer(const ShrinkArgs& a, unsigned ch
             pp.d_i[lane][2] = nrows;
             pp.d_i[lane][3] = j0;
             pp.d_i[lane][4] = p;
+            pp.d_i[lane][5] = t.r;
             valid = 1;
           } else {
             set_status(a.status, SLORA_STATUS_BAD_TABLE);
@@ -314,6 +365,7 @@ __device__ __forceinline__ void shrink_producer(const ShrinkArgs& a, unsigned ch
           c.meta[slot][4] = di[4];
           c.meta[slot][5] = klen;
           c.meta[slot][6] = static_cast<int>(off);
+          c.meta[slot][7] = di[5];  // slot rows of the adapter
         } else if (lane >= kMaxRows && lane < kMaxRows + kTileTokens) {
           c.meta[slot][8 + lane - kMaxRows] = mytok;
         }
@@ -447,8 +499,17 @@ __device__ __forceinline__ void shrink_consumer(const ShrinkArgs& a, const unsig
 #pragma unroll
           for (int w = 0; w < kConsumerWarps; ++w) sum += c.red[buf][w][lane];
           if (j < nrows && i < n && m[3] + j < a.delta_width) {
-            T* d = reinterpret_cast<T*>(pick3(a.delta, m[4]));
-            d[static_cast<int64_t>(m[8 + i]) * a.delta_stride + m[3] + j] = from_f32<T>(sum);
+            if (a.tp.enabled) {
+              // tensor parallelism: this rank's rows go straight into every rank's delta buffer (NVLink stores)
+              const int64_t R = static_cast<int64_t>(a.tp.n_parts) * a.delta_width;
+              const int64_t at = ((static_cast<int64_t>(a.tp.half) * 3 + m[4]) * a.tp.full_tokens + m[8 + i]) * R +
+                                 static_cast<int64_t>(a.tp.my_part) * m[7] + m[3] + j;
+              const T v = from_f32<T>(sum);
+              for (int g = 0; g < a.tp.n_parts; ++g) reinterpret_cast<T*>(a.tp.full[g])[at] = v;
+            } else {
+              T* d = reinterpret_cast<T*>(pick3(a.delta, m[4]));
+              d[static_cast<int64_t>(m[8 + i]) * a.delta_stride + m[3] + j] = from_f32<T>(sum);
+            }
           }
         }
         if (lane == 0) c.red_cnt[buf] = 0;
@@ -471,6 +532,7 @@ __global__ void __launch_bounds__(kPipeThreads) lora_shrink_pipe_kernel(const Sh
   } else {
     shrink_consumer<T>(a, ring_mem, ctl, lane, warp - kProducerWarps);
   }
+  if (a.tp.enabled) tp_link_finish(a.tp, true);
 }
 
 // ------------------------------------------------------------------------------------------------------------
@@ -491,6 +553,8 @@ __device__ __forceinline__ void expand_producer(const ExpandArgs& a, unsigned ch
   PipeCtl::Prod& pp = c.prod[role];
   Ring r;
   r.role = role;
+  r.tp = a.tp.enabled ? &a.tp : nullptr;
+  r.status = a.status;
 
   for (int64_t batch0 = blockIdx.x; batch0 < n_items && !r.dead; batch0 += 32 * G) {
     // d_i[lane] = {valid, n, r, p, clen, first output, scale bits, c0, tok[8]}, d_l[lane][j] = pool row of slot row
@@ -717,6 +781,7 @@ __global__ void __launch_bounds__(kPipeThreads) lora_expand_pipe_kernel(const Ex
   } else {
     expand_consumer<T>(a, ring_mem, ctl, lane, warp - kProducerWarps);
   }
+  if (a.tp.enabled) tp_link_finish(a.tp, false);
 }
 
 }  // namespace slora

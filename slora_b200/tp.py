@@ -87,7 +87,7 @@ class PeerExchange:
         self.full_ptrs = (ctypes.c_void_p * world)(*[int(p) for p in h_full.buffer_ptrs])
         self.flag_ptrs = (ctypes.c_void_p * world)(*[int(p) for p in h_flags.buffer_ptrs])
         self._handles = (h_full, h_flags)
-        self.counter = torch.zeros(1, dtype=torch.int32, device=device)
+        self.counter = torch.zeros(4, dtype=torch.int32, device=device)   # one arrival counter per entry point
         self.seq_state = torch.zeros(2, dtype=torch.int32, device=device)   # exchanges done per half (device-kept)
         torch.cuda.synchronize(device)
         dist.barrier(group=group)   # nobody signals before everybody's flags are zero
@@ -141,14 +141,22 @@ class TpLoraOps:
     def lora_qkv(self, layer, x, q_g, k_g, v_g):
         """``q_g/k_g/v_g``: this rank's ``[T, h_out/N]`` slices, updated in place."""
         t = self.t
-        self.backend.shrink(self.plan, self.ids, [0, 1, 2], [self.local[0], self.local[1], self.local[2]], x,
-                            self.pools_a[layer], t)
+        if self.px is not None and getattr(self.backend, "fused", False):
+            # no launch for the exchange: the shrink writes into every rank's buffer, the expand waits for the flags
+            self.backend.shrink_push(self.px, self.plan, self.ids, [0, 1, 2], x, self.pools_a[layer], t, self.Rl, 0)
+            self.backend.expand_wait(self.px, self.plan, self.ids, [0, 1, 2], [q_g, k_g, v_g], self.pools_b[layer], t,
+                                     self.Rl, 0)
+            return
         if self.px is not None:
+            self.backend.shrink(self.plan, self.ids, [0, 1, 2], [self.local[0], self.local[1], self.local[2]], x,
+                                self.pools_a[layer], t)
             full = self.backend.exchange(self.px, self.plan, self.local, self.ids, t, 3, self.Rl, half=0)
             self.backend.expand(self.plan, self.ids, [0, 1, 2], [q_g, k_g, v_g], [full[p] for p in range(3)],
                                 self.pools_b[layer], t, delta_stride=self.R, delta_width=self.R, delta_parts=1,
                                 delta_part_stride=0, rank_mult=self.N)
             return
+        self.backend.shrink(self.plan, self.ids, [0, 1, 2], [self.local[0], self.local[1], self.local[2]], x,
+                            self.pools_a[layer], t)
         gathered, part_stride = self._exchange(3)
         if self.full is not None:
             # regroup once, then the expand reads ordinary delta rows (and may use the pipelined kernels)
@@ -164,6 +172,10 @@ class TpLoraOps:
 
     def lora_o(self, layer, x, o_g):
         t = self.t
+        if self.px is not None and getattr(self.backend, "fused", False):
+            self.backend.shrink_push(self.px, self.plan, self.ids, [3], x, self.pools_a[layer], t, self.Rl, 1)
+            self.backend.expand_wait(self.px, self.plan, self.ids, [3], [o_g], self.pools_b[layer], t, self.Rl, 1)
+            return
         self.backend.shrink(self.plan, self.ids, [3], [self.local[0]], x, self.pools_a[layer], t)
         if self.px is not None:
             full = self.backend.exchange(self.px, self.plan, self.local, self.ids, t, 1, self.Rl, half=1)
@@ -186,9 +198,10 @@ class TpLoraOps:
 class CudaBackend:
     """The local operations of :class:`TpLoraOps` on the CUDA kernels."""
 
-    def __init__(self, use_pdl=False):
+    def __init__(self, use_pdl=False, fused=True):
         from . import _lib
         self.flags = _lib.FLAG_PDL if use_pdl else 0
+        self.fused = fused   # with a PeerExchange: push from the shrink / wait in the expand, no exchange launch
 
     def make_plan(self, ids, t):
         from .batch_infer import BatchPlan
@@ -216,6 +229,32 @@ class CudaBackend:
                                               px.seq_state.data_ptr(), mode, _lib.dtype_code(local.dtype),
                                               self.flags, _lib.current_stream_ptr()))
         return px.full[half][:, :ids.numel()]
+
+    def shrink_push(self, px, plan, ids, qkvo, x, pool_a, t, part_width, half):
+        """Shrink whose results land in every rank's delta buffer (C entry ``slora_tp_shrink_push``)."""
+        import ctypes
+        from . import _lib
+        n = len(qkvo)
+        _lib.check(_lib.lib.slora_tp_shrink_push(
+            0 if plan is None else plan.ptr, ids.data_ptr(), n, (ctypes.c_int * n)(*qkvo), part_width, x.data_ptr(),
+            x.stride(0), x.size(1), pool_a.data_ptr(), pool_a.size(0), pool_a.stride(0), t.a_start.data_ptr(),
+            t.a_len.data_ptr(), t.a_loc.data_ptr(), t.a_start.numel(), t.a_loc.numel(), ids.numel(), px.full_ptrs,
+            px.flag_ptrs, px.counter.data_ptr(), px.seq_state.data_ptr(), px.rank, px.world, half, px.full.shape[2],
+            _lib.dtype_code(x.dtype), self.flags, _lib.current_stream_ptr()))
+
+    def expand_wait(self, px, plan, ids, qkvo, ys, pool_b, t, part_width, half):
+        """Expand that waits for every rank's flag, then reads this rank's buffer (``slora_tp_expand_wait``)."""
+        import ctypes
+        from . import _lib
+        n = len(qkvo)
+        _lib.check(_lib.lib.slora_tp_expand_wait(
+            0 if plan is None else plan.ptr, ids.data_ptr(), n, (ctypes.c_int * n)(*qkvo),
+            (ctypes.c_void_p * n)(*[y.data_ptr() for y in ys]), (ctypes.c_int64 * n)(*[y.stride(0) for y in ys]),
+            (ctypes.c_int * n)(*[y.size(1) for y in ys]), pool_b.data_ptr(), pool_b.size(0), pool_b.stride(0),
+            t.a_start.data_ptr(), t.a_len.data_ptr(), t.a_loc.data_ptr(), t.a_scaling.data_ptr(), t.a_start.numel(),
+            t.a_loc.numel(), ids.numel(), px.full.data_ptr(), px.flags.data_ptr(), px.counter.data_ptr() + 4,
+            px.seq_state.data_ptr(), px.rank, px.world, half, px.full.shape[2], part_width,
+            _lib.dtype_code(ys[0].dtype), self.flags, _lib.current_stream_ptr()))
 
     def expand(self, plan, ids, qkvo, ys, deltas, pool_b, t, **kw):
         from .batch_infer import expand_multi

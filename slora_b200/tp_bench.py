@@ -23,7 +23,8 @@ def run(args, dist, rank, world, device):
     H, K, T, L, P = spec.hidden, spec.h_kv, wl.T, spec.layers, args.phys_layers
     tables = tp.TpTables(wl.a_start, wl.a_len, wl.a_loc, wl.a_scaling)
     ops = tp.TpLoraOps(tables, wl.pools_a, wl.pools_b, wl.max_rank, world, rank,
-                       tp.CudaBackend(use_pdl=not args.no_pdl), peer_exchange=args.tp_exchange == "p2p").prepare(wl.ids)
+                       tp.CudaBackend(use_pdl=not args.no_pdl, fused=args.tp_exchange == "fused"),
+                       peer_exchange=args.tp_exchange != "nccl").prepare(wl.ids)
     dt = wl.dtype
     q = [torch.zeros((T, H // world), dtype=dt, device=device) for _ in range(P)]
     k = [torch.zeros((T, K // world), dtype=dt, device=device) for _ in range(P)]
@@ -90,7 +91,9 @@ def run(args, dist, rank, world, device):
             "config": {"workload": spec.name, "tokens": T, "layers": L, "hidden": H, "kv_width": K,
                        "adapters": spec.n_adapters, "max_rank": wl.max_rank, "phys_layers": P,
                        "parallelism": f"slora-tp{world}: A rank-sharded, B output-sharded, [T, 3R/N] and [T, R/N] "
-                                      f"exchanged per layer by " + ("one kernel over peer memory (NVLink stores + flags)"
+                                      f"exchanged per layer by " + ("peer memory from inside the shrink / expand kernels (NVLink stores + flags)"
+                                                                    if ops.px is not None and args.tp_exchange == "fused"
+                                                                    else "one kernel over peer memory (NVLink stores + flags)"
                                                                     if ops.px is not None else "NCCL all-gather + regroup"),
                        "l2": "inputs larger than L2", "graph": graph is not None, "pdl": not args.no_pdl},
             "per_rank_hbm": {"algorithmic_bytes_per_step": per_rank_bytes,

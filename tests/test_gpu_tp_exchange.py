@@ -123,7 +123,7 @@ def _worker(rank, world, port, result_dir):
     torch.cuda.set_device(rank)
     dev = torch.device("cuda", rank)
     dist.init_process_group("nccl", device_id=dev)
-    H, T = 1024, 48
+    H, T = 4096, 48                            # pool rows of 4096 elements: every kernel of the pipelined family fits
     ranks = [8, 16, 32, 16]
     g = torch.Generator().manual_seed(33)
     ads = [([torch.randn((r, H), generator=g) / 32 for _ in range(4)],
@@ -141,18 +141,24 @@ def _worker(rank, world, port, result_dir):
     t = tp.TpTables(a_start.to(dev), a_len.to(dev), a_loc.to(dev),
                     torch.tensor([16.0 / r for r in ranks], dtype=torch.float16, device=dev))
     outs = {}
-    for peer in (True, False):                  # the exchange over peer memory, then NCCL all-gather + regroup
-        ops = tp.TpLoraOps(t, [pa.to(dev)], [pb.to(dev)], max(ranks), world, rank, tp.CudaBackend(),
+    # peer memory from inside the shrink / expand kernels; one exchange kernel; NCCL all-gather + regroup
+    for kind, (peer, fused) in {"fused": (True, True), "kernel": (True, False), "nccl": (False, False)}.items():
+        ops = tp.TpLoraOps(t, [pa.to(dev)], [pb.to(dev)], max(ranks), world, rank, tp.CudaBackend(fused=fused),
                            peer_exchange=peer).prepare(ids.to(dev))
+        before = sl.launch_counts()
         for rep in range(3):                    # several layers' worth of exchanges on both buffer halves
             q, k, v, o = (torch.zeros((T, H // world), dtype=torch.float16, device=dev) for _ in range(4))
             ops.lora_qkv(0, x.to(dev), q, k, v)
             ops.lora_o(0, x.to(dev), o)
         torch.cuda.synchronize()
         ops.plan.check()
-        outs[peer] = torch.stack([q, k, v, o]).cpu()
-    assert torch.equal(outs[True], outs[False])
-    np.save(os.path.join(result_dir, f"rank{rank}.npy"), outs[True].float().numpy())
+        outs[kind] = torch.stack([q, k, v, o]).cpu()
+        after = sl.launch_counts()
+        if kind == "fused":                     # two launches per call and nothing else: no exchange kernel, no fallback
+            assert after["pipelined"] - before["pipelined"] == 3 * 4 and after["simple"] == before["simple"]
+            assert after["plan"] == before["plan"]
+    assert torch.equal(outs["fused"], outs["nccl"]) and torch.equal(outs["kernel"], outs["nccl"])
+    np.save(os.path.join(result_dir, f"rank{rank}.npy"), outs["fused"].float().numpy())
     if rank == 0:
         want = [torch.stack([(x[i].float() @ ads[int(ids[i])][0][p].half().float().T)
                              @ ads[int(ids[i])][1][p].half().float().T * (16.0 / ranks[int(ids[i])])
