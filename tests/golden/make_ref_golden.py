@@ -63,4 +63,4 @@ def main(out_path):
 
 
 if __name__ == "__main__":
-    main(sys.argv[1] if len(sys.argv) > 1 else os.path.join(ROOT, "gpurun_out", "ref_kernels.npz"))
+    main(sys.argv[1] if len(sys.argv) > 1 else "ref_kernels.npz")
