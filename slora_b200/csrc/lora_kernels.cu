@@ -526,6 +526,11 @@ int run_shrink(const TileSrc& src, const Tables& tb, const void* w, const void* 
     const size_t red_bytes = static_cast<size_t>(kMmaTokens) * (npad_max + 4) * 4;  // split-K partial sums
     if (ks > 1 && smem < red_bytes) smem = red_bytes;
     smem += 1024;
+    // Tensor memory: a CTA takes 128 or 256 of the SM's 512 columns and tcgen05.alloc blocks while they are taken.
+    // CTAs of two clusters blocked on each other's columns would never reach their cluster barriers, so the
+    // shared-memory request is kept large enough that the CTAs that fit on an SM never want more than 512 columns.
+    const size_t min_smem = (npad_max > 128 ? 80 : 48) * 1024;
+    if (smem < min_smem) smem = min_smem;
     const int64_t grid = mma_tiles * m.max_rb * ks;
     CUtensorMap x_map;
     rc = make_tmap(&x_map, dtype, x, h_in, src.T, x_stride, kMmaTokens);
