@@ -50,6 +50,21 @@ class OracleBackend:
             y.copy_(torch.from_numpy(out))
 
 
+class OracleRegroupBackend(OracleBackend):
+    """The same with the regroup step of tp.CudaBackend (slora_tp_regroup), restated in torch."""
+
+    def regroup(self, out, gathered, ids, t, n_parts, nproj, part_width, part_stride):
+        store = torch.as_strided(gathered, (gathered.untyped_storage().nbytes() // gathered.element_size(),), (1,), 0)
+        base = gathered.storage_offset()
+        Tn = ids.numel()
+        for p in range(nproj):
+            for tok in range(Tn):
+                rs = int(t.a_len[int(ids[tok])]) // 4
+                for g in range(n_parts):
+                    src = base + g * part_stride + (p * Tn + tok) * part_width
+                    out[p, tok, g * rs:(g + 1) * rs] = store[src:src + rs]
+
+
 def _logical_adapters(seed):
     g = torch.Generator().manual_seed(seed)
     ads = []
@@ -68,7 +83,7 @@ def _free_port():
     return port
 
 
-def _worker(rank, port, out_dir):
+def _worker(rank, port, out_dir, regroup):
     sys.path.insert(0, ROOT)
     os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
     dist.init_process_group("gloo", rank=rank, world_size=WORLD)
@@ -87,7 +102,8 @@ def _worker(rank, port, out_dir):
     g = torch.Generator().manual_seed(5)
     x_qkv, x_o = torch.randn((T, H), generator=g), torch.randn((T, H), generator=g)
     ids = torch.randint(0, len(RANKS), (T,), generator=g)
-    ops = tp.TpLoraOps(tables, [pool_a], [pool_b], max(RANKS), WORLD, rank, OracleBackend()).prepare(ids)
+    backend = OracleRegroupBackend() if regroup else OracleBackend()
+    ops = tp.TpLoraOps(tables, [pool_a], [pool_b], max(RANKS), WORLD, rank, backend).prepare(ids)
     q, k, v, o = (torch.zeros((T, H // WORLD)) for _ in range(4))
     ops.lora_qkv(0, x_qkv, q, k, v)
     ops.lora_o(0, x_o, o)
@@ -97,8 +113,10 @@ def _worker(rank, port, out_dir):
     dist.destroy_process_group()
 
 
-def test_two_rank_tp_matches_single_rank(tmp_path):
-    mp.spawn(_worker, args=(_free_port(), str(tmp_path)), nprocs=WORLD, join=True)
+@pytest.mark.parametrize("regroup", [False, True])
+def test_two_rank_tp_matches_single_rank(tmp_path, regroup):
+    """regroup=False: the expand reads the gathered [N, nproj, T, R/N] buffer; True: all-gather, regroup, plain rows."""
+    mp.spawn(_worker, args=(_free_port(), str(tmp_path), regroup), nprocs=WORLD, join=True)
     outs = [torch.load(os.path.join(tmp_path, f"rank{r}.pt")) for r in range(WORLD)]
     ads = _logical_adapters(11)
     ids, x_qkv, x_o = outs[0]["ids"], outs[0]["x_qkv"], outs[0]["x_o"]
