@@ -64,7 +64,8 @@ extern "C" {
 /* Bits of the device status word (plan header / status argument). */
 #define SLORA_STATUS_BAD_ID 1      /* a token's adapter id was outside [0, n_adapters) - token skipped   */
 #define SLORA_STATUS_BAD_TABLE 2   /* start/ranks4/loc entry out of range - work item skipped            */
-#define SLORA_STATUS_BAD_RANK 4    /* expand met a rank outside {8,16,32,64,128} - work item skipped      */
+#define SLORA_STATUS_BAD_RANK 4    /* expand met a rank outside {8,16,32,64,128} or wider than the delta
+                                      buffers - work item skipped                                         */
 #define SLORA_STATUS_TIMEOUT 8     /* a bounded wait for a bulk copy ran out - work item skipped          */
 
 int slora_version(void);

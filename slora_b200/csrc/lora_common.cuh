@@ -46,6 +46,7 @@ struct TileSrc {
   int seg_split;          // > 0 when segments (SEGMENT) / groups (PLAN) at least this long go to the tensor-core kernels
   int mma_tiles_per_seg;  // SEGMENT: 128-token tiles enumerated per segment by the tensor-core kernels
   int big_slots;          // PLAN: big-tile slots the tensor-core launch enumerates
+  int mma_max_rows;       // adapters with more slot rows than this (the call's delta width) stay on the CUDA cores
   int64_t T;
 };
 
@@ -121,6 +122,7 @@ struct ExpandArgs {
   int delta_parts;
   int64_t delta_part_stride;
   int rank_mult;
+  int max_rank;  // widest rank the delta buffers hold (delta_width * delta_parts): wider adapters are refused
   int piece;  // elements per bulk copy (power of two dividing pool_stride, <= kChunk)
   int mma_stage_bytes;  // tensor-core kernel: bytes of one operand tile [128 x kpad_max]
   TpLink tp;
@@ -276,7 +278,7 @@ __device__ __forceinline__ bool lookup_tile(const TileSrc& s, const Tables& tb, 
     t.loc_base = r1.x;
     t.perm = s.plan + PH_WORDS + kTileWords * hdr[PH_MAXTILES];
     // big groups an eligible layout lets the tensor-core kernels serve are theirs (same predicate as mma_serves)
-    if (s.seg_split > 0 && r1.y != 0 && tb.pool_stride % t.r == 0) return false;
+    if (s.seg_split > 0 && r1.y != 0 && tb.pool_stride % t.r == 0 && t.r <= s.mma_max_rows) return false;
     return t.n > 0 && t.r > 0;
   }
   int64_t adapter;
@@ -317,7 +319,7 @@ __device__ __forceinline__ bool lookup_tile(const TileSrc& s, const Tables& tb, 
   t.loc_base = st;
   // long segments of an adapter the tensor-core kernels can serve are theirs (same predicate as mma_serves)
   if (s.mode == MODE_SEGMENT && s.seg_split > 0 && s.seg_len[tile_idx / s.tiles_per_seg] >= s.seg_split &&
-      t.r >= 8 && t.r <= 128 && t.r % 8 == 0 && tb.pool_stride % t.r == 0)
+      t.r >= 8 && t.r <= 128 && t.r % 8 == 0 && tb.pool_stride % t.r == 0 && t.r <= s.mma_max_rows)
     return false;
   return t.r > 0;
 }

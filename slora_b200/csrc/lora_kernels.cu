@@ -508,6 +508,7 @@ int run_shrink(const TileSrc& src, const Tables& tb, const void* w, const void* 
     const int npad_max = (gp * wmax + 15) & ~15;
     ShrinkArgs m = a;
     m.src.seg_split = src.seg_split;
+    m.src.mma_max_rows = wmax;
     m.rows_per_cta = gp;
     m.max_rb = nproj / gp;
     m.mma_stage_bytes = kMmaXTileBytes + npad_max * kMmaKBlock * 2;
@@ -551,6 +552,7 @@ int run_shrink(const TileSrc& src, const Tables& tb, const void* w, const void* 
     if (mma_stream != stream) side_join.arm(sd, stream);
     if (rc) return rc;
     a.src.seg_split = src.seg_split;
+    a.src.mma_max_rows = wmax;
     // without a side stream the CUDA-core launch of the same call may still start while the tensor-core kernel
     // runs: neither writes what the other reads before its grid-dependency wait, and their outputs are disjoint
     if (mma_stream == stream) flags |= SLORA_FLAG_PDL;
@@ -644,6 +646,7 @@ int run_expand(const TileSrc& src, const Tables& tb, const void* w, const void* 
   a.delta_parts = delta_parts;
   a.delta_part_stride = delta_part_stride;
   a.rank_mult = rank_mult;
+  a.max_rank = max_rank;
   a.status = status;
   a.src.seg_split = 0;
   SideJoin side_join;
@@ -660,6 +663,7 @@ int run_expand(const TileSrc& src, const Tables& tb, const void* w, const void* 
   if (can_mma) {
     ExpandArgs m = a;
     m.src.seg_split = src.seg_split;
+    m.src.mma_max_rows = delta_width < kMmaMaxRank ? delta_width : kMmaMaxRank;
     m.chunk_begin[0] = 0;
     for (int p = 0; p < nproj; ++p)
       m.chunk_begin[p + 1] = m.chunk_begin[p] + (h_out[p] + kMmaOutPerCta - 1) / kMmaOutPerCta;
@@ -689,6 +693,7 @@ int run_expand(const TileSrc& src, const Tables& tb, const void* w, const void* 
     if (mma_stream != stream) side_join.arm(sd, stream);
     if (rc) return rc;
     a.src.seg_split = src.seg_split;
+    a.src.mma_max_rows = delta_width < kMmaMaxRank ? delta_width : kMmaMaxRank;
     if (mma_stream == stream) flags |= SLORA_FLAG_PDL;  // as in the shrink
   }
   const int pipe_piece = pow2_divisor(tb.pool_stride, kPipeChunk);

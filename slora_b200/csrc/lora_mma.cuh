@@ -248,7 +248,8 @@ __device__ __forceinline__ int64_t mma_token(const MmaTile& t, int i) {
 // May the tensor-core kernels take a segment of `len` tokens whose adapter has `r` slot rows?  The CUDA-core kernels
 // skip exactly the segments for which this holds (TileSrc::seg_split > 0), so the two launches partition the work.
 __device__ __forceinline__ bool mma_serves(const TileSrc& s, const Tables& tb, int64_t len, int64_t r) {
-  return s.seg_split > 0 && len >= s.seg_split && r >= 8 && r <= kMmaMaxRank && r % 8 == 0 && tb.pool_stride % r == 0;
+  return s.seg_split > 0 && len >= s.seg_split && r >= 8 && r <= kMmaMaxRank && r % 8 == 0 && tb.pool_stride % r == 0 &&
+         r <= s.mma_max_rows;
 }
 
 __device__ __forceinline__ bool lookup_mma_tile(const TileSrc& s, const Tables& tb, int tile_idx, MmaTile& t,
@@ -266,7 +267,7 @@ __device__ __forceinline__ bool lookup_mma_tile(const TileSrc& s, const Tables& 
     t.r = r0.w;
     t.loc_base = r1.x;
     t.perm = s.plan + PH_WORDS + kTileWords * hdr[PH_MAXTILES];
-    return t.n > 0 && t.r > 0 && tb.pool_stride % t.r == 0;
+    return t.n > 0 && t.r > 0 && tb.pool_stride % t.r == 0 && t.r <= s.mma_max_rows;
   }
   t.perm = nullptr;
   const int seg = tile_idx / s.mma_tiles_per_seg;

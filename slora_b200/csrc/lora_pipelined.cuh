@@ -574,7 +574,7 @@ __device__ __forceinline__ void expand_producer(const ExpandArgs& a, unsigned ch
         const int64_t flat_total = static_cast<int64_t>(h_out) * rk;
         const int64_t c0 = static_cast<int64_t>(ch) * kPipeChunk;
         if (c0 < flat_total) {
-          if (rk != 8 && rk != 16 && rk != 32 && rk != 64 && rk != 128) {
+          if ((rk != 8 && rk != 16 && rk != 32 && rk != 64 && rk != 128) || rk > a.max_rank) {
             set_status(a.status, SLORA_STATUS_BAD_RANK);
           } else {
             const int clen = static_cast<int>(min(static_cast<int64_t>(kPipeChunk), flat_total - c0));

@@ -245,7 +245,7 @@ __global__ void __launch_bounds__(kThreads) lora_expand_kernel(const ExpandArgs 
   const int64_t flat_total = static_cast<int64_t>(h_out) * r;
   const int64_t c0 = static_cast<int64_t>(c) * kChunk;
   if (c0 >= flat_total) return;
-  if (r != 8 && r != 16 && r != 32 && r != 64 && r != 128) {
+  if ((r != 8 && r != 16 && r != 32 && r != 64 && r != 128) || r > a.max_rank) {
     if (tid == 0) set_status(status, SLORA_STATUS_BAD_RANK);
     return;
   }

@@ -258,6 +258,26 @@ def test_unsupported_inputs_raise():
         sl.dispatch_bgmv(d, x_odd, ka, w.a_start, w.a_len, w.a_loc, w.ids, 0, w.a_scaling)
 
 
+def test_adapter_wider_than_the_delta_buffers_is_refused_not_overread():
+    """Delta buffers of 16 columns, one adapter of rank 64 in the batch: its tokens are skipped by the expand and the
+    status word says so; nothing is read past a delta row; the other tokens are right."""
+    wl = build_workload(3, pool_rows=4096, n_adapters=6, decode_tokens=40, prefill=None, hidden=1024,
+                        rank_choices=(16, 64))
+    assert 64 in [wl.ranks[int(a)] for a in wl.ids] and 16 in [wl.ranks[int(a)] for a in wl.ids]
+    w = wl.to(DEV)
+    ops = sl.LoraBatchOps(w.a_start, w.a_len, w.a_loc, w.a_scaling, w.pools_a, w.pools_b, 16)
+    ops.prepare(w.ids)
+    q, k, v = (torch.zeros((wl.T, 1024), dtype=wl.dtype, device=DEV) for _ in range(3))
+    ops.lora_get_qkv(0, w.x_qkv[0], q, k, v)
+    torch.cuda.synchronize()
+    with pytest.raises(RuntimeError, match="unsupported rank"):
+        ops.plan.check()
+    ref = oracle_layer(wl)
+    narrow = torch.tensor([wl.ranks[int(a)] == 16 for a in wl.ids])
+    assert float(q[~narrow.to(DEV)].abs().max()) == 0.0
+    assert_parity(q[narrow.to(DEV)], ref[0][narrow.numpy()], what="rank-16 tokens beside a refused adapter")
+
+
 def test_tensor_parallel_shards_on_one_gpu():
     """The per-rank shard layout of slora_b200.tp through the real kernels: the N ranks are run one after the other on
     one GPU, their intermediates concatenated the way the all-gather would, and the output slices compared with the
