@@ -281,6 +281,19 @@ int slora_tp_expand_wait(const void* plan, const int64_t* ids, int nproj, const 
                          int32_t* my_flags, int32_t* counter, int32_t* seq_state, int my_part, int n_parts, int half,
                          int64_t full_tokens, int part_width, int dtype, unsigned flags, void* stream);
 
+/*
+ * Adapter load into the Unified-Paging pool: replaces the per-layer indexed copies of InferAdapter.load_lora_A /
+ * load_lora_B (slora/server/router/model_infer/infer_adapter.py:41-90: two index_put launches per layer and adapter)
+ * by one launch for all layers and both buffers.  key_buffers / value_buffers / src are HOST arrays of n_layers device
+ * pointers: src[l] holds the adapter's [2][n_rows][row_bytes] block of layer l (w_combined: A rows, then B rows,
+ * lora_layer_weight.py:215-224); row i goes to pool row loc[i] (device int64) of key_buffers[l] (A) and
+ * value_buffers[l] (B), pool rows being pool_row_bytes apart.  Rows are multiples of 16 bytes.  A loc entry outside
+ * [0, pool_rows) is skipped and SLORA_STATUS_BAD_TABLE is set in *status (device int32, may be NULL).
+ */
+int slora_pool_scatter_rows(void* const* key_buffers, void* const* value_buffers, const void* const* src, int n_layers,
+                            const int64_t* loc, int64_t n_rows, int64_t row_bytes, int64_t pool_rows,
+                            int64_t pool_row_bytes, int32_t* status, void* stream);
+
 /* Kernels this process has launched through the library so far, per family:
  * out[0] simple (one CTA per work item), out[1] pipelined (persistent, warp-specialised), out[2] tensor core
  * (tcgen05, long segments), out[3] plan building and table validation.  The counters only ever grow; a caller

@@ -166,6 +166,34 @@ __global__ void __launch_bounds__(128) tp_exchange_kernel(const TpExchangeArgs a
   if ((a.mode & 2) && tid == 0) a.seq_state[half] = seq;
 }
 
+// Adapter load: rows of one adapter for many layers and both buffers go into the pool in one launch.
+// src[l] is the adapter's [2][n_rows][row_elems] block of layer l (A rows, then B rows); row i lands in pool row
+// loc[i] of key_buffer[l] (A) and value_buffer[l] (B).  One CTA per (row, buffer, layer); 16-byte copies.
+constexpr int kScatterLayers = 64;  // layers per launch (pointer tables travel as kernel arguments)
+struct PoolScatterArgs {
+  void* key[kScatterLayers];
+  void* value[kScatterLayers];
+  const void* src[kScatterLayers];
+  const int64_t* loc;
+  int64_t n_rows, row_bytes, pool_rows, pool_row_bytes;
+  int n_layers;
+  int32_t* status;
+};
+__global__ void __launch_bounds__(256) pool_scatter_kernel(const PoolScatterArgs a) {
+  const int64_t i = blockIdx.x;
+  const int which = blockIdx.y;  // 0: A rows -> key buffer, 1: B rows -> value buffer
+  const int l = blockIdx.z;
+  const int64_t row = a.loc[i];
+  if (row < 0 || row >= a.pool_rows) {
+    if (threadIdx.x == 0) set_status(a.status, SLORA_STATUS_BAD_TABLE);
+    return;
+  }
+  const uint4* src = reinterpret_cast<const uint4*>(static_cast<const char*>(a.src[l]) +
+                                                    (static_cast<int64_t>(which) * a.n_rows + i) * a.row_bytes);
+  uint4* dst = reinterpret_cast<uint4*>(static_cast<char*>(which == 0 ? a.key[l] : a.value[l]) + row * a.pool_row_bytes);
+  for (int64_t c = threadIdx.x; c < a.row_bytes / 16; c += blockDim.x) dst[c] = src[c];
+}
+
 __global__ void zero_report_kernel(int32_t* report) {
   if (threadIdx.x < 4) report[threadIdx.x] = 0;
 }
@@ -1221,6 +1249,43 @@ int slora_tp_exchange(const void* local, void* const* peer_full, int32_t* const*
     rc = launch(tp_exchange_kernel<__nv_bfloat16>, grid, 128, 0, flags, s, a, "tp_exchange");
   }
   return rc;
+}
+
+int slora_pool_scatter_rows(void* const* key_buffers, void* const* value_buffers, const void* const* src, int n_layers,
+                            const int64_t* loc, int64_t n_rows, int64_t row_bytes, int64_t pool_rows,
+                            int64_t pool_row_bytes, int32_t* status, void* stream) {
+  if (n_rows == 0 || n_layers == 0) return SLORA_OK;
+  if (!key_buffers || !value_buffers || !src || !loc) return fail(SLORA_ERR_NULL, "null pointer table or loc");
+  if (n_layers < 0 || n_rows < 0 || n_rows > 0x7fffffff || pool_rows <= 0)
+    return fail(SLORA_ERR_SHAPE, "pool_scatter_rows: bad sizes");
+  if (row_bytes <= 0 || row_bytes % 16 != 0 || pool_row_bytes < row_bytes || pool_row_bytes % 16 != 0)
+    return fail(SLORA_ERR_ALIGN, "pool_scatter_rows: rows must be multiples of 16 bytes and fit a pool row");
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  for (int l0 = 0; l0 < n_layers; l0 += kScatterLayers) {
+    PoolScatterArgs a;
+    memset(&a, 0, sizeof(a));
+    a.n_layers = n_layers - l0 < kScatterLayers ? n_layers - l0 : kScatterLayers;
+    for (int l = 0; l < a.n_layers; ++l) {
+      if (!key_buffers[l0 + l] || !value_buffers[l0 + l] || !src[l0 + l])
+        return fail(SLORA_ERR_NULL, "pool_scatter_rows: null buffer of layer %d", l0 + l);
+      if (!aligned16(key_buffers[l0 + l]) || !aligned16(value_buffers[l0 + l]) || !aligned16(src[l0 + l]))
+        return fail(SLORA_ERR_ALIGN, "pool_scatter_rows: buffer of layer %d is not 16-byte aligned", l0 + l);
+      a.key[l] = key_buffers[l0 + l];
+      a.value[l] = value_buffers[l0 + l];
+      a.src[l] = src[l0 + l];
+    }
+    a.loc = loc;
+    a.n_rows = n_rows;
+    a.row_bytes = row_bytes;
+    a.pool_rows = pool_rows;
+    a.pool_row_bytes = pool_row_bytes;
+    a.status = status;
+    const dim3 grid(static_cast<unsigned>(n_rows), 2, static_cast<unsigned>(a.n_layers));
+    pool_scatter_kernel<<<grid, 256, 0, s>>>(a);
+    const int rc = check_launch("pool_scatter_rows", 1);
+    if (rc) return rc;
+  }
+  return SLORA_OK;
 }
 
 int slora_validate_tables(const int64_t* start, const int64_t* ranks4, const int64_t* loc, const int64_t* ids,

@@ -51,8 +51,48 @@ class InferAdapter:
         )
 
     # -- copy one adapter's rows into the pool ----------------------------------------------------------
+    def _copy_rows_cuda(self, adapter, loc, prefetch):
+        """All layers and both buffers in one launch (C entry ``slora_pool_scatter_rows``).  Returns False when the
+        layout is not one the kernel takes (the caller then copies layer by layer)."""
+        import ctypes
+        from . import _lib
+        mm = self.mem_manager
+        L = len(adapter.layers)
+        row_bytes = mm.head_num * mm.head_dim * mm.key_buffer[0].element_size()
+        blocks = []
+        for layer in adapter.layers:
+            if hasattr(layer, "load_to_gpu"):
+                layer.load_to_gpu(prefetch=prefetch)
+            w = layer.w_combined
+            if w.device != loc.device:
+                w = w.to(loc.device, non_blocking=True)
+            blocks.append(w.contiguous())
+        n = loc.numel()
+        ok = (row_bytes % 16 == 0 and all(b.dtype == mm.key_buffer[0].dtype and b.numel() == 2 * n * mm.head_num * mm.head_dim
+                                          for b in blocks)
+              and all(mm.key_buffer[l].is_contiguous() and mm.value_buffer[l].is_contiguous() for l in range(L)))
+        if ok:
+            arr = ctypes.c_void_p * L
+            loc64 = loc.to(torch.long).contiguous()
+            key = tuple(b.data_ptr() for b in mm.key_buffer[:L]) + tuple(b.data_ptr() for b in mm.value_buffer[:L])
+            cached = getattr(mm, "_pool_ptr_tables", None)
+            if cached is None or cached[0] != key:   # the pool's pointer tables, rebuilt only when the pool changes
+                cached = (key, arr(*key[:L]), arr(*key[L:]))
+                mm._pool_ptr_tables = cached
+            _lib.check(_lib.lib.slora_pool_scatter_rows(
+                cached[1], cached[2], arr(*[b.data_ptr() for b in blocks]), L,
+                loc64.data_ptr(), n, row_bytes, mm.key_buffer[0].size(0), row_bytes, 0, _lib.current_stream_ptr()))
+            for b in blocks:     # the copies above are asynchronous: keep the sources alive on this stream
+                b.record_stream(torch.cuda.current_stream())
+        for layer in adapter.layers:
+            if ok and hasattr(layer, "offload_from_gpu"):
+                layer.offload_from_gpu()
+        return ok
+
     def _copy_rows(self, adapter, loc, prefetch):
         mm = self.mem_manager
+        if loc.is_cuda and self._copy_rows_cuda(adapter, loc, prefetch):
+            return
         for layer_id, layer in enumerate(adapter.layers):
             if hasattr(layer, "load_to_gpu"):
                 layer.load_to_gpu(prefetch=prefetch)
