@@ -255,6 +255,28 @@ int slora_tp_exchange(const void* local, void* const* peer_full, int32_t* const*
                       int mode, int dtype, unsigned flags, void* stream);
 
 /*
+ * Tensor parallelism with a head-sharded input (the o projection after attention: each rank holds x[T, h_in / N]):
+ * A is then sharded over the INPUT dimension - a rank's slot holds the [r, h_in / N] slice of A, flat, in r / N pool
+ * rows - every rank computes a partial [T, r] and the partials are summed (figures/slora_tp.png; the reference has
+ * no code for it).
+ *   slora_lora_shrink_rows: slora_lora_shrink_multi with rank_mult A rows per slot row (rank_mult = N here, h_in the
+ *     shard width; delta_width must hold r).
+ *   slora_tp_allsum: all-reduce (sum) of the partials over peer memory.  Every rank copies its local [T][width] block
+ *     into slot my_part of every rank's parts buffer ([n_parts][full_tokens][width]), signals and waits exactly as
+ *     slora_tp_exchange does (same flags / seq_state / half / counter conventions; o calls use half 1), then a second
+ *     small launch adds the n_parts slots in FP32 and writes out[T][width] in the I/O type.  width % 8 == 0.
+ *     mode: 1 = write and signal, 2 = wait and sum, 3 = both (the normal call).
+ */
+int slora_lora_shrink_rows(const void* plan, const int64_t* ids, int nproj, const int* qkvo, void* const* delta,
+                           int64_t delta_stride, int delta_width, int rank_mult, const void* x, int64_t x_stride,
+                           int h_in, const void* pool_a, int64_t pool_rows, int64_t pool_stride, const int64_t* start,
+                           const int64_t* ranks4, const int64_t* loc, int64_t n_adapters, int64_t loc_len, int64_t T,
+                           int dtype, unsigned flags, void* stream);
+int slora_tp_allsum(const void* local, void* const* peer_parts, int32_t* const* peer_flags, int32_t* counter,
+                    int32_t* status, void* out, int my_part, int n_parts, int64_t T, int64_t full_tokens, int width,
+                    int half, int32_t* seq_state, int mode, int dtype, unsigned flags, void* stream);
+
+/*
  * The same exchange without a launch of its own (the pipelined kernels only; SLORA_ERR_SHAPE / SLORA_ERR_ALIGN with
  * "No suitable kernel" when the layout needs another kernel family - then use slora_lora_shrink_multi +
  * slora_tp_exchange + slora_lora_expand_multi).

@@ -72,16 +72,18 @@ def _slot_flat(pool, loc, base, slot_rows, count):
     return _f32(got).reshape(-1)[:count]
 
 
-def adapter_matrix_A(pool, a_start, a_len, a_loc, adapter, qkvo, h_in):
+def adapter_matrix_A(pool, a_start, a_len, a_loc, adapter, qkvo, h_in, rank_mult=1):
     """``[r, h_in]`` float32 shrink matrix of one adapter/projection, gathered through the tables.
 
     Follows ``bgmv_impl.cuh:34-38``: ``r = a_len[a] / 4``, ``mem_pos = a_start[a] + r * qkvo``,
-    row ``j`` lives in pool row ``a_loc[mem_pos + j]``.
+    row ``j`` lives in pool row ``a_loc[mem_pos + j]``.  ``rank_mult`` > 1 (no counterpart in the reference): the slot
+    holds ``rank_mult`` rows of ``h_in`` elements per pool row (an input-sharded A under tensor parallelism).
     """
     a_start, a_len, a_loc = _i64(a_start), _i64(a_len), _i64(a_loc)
-    r = int(a_len[adapter]) // 4
-    base = int(a_start[adapter]) + r * qkvo
-    return _slot_flat(pool, a_loc, base, r, r * h_in).reshape(r, h_in)
+    slot = int(a_len[adapter]) // 4
+    r = slot * rank_mult
+    base = int(a_start[adapter]) + slot * qkvo
+    return _slot_flat(pool, a_loc, base, slot, r * h_in).reshape(r, h_in)
 
 
 def adapter_matrix_B(pool, a_start, a_len, a_loc, adapter, qkvo, h_out, rank_mult=1):
@@ -97,7 +99,7 @@ def adapter_matrix_B(pool, a_start, a_len, a_loc, adapter, qkvo, h_out, rank_mul
     return _slot_flat(pool, a_loc, base, slot, h_out * r).reshape(h_out, r)
 
 
-def lora_shrink_ref(x, pool, a_start, a_len, a_loc, ids, qkvo, out_width=None):
+def lora_shrink_ref(x, pool, a_start, a_len, a_loc, ids, qkvo, out_width=None, rank_mult=1):
     """Per-token shrink: ``delta[t, :r] = x[t] @ A_{ids[t], qkvo}.T``; columns ``>= r`` stay zero.
 
     The loop is the reference's own (``test_kernel_correctness_multi_rank.py:97-106``, part "A").
@@ -107,13 +109,13 @@ def lora_shrink_ref(x, pool, a_start, a_len, a_loc, ids, qkvo, out_width=None):
     a_len_i = _i64(a_len)
     T, h_in = xf.shape
     if out_width is None:
-        out_width = int(a_len_i.max()) // 4 if a_len_i.size else 0
+        out_width = int(a_len_i.max()) // 4 * rank_mult if a_len_i.size else 0
     out = np.zeros((T, out_width), dtype=np.float32)
     cache = {}
     for t in range(T):
         a = int(ids[t])
         if a not in cache:
-            cache[a] = adapter_matrix_A(pool, a_start, a_len, a_loc, a, qkvo, h_in)
+            cache[a] = adapter_matrix_A(pool, a_start, a_len, a_loc, a, qkvo, h_in, rank_mult)
         A = cache[a]
         r = A.shape[0]
         out[t, :r] = xf[t:t + 1] @ A.T

@@ -74,6 +74,10 @@ _SIGS = {
                                      c_int64, c_int64, _P, _P, _P, _P, c_int, c_int, c_int, c_int64, c_int, c_int,
                                      c_uint, _P]),
     "slora_pool_scatter_rows": (c_int, [_P, _P, _P, c_int, _P, c_int64, c_int64, c_int64, c_int64, _P, _P]),
+    "slora_lora_shrink_rows": (c_int, [_P, _P, c_int, _P, _P, c_int64, c_int, c_int, _P, c_int64, c_int, _P, c_int64,
+                                       c_int64, _P, _P, _P, c_int64, c_int64, c_int64, c_int, c_uint, _P]),
+    "slora_tp_allsum": (c_int, [_P, _P, _P, _P, _P, _P, c_int, c_int, c_int64, c_int64, c_int, c_int, _P, c_int, c_int,
+                                c_uint, _P]),
     "slora_launch_counts": (None, [_P]),
     "slora_plan_big_tiles": (c_int, [_P, _P, _P]),
 }

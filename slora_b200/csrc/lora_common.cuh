@@ -95,6 +95,7 @@ struct ShrinkArgs {
   int nproj;
   int64_t delta_stride;
   int delta_width;
+  int rank_mult;     // A rows per slot row (1 in the reference layout; N when a rank holds [r, h_in / N] slices)
   int max_rb;        // row blocks enumerated per (tile, projection)
   int rows_per_cta;  // <= kMaxRows
   int tok_pass;      // simple kernel: tokens staged per pass

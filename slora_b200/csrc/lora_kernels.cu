@@ -100,7 +100,8 @@ struct TpExchangeArgs {
   int64_t full_tokens;  // token rows per projection in a delta buffer (>= T)
   int32_t* seq_state;
   int half;
-  int mode;  // bit 0: write and signal, bit 1: wait for every rank's signal
+  int mode;  // bit 0: write and signal, bit 1: wait for every rank's signal, bit 2: the write is a plain block copy
+             // of local [T][part_width] into slot my_part of every rank's [n_parts][full_tokens][part_width]
 };
 
 template <typename T>
@@ -116,7 +117,18 @@ __global__ void __launch_bounds__(128) tp_exchange_kernel(const TpExchangeArgs a
   const int seq = a.seq_state[half] + 1;
   const int N = a.n_parts, pw = a.part_width;
   const int64_t R = static_cast<int64_t>(N) * pw;
-  if (a.mode & 1) {
+  if ((a.mode & 5) == 5) {
+    // partial sums travel unchanged: 16-byte copies of this rank's rows into its slot on every rank
+    const int64_t vec_per_row = static_cast<int64_t>(pw) * sizeof(T) / 16;
+    const int64_t total = a.T * vec_per_row;
+    const uint4* src = reinterpret_cast<const uint4*>(a.local);
+    for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + tid; i < total;
+         i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+      const uint4 v = src[i];
+      for (int g = 0; g < N; ++g)
+        reinterpret_cast<uint4*>(a.full[g])[static_cast<int64_t>(a.my_part) * a.full_tokens * vec_per_row + i] = v;
+    }
+  } else if (a.mode & 1) {
     const int p = blockIdx.x % a.nproj;
     const int64_t t0 = static_cast<int64_t>(blockIdx.x / a.nproj) * kTpTokensPerCta;
     const T* local = reinterpret_cast<const T*>(a.local);
@@ -192,6 +204,36 @@ __global__ void __launch_bounds__(256) pool_scatter_kernel(const PoolScatterArgs
                                                     (static_cast<int64_t>(which) * a.n_rows + i) * a.row_bytes);
   uint4* dst = reinterpret_cast<uint4*>(static_cast<char*>(which == 0 ? a.key[l] : a.value[l]) + row * a.pool_row_bytes);
   for (int64_t c = threadIdx.x; c < a.row_bytes / 16; c += blockDim.x) dst[c] = src[c];
+}
+
+// out[i] = sum over ranks of parts[g][i], FP32 accumulation, i over T * width elements (width a multiple of 8).
+template <typename T>
+__global__ void __launch_bounds__(256) tp_sum_parts_kernel(T* __restrict__ out, const T* __restrict__ parts, int n_parts,
+                                                           int64_t tokens, int64_t full_tokens, int width) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int64_t vec_per_row = width / 8;
+  const int64_t total = tokens * vec_per_row;
+  for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
+       i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    float acc[8];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) acc[e] = 0.f;
+    for (int g = 0; g < n_parts; ++g) {
+      const uint4 v = reinterpret_cast<const uint4*>(parts)[static_cast<int64_t>(g) * full_tokens * vec_per_row + i];
+      float f[8];
+      cvt8<T>(v, f);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) acc[e] += f[e];
+    }
+    union {
+      uint4 q;
+      T e[8];
+    } pk;
+#pragma unroll
+    for (int e = 0; e < 8; ++e) pk.e[e] = from_f32<T>(acc[e]);
+    reinterpret_cast<uint4*>(out)[i] = pk.q;
+  }
 }
 
 __global__ void zero_report_kernel(int32_t* report) {
@@ -483,9 +525,10 @@ int ensure_dyn_smem(K kernel, int which, size_t smem, size_t static_bytes = 0) {
 
 int run_shrink(const TileSrc& src, const Tables& tb, const void* w, const void* x, int64_t x_stride, int h_in,
                int nproj, const int* qkvo, void* const* delta, int64_t delta_stride, int delta_width, int dtype,
-               unsigned flags, int32_t* status, cudaStream_t stream, const TpLink* tp = nullptr) {
+               unsigned flags, int32_t* status, cudaStream_t stream, const TpLink* tp = nullptr, int rank_mult = 1) {
   int rc = check_common(dtype, tb, w);
   if (rc) return rc;
+  if (rank_mult < 1) return fail(SLORA_ERR_SHAPE, "rank_mult must be >= 1");
   if (!x) return fail(SLORA_ERR_NULL, "x is null");
   if (nproj < 1 || nproj > 3) return fail(SLORA_ERR_SHAPE, "nproj=%d outside 1..3", nproj);
   if (h_in <= 0 || h_in % 8 != 0 || h_in >= 65536 * 8)
@@ -519,6 +562,7 @@ int run_shrink(const TileSrc& src, const Tables& tb, const void* w, const void* 
   }
   a.delta_stride = delta_stride;
   a.delta_width = delta_width;
+  a.rank_mult = rank_mult;
   a.status = status;
   // long segments first go to the tensor-core kernel; the launch below then skips them
   a.src.seg_split = 0;
@@ -527,7 +571,8 @@ int run_shrink(const TileSrc& src, const Tables& tb, const void* w, const void* 
     a.tp = *tp;
     a.tp.enabled = 1;
   }
-  if (!tp && (src.mode == MODE_SEGMENT || src.mode == MODE_PLAN) && src.seg_split > 0 && mma_enabled() && S == h_in &&
+  if (!tp && rank_mult == 1 && (src.mode == MODE_SEGMENT || src.mode == MODE_PLAN) && src.seg_split > 0 &&
+      mma_enabled() && S == h_in &&
       h_in % kMmaKBlock == 0 && src.T < 0x7fffffff) {
     bool consecutive = true;
     for (int p = 1; p < nproj; ++p) consecutive = consecutive && qkvo[p] == qkvo[0] + p;
@@ -969,6 +1014,21 @@ int slora_lora_shrink_multi(const void* plan, const int64_t* ids, int nproj, con
                     static_cast<cudaStream_t>(stream));
 }
 
+int slora_lora_shrink_rows(const void* plan, const int64_t* ids, int nproj, const int* qkvo, void* const* delta,
+                           int64_t delta_stride, int delta_width, int rank_mult, const void* x, int64_t x_stride,
+                           int h_in, const void* pool_a, int64_t pool_rows, int64_t pool_stride, const int64_t* start,
+                           const int64_t* ranks4, const int64_t* loc, int64_t n_adapters, int64_t loc_len, int64_t T,
+                           int dtype, unsigned flags, void* stream) {
+  if (!qkvo || !delta) return fail(SLORA_ERR_NULL, "qkvo or delta array is null");
+  TileSrc src;
+  int32_t* status;
+  int rc = make_src(plan, ids, T, n_adapters, flags, &src, &status);
+  if (rc) return rc;
+  return run_shrink(src, make_tables(start, ranks4, loc, n_adapters, loc_len, pool_rows, pool_stride), pool_a, x,
+                    x_stride, h_in, nproj, qkvo, delta, delta_stride, delta_width, dtype, flags, status,
+                    static_cast<cudaStream_t>(stream), nullptr, rank_mult);
+}
+
 int slora_lora_expand_multi(const void* plan, const int64_t* ids, int nproj, const int* qkvo, void* const* y,
                             const int64_t* y_stride, const int* h_out, const void* const* delta,
                             int64_t delta_stride, int delta_width, int delta_parts, int64_t delta_part_stride,
@@ -984,6 +1044,71 @@ int slora_lora_expand_multi(const void* plan, const int64_t* ids, int nproj, con
   return run_expand(src, make_tables(start, ranks4, loc, n_adapters, loc_len, pool_rows, pool_stride), pool_b,
                     scales, nproj, qkvo, y, y_stride, h_out, delta, delta_stride, delta_width, delta_parts,
                     delta_part_stride, rank_mult, dtype, flags, status, static_cast<cudaStream_t>(stream));
+}
+
+int slora_tp_allsum(const void* local, void* const* peer_parts, int32_t* const* peer_flags, int32_t* counter,
+                    int32_t* status, void* out, int my_part, int n_parts, int64_t T, int64_t full_tokens, int width,
+                    int half, int32_t* seq_state, int mode, int dtype, unsigned flags, void* stream) {
+  if (T == 0) return SLORA_OK;
+  if ((mode & 3) == 0) return fail(SLORA_ERR_SHAPE, "tp_allsum: mode must hold 1 (write and signal) and/or 2 (wait, sum)");
+  if (dtype != SLORA_F16 && dtype != SLORA_BF16) return fail(SLORA_ERR_DTYPE, "unsupported dtype %d", dtype);
+  if (!local || !peer_parts || !peer_flags || !counter || !seq_state || !out) return fail(SLORA_ERR_NULL, "null argument");
+  if (n_parts < 1 || n_parts > kTpMaxParts || my_part < 0 || my_part >= n_parts || half < 0 || half > 1 || T < 0 ||
+      full_tokens < T || width < 8 || width % 8 != 0)
+    return fail(SLORA_ERR_SHAPE, "tp_allsum: bad part, half, width (a multiple of 8) or buffer size");
+  if (!aligned16(local) || !aligned16(out)) return fail(SLORA_ERR_ALIGN, "tp_allsum: buffers must be 16-byte aligned");
+  TpExchangeArgs a;
+  memset(&a, 0, sizeof(a));
+  a.local = local;
+  for (int g = 0; g < n_parts; ++g) {
+    if (!peer_parts[g] || !peer_flags[g]) return fail(SLORA_ERR_NULL, "tp_allsum: null peer pointer %d", g);
+    if (!aligned16(peer_parts[g])) return fail(SLORA_ERR_ALIGN, "tp_allsum: peer buffer %d is not 16-byte aligned", g);
+    a.full[g] = peer_parts[g];
+    a.flags[g] = peer_flags[g];
+  }
+  a.counter = counter;
+  a.status = status;
+  a.my_part = my_part;
+  a.n_parts = n_parts;
+  a.nproj = 1;
+  a.part_width = width;
+  a.T = T;
+  a.full_tokens = full_tokens;
+  a.seq_state = seq_state;
+  a.half = half;
+  a.mode = (mode & 3) | 4;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const int64_t vecs = T * (static_cast<int64_t>(width) / 8);
+  const int64_t grid = vecs < 128 * 64 ? (vecs + 127) / 128 : 64;
+  int rc = dtype == SLORA_F16 ? launch(tp_exchange_kernel<__half>, grid, 128, 0, flags, s, a, "tp_exchange")
+                              : launch(tp_exchange_kernel<__nv_bfloat16>, grid, 128, 0, flags, s, a, "tp_exchange");
+  if (rc) return rc;
+  if (!(mode & 2)) return SLORA_OK;
+  const int64_t sgrid = vecs < 256 * 148 ? (vecs + 255) / 256 : 148;
+  cudaLaunchConfig_t cfg;
+  memset(&cfg, 0, sizeof(cfg));
+  cfg.gridDim = dim3(static_cast<unsigned>(sgrid), 1, 1);
+  cfg.blockDim = dim3(256, 1, 1);
+  cfg.stream = s;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = (flags & SLORA_FLAG_PDL) ? 1 : 0;
+  cudaError_t e;
+  if (dtype == SLORA_F16) {
+    e = cudaLaunchKernelEx(&cfg, tp_sum_parts_kernel<__half>, static_cast<__half*>(out),
+                           static_cast<const __half*>(peer_parts[my_part]), n_parts, T, full_tokens, width);
+  } else {
+    e = cudaLaunchKernelEx(&cfg, tp_sum_parts_kernel<__nv_bfloat16>, static_cast<__nv_bfloat16*>(out),
+                           static_cast<const __nv_bfloat16*>(peer_parts[my_part]), n_parts, T, full_tokens, width);
+  }
+  if (e != cudaSuccess) {
+    cudaGetLastError();
+    return fail(SLORA_ERR_LAUNCH, "tp_sum_parts: %s", cudaGetErrorString(e));
+  }
+  g_launches[3].fetch_add(1, std::memory_order_relaxed);
+  return SLORA_OK;
 }
 
 int slora_tp_shrink_push(const void* plan, const int64_t* ids, int nproj, const int* qkvo, int part_width,

@@ -295,8 +295,9 @@ __device__ __forceinline__ void shrink_producer(const ShrinkArgs& a, unsigned ch
       TileInfo t;
       if (lookup_tile(a.src, a.tb, tile, t, a.status)) {
         const int j0 = rb * kMaxRows;
-        if (j0 < t.r) {
-          const int nrows = min(kMaxRows, t.r - j0);
+        const int rows_total = t.r * a.rank_mult;  // A rows of the projection (rows may be shorter than a pool row)
+        if (j0 < rows_total) {
+          const int nrows = min(kMaxRows, rows_total - j0);
           const int64_t base = t.loc_base + static_cast<int64_t>(t.r) * pick3(a.qkvo, p);
           bool ok = true;
 #pragma unroll

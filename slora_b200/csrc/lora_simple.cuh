@@ -42,8 +42,9 @@ __global__ void __launch_bounds__(kThreads) lora_shrink_kernel(const ShrinkArgs 
   const int r = t.r;
   const int64_t st = t.loc_base;
   const int j0 = rb * a.rows_per_cta;
-  if (j0 >= r) return;
-  const int nrows = min(a.rows_per_cta, r - j0);
+  const int rows_total = r * a.rank_mult;  // A rows of the projection (rows may be shorter than a pool row)
+  if (j0 >= rows_total) return;
+  const int nrows = min(a.rows_per_cta, rows_total - j0);
   const int64_t base = st + static_cast<int64_t>(r) * a.qkvo[p];
   const int h_in = a.h_in;
   const int64_t S = a.tb.pool_stride;

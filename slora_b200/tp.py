@@ -26,11 +26,14 @@ from typing import List, Sequence
 import torch
 
 
-def shard_adapter(A: Sequence[torch.Tensor], B: Sequence[torch.Tensor], rank: int, world: int, pool_stride: int):
+def shard_adapter(A: Sequence[torch.Tensor], B: Sequence[torch.Tensor], rank: int, world: int, pool_stride: int,
+                  o_input_sharded: bool = False):
     """Rows one adapter contributes to rank ``rank``'s A pool and B pool.
 
     ``A[p]``: ``[r, h_in]``, ``B[p]``: ``[h_out_p, r]`` for p = q, k, v, o.  Returns ``(rows_a, rows_b)``, each
-    ``[4 * r / world, pool_stride]``.
+    ``[4 * r / world, pool_stride]``.  With ``o_input_sharded`` the o projection's A is cut over its INPUT columns
+    instead of its rank rows (the attention output arrives head-sharded): the slot then holds ``A_o[:, g*h/N:(g+1)*h/N]``
+    (``[r, h_in / world]``) flat, and the ranks' partial results are summed (see :meth:`TpLoraOps.lora_o_sharded`).
     """
     r = A[0].shape[0]
     if r % world != 0:
@@ -43,7 +46,13 @@ def shard_adapter(A: Sequence[torch.Tensor], B: Sequence[torch.Tensor], rank: in
             raise ValueError("the A shard needs pool_stride == h_in")
         if h_out % world != 0:
             raise ValueError(f"h_out {h_out} is not divisible by the tensor-parallel size {world}")
-        rows_a.append(A[p][rank * rs:(rank + 1) * rs])
+        if p == 3 and o_input_sharded:
+            if h_in % world != 0:
+                raise ValueError(f"h_in {h_in} is not divisible by the tensor-parallel size {world}")
+            hs = h_in // world
+            rows_a.append(A[p][:, rank * hs:(rank + 1) * hs].reshape(rs, pool_stride))
+        else:
+            rows_a.append(A[p][rank * rs:(rank + 1) * rs])
         ho = h_out // world
         flat = B[p][rank * ho:(rank + 1) * ho].reshape(-1)
         if flat.numel() > rs * pool_stride:
@@ -80,13 +89,17 @@ class PeerExchange:
         self.world, self.rank = world, rank
         self.full = symm_mem.empty((2, 3, max(T, 1), R), dtype=dtype, device=device)
         self.flags = symm_mem.empty((2, world), dtype=torch.int32, device=device)
+        self.parts = symm_mem.empty((world, max(T, 1), R), dtype=dtype, device=device)  # partial sums of the o shrink
         self.full.zero_()
         self.flags.zero_()
+        self.parts.zero_()
         h_full = symm_mem.rendezvous(self.full, group.group_name)
         h_flags = symm_mem.rendezvous(self.flags, group.group_name)
+        h_parts = symm_mem.rendezvous(self.parts, group.group_name)
         self.full_ptrs = (ctypes.c_void_p * world)(*[int(p) for p in h_full.buffer_ptrs])
         self.flag_ptrs = (ctypes.c_void_p * world)(*[int(p) for p in h_flags.buffer_ptrs])
-        self._handles = (h_full, h_flags)
+        self.parts_ptrs = (ctypes.c_void_p * world)(*[int(p) for p in h_parts.buffer_ptrs])
+        self._handles = (h_full, h_flags, h_parts)
         self.counter = torch.zeros(4, dtype=torch.int32, device=device)   # one arrival counter per entry point
         self.seq_state = torch.zeros(2, dtype=torch.int32, device=device)   # exchanges done per half (device-kept)
         torch.cuda.synchronize(device)
@@ -111,6 +124,7 @@ class TpLoraOps:
         self.backend, self.group = backend, group
         self.peer_exchange = peer_exchange and world > 1 and hasattr(backend, "exchange")
         self.px = None
+        self.sum_in = self.sum_out = None
         self.ids = None
 
     def prepare(self, token_adapter_ids: torch.Tensor):
@@ -195,6 +209,27 @@ class TpLoraOps:
                             delta_part_stride=part_stride, rank_mult=self.N)
 
 
+    def lora_o_sharded(self, layer, x_g, o_g):
+        """The o projection with a head-sharded input: ``x_g`` is this rank's ``[T, h_in / N]`` slice of the attention
+        output, the adapters were sharded with ``o_input_sharded=True``.  Every rank computes a partial ``[T, R]``
+        (all rank rows, its input columns), the partials are summed over the ranks (peer memory, or ``all_reduce``),
+        and the output-sharded B gives this rank's ``[T, h_out / N]`` slice as in :meth:`lora_o`."""
+        import torch.distributed as dist
+        t = self.t
+        if self.sum_in is None or self.sum_in.shape[0] != self.ids.numel():
+            self.sum_in = torch.zeros((self.ids.numel(), self.R), dtype=self.local.dtype, device=self.local.device)
+            self.sum_out = torch.zeros_like(self.sum_in)
+        self.backend.shrink(self.plan, self.ids, [3], [self.sum_in], x_g, self.pools_a[layer], t, rank_mult=self.N)
+        if self.px is not None:
+            self.backend.allsum(self.px, self.plan, self.sum_in, self.sum_out, half=1)
+            total = self.sum_out
+        else:
+            dist.all_reduce(self.sum_in, group=self.group)
+            total = self.sum_in
+        self.backend.expand(self.plan, self.ids, [3], [o_g], [total], self.pools_b[layer], t, delta_stride=self.R,
+                            delta_width=self.R, delta_parts=1, delta_part_stride=0, rank_mult=self.N)
+
+
 class CudaBackend:
     """The local operations of :class:`TpLoraOps` on the CUDA kernels."""
 
@@ -207,9 +242,29 @@ class CudaBackend:
         from .batch_infer import BatchPlan
         return BatchPlan(ids, t.a_start, t.a_len, t.a_loc.numel())
 
-    def shrink(self, plan, ids, qkvo, deltas, x, pool_a, t):
+    def shrink(self, plan, ids, qkvo, deltas, x, pool_a, t, rank_mult=1):
         from .batch_infer import shrink_multi
-        shrink_multi(plan, ids, qkvo, deltas, x, pool_a, t.a_start, t.a_len, t.a_loc, self.flags)
+        if rank_mult == 1:
+            shrink_multi(plan, ids, qkvo, deltas, x, pool_a, t.a_start, t.a_len, t.a_loc, self.flags)
+            return
+        import ctypes
+        from . import _lib
+        n = len(qkvo)
+        _lib.check(_lib.lib.slora_lora_shrink_rows(
+            0 if plan is None else plan.ptr, ids.data_ptr(), n, (ctypes.c_int * n)(*qkvo),
+            (ctypes.c_void_p * n)(*[d.data_ptr() for d in deltas]), deltas[0].stride(0), deltas[0].size(1), rank_mult,
+            x.data_ptr(), x.stride(0), x.size(1), pool_a.data_ptr(), pool_a.size(0), pool_a.stride(0),
+            t.a_start.data_ptr(), t.a_len.data_ptr(), t.a_loc.data_ptr(), t.a_start.numel(), t.a_loc.numel(),
+            ids.numel(), _lib.dtype_code(x.dtype), self.flags, _lib.current_stream_ptr()))
+
+    def allsum(self, px, plan, local, out, half):
+        """Sum of every rank's ``local [T, R]`` into ``out`` over peer memory (C entry ``slora_tp_allsum``)."""
+        from . import _lib
+        status = 0 if plan is None else plan.ptr + 8
+        _lib.check(_lib.lib.slora_tp_allsum(local.data_ptr(), px.parts_ptrs, px.flag_ptrs, px.counter.data_ptr() + 8,
+                                            status, out.data_ptr(), px.rank, px.world, local.size(0), px.parts.shape[1],
+                                            local.size(1), half, px.seq_state.data_ptr(), 3, _lib.dtype_code(local.dtype),
+                                            self.flags, _lib.current_stream_ptr()))
 
     def regroup(self, out, gathered, ids, t, n_parts, nproj, part_width, part_stride):
         """``out[p, t, g*rs + j] = gathered[g, p, t, j]`` (C entry ``slora_tp_regroup``)."""

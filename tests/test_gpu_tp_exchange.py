@@ -88,6 +88,86 @@ def test_regroup_and_exchange_emulated_on_one_gpu(nproj):
             assert int(seq_states[rank][half]) == done
 
 
+def test_input_sharded_o_projection_emulated_on_one_gpu():
+    """A cut over its input columns (``rank_mult`` rows per slot row), partial shrinks per rank, the all-sum over
+    (emulated) peer memory, then the output-sharded expand: concatenated slices against the formula."""
+    H, N, T = 1024, 4, 29
+    ranks = [8, 32, 16]
+    g = torch.Generator().manual_seed(8)
+    ads = [([torch.randn((r, H), generator=g) / 32 for _ in range(4)],
+            [torch.randn((H, r), generator=g) * 0.02 for _ in range(4)]) for r in ranks]
+    x = torch.randn((T, H), generator=g).to(torch.float16)
+    ids = torch.randint(0, len(ranks), (T,), generator=g)
+    R, hs = max(ranks), H // N
+    shards = []
+    for rank in range(N):
+        a_start, a_len, a_loc = make_tables([r // N for r in ranks], 256, 500 + rank, True)
+        pa = torch.zeros((256, H), dtype=torch.float16)
+        pb = torch.zeros((256, H), dtype=torch.float16)
+        for i, (A, B) in enumerate(ads):
+            ra, rb = tp.shard_adapter(A, B, rank, N, H, o_input_sharded=True)
+            loc = a_loc[a_start[i]: a_start[i] + a_len[i]]
+            pa[loc] = ra.to(torch.float16)
+            pb[loc] = rb.to(torch.float16)
+        t = tp.TpTables(a_start.to(DEV), a_len.to(DEV), a_loc.to(DEV),
+                        torch.tensor([16.0 / r for r in ranks], dtype=torch.float16, device=DEV))
+        shards.append((t, pa.to(DEV), pb.to(DEV)))
+    be = tp.CudaBackend()
+    idd = ids.to(DEV)
+    partials = []
+    for rank, (t, pa, pb) in enumerate(shards):
+        part = torch.zeros((T, R), dtype=torch.float16, device=DEV)
+        plan = be.make_plan(idd, t)
+        be.shrink(plan, idd, [3], [part], x[:, rank * hs:(rank + 1) * hs].contiguous().to(DEV), pa, t, rank_mult=N)
+        partials.append(part)
+    torch.cuda.synchronize()
+    got_delta = sum(p.float() for p in partials).cpu().numpy()
+    for i in range(T):
+        A = ads[int(ids[i])][0][3].half().float().numpy()
+        ref = x[i].float().numpy() @ A.T
+        assert np.abs(got_delta[i, :A.shape[0]] - ref).max() <= 2e-2 * max(np.abs(ref).max(), 1e-3)
+
+    # all-sum over emulated peer memory: every rank owns parts [N, cap, R] and flags [2, N]
+    cap = T + 5
+    parts = [torch.zeros((N, cap, R), dtype=torch.float16, device=DEV) for _ in range(N)]
+    flags = [torch.zeros((2, N), dtype=torch.int32, device=DEV) for _ in range(N)]
+    counters = [torch.zeros(1, dtype=torch.int32, device=DEV) for _ in range(N)]
+    seq_states = [torch.zeros(2, dtype=torch.int32, device=DEV) for _ in range(N)]
+    outs = [torch.zeros((T, R), dtype=torch.float16, device=DEV) for _ in range(N)]
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    part_ptrs = (ctypes.c_void_p * N)(*[p.data_ptr() for p in parts])
+    flag_ptrs = (ctypes.c_void_p * N)(*[f.data_ptr() for f in flags])
+
+    def call(rank, mode):
+        _lib.check(_lib.lib.slora_tp_allsum(partials[rank].data_ptr(), part_ptrs, flag_ptrs, counters[rank].data_ptr(),
+                                            status.data_ptr(), outs[rank].data_ptr(), rank, N, T, cap, R, 1,
+                                            seq_states[rank].data_ptr(), mode, _lib.F16, 0, _lib.current_stream_ptr()))
+
+    for rank in range(N - 1):
+        call(rank, 1)
+    call(N - 1, 3)
+    for rank in range(N - 1):
+        call(rank, 2)
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0
+    total = sum(p.float() for p in partials).to(torch.float16)
+    for rank in range(N):
+        assert torch.equal(outs[rank], total)
+
+    slices = []
+    for rank, (t, pa, pb) in enumerate(shards):
+        y = torch.zeros((T, H // N), dtype=torch.float16, device=DEV)
+        plan = be.make_plan(idd, t)
+        be.expand(plan, idd, [3], [y], [outs[rank]], pb, t, delta_stride=R, delta_width=R, delta_parts=1,
+                  delta_part_stride=0, rank_mult=N)
+        slices.append(y)
+    torch.cuda.synchronize()
+    got = torch.cat(slices, dim=1)
+    want = torch.stack([(x[i].float() @ ads[int(ids[i])][0][3].half().float().T)
+                        @ ads[int(ids[i])][1][3].half().float().T * (16.0 / ranks[int(ids[i])]) for i in range(T)])
+    assert_parity(got, want.numpy(), what="input-sharded o projection")
+
+
 def test_exchange_wait_runs_out_without_hanging():
     """A flag that nobody raises: the bounded wait gives up, the status word says so, the context stays usable."""
     N, T, Rl = 2, 8, 8
@@ -159,6 +239,27 @@ def _worker(rank, world, port, result_dir):
             assert after["plan"] == before["plan"]
     assert torch.equal(outs["fused"], outs["nccl"]) and torch.equal(outs["kernel"], outs["nccl"])
     np.save(os.path.join(result_dir, f"rank{rank}.npy"), outs["fused"].float().numpy())
+
+    # the o projection with a head-sharded input: partial shrinks summed over peer memory, and by NCCL all_reduce
+    pa2 = torch.zeros((512, H), dtype=torch.float16)
+    for i, (A, B) in enumerate(ads):
+        ra, _ = tp.shard_adapter(A, B, rank, world, H, o_input_sharded=True)
+        pa2[a_loc[a_start[i]: a_start[i] + a_len[i]]] = ra.to(torch.float16)
+    hs = H // world
+    x_g = x[:, rank * hs:(rank + 1) * hs].contiguous().to(dev)
+    o_outs = {}
+    for peer in (True, False):
+        ops = tp.TpLoraOps(t, [pa2.to(dev)], [pb.to(dev)], max(ranks), world, rank, tp.CudaBackend(),
+                           peer_exchange=peer).prepare(ids.to(dev))
+        for rep in range(3):
+            o = torch.zeros((T, H // world), dtype=torch.float16, device=dev)
+            ops.lora_o_sharded(0, x_g, o)
+        torch.cuda.synchronize()
+        ops.plan.check()
+        o_outs[peer] = o.cpu()
+    # (the two sums round differently: FP32 sum rounded once against a 16-bit all_reduce)
+    assert (o_outs[True].float() - o_outs[False].float()).abs().max() <= 2e-2 * o_outs[False].float().abs().max()
+    np.save(os.path.join(result_dir, f"o_sharded_rank{rank}.npy"), o_outs[True].float().numpy())
     if rank == 0:
         want = [torch.stack([(x[i].float() @ ads[int(ids[i])][0][p].half().float().T)
                              @ ads[int(ids[i])][1][p].half().float().T * (16.0 / ranks[int(ids[i])])
@@ -177,3 +278,5 @@ def test_exchange_over_symmetric_memory_on_two_gpus(tmp_path):
     got = np.concatenate([np.load(tmp_path / f"rank{r}.npy") for r in range(world)], axis=2)
     for p in range(4):
         assert_parity(got[p], want[p], what=f"tp2 proj {p}")
+    got_o = np.concatenate([np.load(tmp_path / f"o_sharded_rank{r}.npy") for r in range(world)], axis=1)
+    assert_parity(got_o, want[3], what="tp2 input-sharded o projection")

@@ -25,9 +25,10 @@ class OracleBackend:
     def make_plan(self, ids, t):
         return None
 
-    def shrink(self, plan, ids, qkvo, deltas, x, pool_a, t):
+    def shrink(self, plan, ids, qkvo, deltas, x, pool_a, t, rank_mult=1):
         for p, d in zip(qkvo, deltas):
-            out = orc.lora_shrink_ref(x, pool_a, t.a_start, t.a_len, t.a_loc, ids, p, out_width=d.shape[1])
+            out = orc.lora_shrink_ref(x, pool_a, t.a_start, t.a_len, t.a_loc, ids, p, out_width=d.shape[1],
+                                      rank_mult=rank_mult)
             d.copy_(torch.from_numpy(out))
 
     def expand(self, plan, ids, qkvo, ys, deltas, pool_b, t, delta_stride, delta_width, delta_parts, delta_part_stride,
@@ -83,7 +84,7 @@ def _free_port():
     return port
 
 
-def _worker(rank, port, out_dir, regroup):
+def _worker(rank, port, out_dir, regroup, o_sharded=False):
     sys.path.insert(0, ROOT)
     os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
     dist.init_process_group("gloo", rank=rank, world_size=WORLD)
@@ -94,7 +95,7 @@ def _worker(rank, port, out_dir, regroup):
     pool_a = torch.zeros((pool_rows, H))
     pool_b = torch.zeros((pool_rows, H))
     for i, (A, B) in enumerate(ads):
-        ra, rb = tp.shard_adapter(A, B, rank, WORLD, H)
+        ra, rb = tp.shard_adapter(A, B, rank, WORLD, H, o_input_sharded=o_sharded)
         loc = a_loc[a_start[i]: a_start[i] + a_len[i]]
         pool_a[loc] = ra
         pool_b[loc] = rb
@@ -106,7 +107,11 @@ def _worker(rank, port, out_dir, regroup):
     ops = tp.TpLoraOps(tables, [pool_a], [pool_b], max(RANKS), WORLD, rank, backend).prepare(ids)
     q, k, v, o = (torch.zeros((T, H // WORLD)) for _ in range(4))
     ops.lora_qkv(0, x_qkv, q, k, v)
-    ops.lora_o(0, x_o, o)
+    if o_sharded:   # the attention output arrives head-sharded: this rank sees its columns only
+        hs = H // WORLD
+        ops.lora_o_sharded(0, x_o[:, rank * hs:(rank + 1) * hs].contiguous(), o)
+    else:
+        ops.lora_o(0, x_o, o)
     torch.save({"q": q, "k": k, "v": v, "o": o, "x_qkv": x_qkv, "x_o": x_o, "ids": ids},
                os.path.join(out_dir, f"rank{rank}.pt"))
     dist.barrier()
@@ -126,6 +131,19 @@ def test_two_rank_tp_matches_single_rank(tmp_path, regroup):
         want = torch.stack([(x[t] @ ads[int(ids[t])][0][p].T) @ ads[int(ids[t])][1][p].T * (16.0 / RANKS[int(ids[t])])
                             for t in range(T)])
         np.testing.assert_allclose(got.numpy(), want.numpy(), rtol=1e-4, atol=1e-5)
+
+
+def test_two_rank_tp_with_input_sharded_o_projection(tmp_path):
+    """The o projection with a head-sharded input: A cut over its input columns, partial results summed over the ranks
+    (all_reduce), B output-sharded as before."""
+    mp.spawn(_worker, args=(_free_port(), str(tmp_path), False, True), nprocs=WORLD, join=True)
+    outs = [torch.load(os.path.join(tmp_path, f"rank{r}.pt")) for r in range(WORLD)]
+    ads = _logical_adapters(11)
+    ids, x_o = outs[0]["ids"], outs[0]["x_o"]
+    got = torch.cat([o["o"] for o in outs], dim=1)
+    want = torch.stack([(x_o[t] @ ads[int(ids[t])][0][3].T) @ ads[int(ids[t])][1][3].T * (16.0 / RANKS[int(ids[t])])
+                        for t in range(T)])
+    np.testing.assert_allclose(got.numpy(), want.numpy(), rtol=1e-4, atol=1e-5)
 
 
 def test_shard_adapter_layout():
