@@ -144,9 +144,13 @@ def run_cpu_baseline(cfg, pool_rows, seconds):
     from oracle import cpu_baseline as cb
     wl = cpu_workload(cfg, pool_rows)
     sec_per_layer, reps = cb.time_layer(wl, min_seconds=seconds)
+    sec_grouped, reps_grouped = cb.time_layer(wl, min_seconds=min(seconds, 3.0), fn=cb.grouped_layer)
     L = wl.spec.layers
     return {"value": wl.T / (sec_per_layer * L), "unit": "tokens/s", "cores": torch.get_num_threads(),
             "kind": "port",
+            "grouped_by_adapter": {"value": wl.T / (sec_grouped * L), "unit": "tokens/s",
+                                   "sample": f"same layer, tokens of one adapter multiplied together, {reps_grouped} "
+                                             f"repetitions, {sec_grouped:.3f} s per layer"},
             "sample": f"1 of {L} layers (q,k,v,o over the whole {wl.T}-token batch) x {reps} repetitions, "
                       f"{sec_per_layer:.3f} s per layer, extrapolated x{L}; torch per-token formula, fp32, "
                       f"{torch.get_num_threads()} threads of {os.cpu_count()} cpus"}, wl
@@ -549,6 +553,7 @@ def main():
             "roofline_shrink": roof["lora_pipe_kernel<shrink>(qkv)"],
             "step_hbm": {"algorithmic_bytes_per_step": bytes_layer * run.L, "achieved": step_gbs, "peak": peak_gbs,
                          "frac": step_gbs / peak_gbs, "unit": "GB/s", "peak_kind": peak_kind,
+                         "gathered_bytes_per_step": wl.gathered_bytes_per_layer() * run.L,
                          "frac_of_nominal_8TBs": step_gbs / 8000.0},
             "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": run.launches_per_step * args.steps,
             "clocks": clocks.summary(),
