@@ -28,5 +28,7 @@ extern "C" int ref_dispatch_bgmv(void* y, const void* x, const void* w, const in
   REF_CASE(64, 4096)
   REF_CASE(1024, 16)
   REF_CASE(16, 1024)
+  REF_CASE(5120, 64)
+  REF_CASE(64, 5120)
   return -1;
 }
