@@ -171,3 +171,26 @@ def test_small_batch_below_one_tile():
     for p in (0, 3):
         _, y = _run_segments(wl, w, p)
         assert_parity(y, _oracle(wl, p), what=f"40 tokens proj {p}")
+
+
+def test_empty_and_out_of_range_segments_are_ignored():
+    """Zero-length segments, a segment that runs past the batch and a grid sized for a length no segment has: the
+    valid tokens are computed, everything else is left alone."""
+    wl = build_workload(3, pool_rows=4096, n_adapters=4, decode_tokens=0, prefill=("seqs", 2, 150, 150), hidden=1024,
+                        rank_choices=(16,))
+    w = wl.to(DEV)
+    T = wl.T                                   # 300 tokens: two sequences of 150
+    (s0, n0, a0), (s1, n1, a1) = wl.segments
+    b_start = torch.tensor([s0, 0, s1, s1 + 100], dtype=torch.int32, device=DEV)
+    b_len = torch.tensor([n0, 0, 100, 50 + 77], dtype=torch.int32, device=DEV)      # the last one runs 77 past T
+    req = torch.tensor([a0, a0, a1, a1], dtype=torch.int64, device=DEV)
+    delta = torch.zeros((T, wl.max_rank), dtype=wl.dtype, device=DEV)
+    y = torch.zeros((T, 1024), dtype=wl.dtype, device=DEV)
+    guard = torch.full((64, 1024), 9.0, dtype=wl.dtype, device=DEV)                 # memory right behind nothing we own
+    sl.lora_get_qkvo_fwd_shrink(w.x_qkv[0], w.pools_a[0], delta, w.a_loc, w.a_start, w.a_len, b_start, b_len, req,
+                                1024, 0, wl.max_rank, 1000)
+    sl.lora_get_qkvo_fwd_expand(delta, w.pools_b[0], y, w.a_scaling, w.a_loc, w.a_start, w.a_len, b_start, b_len, req,
+                                1024, 0, wl.max_rank, 1000)
+    torch.cuda.synchronize()
+    assert float(guard.min()) == 9.0
+    assert_parity(y, _oracle(wl, 0), what="ragged segment table")
