@@ -316,6 +316,43 @@ int slora_pool_scatter_rows(void* const* key_buffers, void* const* value_buffers
                             const int64_t* loc, int64_t n_rows, int64_t row_bytes, int64_t pool_rows,
                             int64_t pool_row_bytes, int32_t* status, void* stream);
 
+/*
+ * Row allocation from the pool's free map: replaces MemoryAllocator.alloc (slora/common/mem_allocator.py:30-39: a
+ * cumulative sum over the whole map, a mask and a nonzero, whose result size the host has to wait for).  mem_state is
+ * the map itself (one byte per pool row, non-zero = free; a torch.bool tensor), 16-byte aligned.  The first `need`
+ * free rows, in increasing order, are written to out_rows[0..need) (device int64) and marked used; nothing comes back
+ * to the host, so the call is asynchronous - the caller keeps the count of free rows, as the reference does
+ * (can_use_mem_size).  If the map holds fewer than `need` free rows, those it has are handed out, the remaining
+ * entries are set to -1 and SLORA_STATUS_BAD_TABLE is set in *status (device int32, may be NULL).
+ * workspace: slora_pool_alloc_workspace_bytes(tot_rows) bytes of device memory, contents irrelevant.
+ */
+size_t slora_pool_alloc_workspace_bytes(int64_t tot_rows);
+int slora_pool_alloc_rows(uint8_t* mem_state, int64_t tot_rows, int64_t need, int64_t* out_rows, void* workspace,
+                          size_t workspace_bytes, int32_t* status, void* stream);
+
+/*
+ * MemoryAllocator.free (slora/common/mem_allocator.py:185-199): mem_state[rows[i]] = 1 for i < n.  Rows outside
+ * [0, tot_rows) are skipped with SLORA_STATUS_BAD_TABLE.
+ */
+int slora_pool_free_rows(uint8_t* mem_state, int64_t tot_rows, const int64_t* rows, int64_t n, int32_t* status,
+                         void* stream);
+
+/*
+ * Table compaction after adapters are dropped: replaces the body of InferAdapter.offload_adapters
+ * (slora/server/router/model_infer/infer_adapter.py:186-250: index gathers, a cumulative sum, a Triton
+ * variable-length copy and MemoryAllocator.free) by two launches.  keep[i] != 0 (device bytes) marks the adapters that
+ * stay; they keep their order.  new_len / new_scaling = the kept entries, new_start = exclusive prefix sum of the kept
+ * lengths, new_loc = the kept runs of a_loc back to back; every pool row of a dropped adapter is marked free in
+ * mem_state (skipped when mem_state is NULL).  a_scaling / new_scaling have 2-byte elements.  The new tables are
+ * separate buffers with room for n_adapters / loc_len entries; scratch holds n_adapters int64; counts (device int64[2],
+ * may be NULL) receives the kept adapters and kept rows.  An adapter whose run does not fit in a_loc is neither kept
+ * nor freed and sets SLORA_STATUS_BAD_TABLE.
+ */
+int slora_tables_compact(const int64_t* a_start, const int64_t* a_len, const int64_t* a_loc, const void* a_scaling,
+                         const uint8_t* keep, int64_t n_adapters, int64_t loc_len, int64_t* new_start,
+                         int64_t* new_len, int64_t* new_loc, void* new_scaling, int64_t* scratch, int64_t* counts,
+                         uint8_t* mem_state, int64_t tot_rows, int32_t* status, void* stream);
+
 /* Kernels this process has launched through the library so far, per family:
  * out[0] simple (one CTA per work item), out[1] pipelined (persistent, warp-specialised), out[2] tensor core
  * (tcgen05, long segments), out[3] plan building and table validation.  The counters only ever grow; a caller

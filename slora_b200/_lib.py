@@ -78,6 +78,11 @@ _SIGS = {
                                        c_int64, _P, _P, _P, c_int64, c_int64, c_int64, c_int, c_uint, _P]),
     "slora_tp_allsum": (c_int, [_P, _P, _P, _P, _P, _P, c_int, c_int, c_int64, c_int64, c_int, c_int, _P, c_int, c_int,
                                 c_uint, _P]),
+    "slora_pool_alloc_workspace_bytes": (ctypes.c_size_t, [c_int64]),
+    "slora_pool_alloc_rows": (c_int, [_P, c_int64, c_int64, _P, _P, ctypes.c_size_t, _P, _P]),
+    "slora_pool_free_rows": (c_int, [_P, c_int64, _P, c_int64, _P, _P]),
+    "slora_tables_compact": (c_int, [_P, _P, _P, _P, _P, c_int64, c_int64, _P, _P, _P, _P, _P, _P, _P, c_int64, _P,
+                                     _P]),
     "slora_launch_counts": (None, [_P]),
     "slora_plan_big_tiles": (c_int, [_P, _P, _P]),
 }

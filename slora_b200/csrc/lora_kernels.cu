@@ -19,6 +19,7 @@
 #include "lora_mma.cuh"
 #include "lora_plan.cuh"
 #include "lora_simple.cuh"
+#include "pool_ops.cuh"
 
 using namespace slora;
 
@@ -864,7 +865,7 @@ Tables make_tables(const int64_t* start, const int64_t* ranks4, const int64_t* l
 // ------------------------------------------------------------------------------------------------------------
 extern "C" {
 
-int slora_version(void) { return 101; }
+int slora_version(void) { return 102; }
 
 void slora_launch_counts(int64_t out[4]) {
   for (int i = 0; i < 4; ++i) out[i] = g_launches[i].load(std::memory_order_relaxed);
@@ -1411,6 +1412,76 @@ int slora_pool_scatter_rows(void* const* key_buffers, void* const* value_buffers
     if (rc) return rc;
   }
   return SLORA_OK;
+}
+
+size_t slora_pool_alloc_workspace_bytes(int64_t tot_rows) {
+  if (tot_rows <= 0) return 0;
+  return static_cast<size_t>((tot_rows + kPoolSegRows - 1) / kPoolSegRows) * sizeof(int32_t);
+}
+
+int slora_pool_alloc_rows(uint8_t* mem_state, int64_t tot_rows, int64_t need, int64_t* out_rows, void* workspace,
+                          size_t workspace_bytes, int32_t* status, void* stream) {
+  if (need == 0) return SLORA_OK;
+  if (!mem_state || !out_rows || !workspace) return fail(SLORA_ERR_NULL, "pool_alloc_rows: null free map, output or workspace");
+  if (tot_rows <= 0 || need < 0 || need > tot_rows) return fail(SLORA_ERR_SHAPE, "pool_alloc_rows: bad sizes");
+  if (!aligned16(mem_state)) return fail(SLORA_ERR_ALIGN, "pool_alloc_rows: the free map must be 16-byte aligned");
+  if (workspace_bytes < slora_pool_alloc_workspace_bytes(tot_rows))
+    return fail(SLORA_ERR_WORKSPACE, "pool_alloc_rows: workspace of %zu bytes, %zu needed", workspace_bytes,
+                slora_pool_alloc_workspace_bytes(tot_rows));
+  const int64_t segs = (tot_rows + kPoolSegRows - 1) / kPoolSegRows;
+  if (segs > 0x7fffffff) return fail(SLORA_ERR_SHAPE, "pool_alloc_rows: free map too large");
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  int32_t* seg_free = static_cast<int32_t*>(workspace);
+  pool_count_kernel<<<static_cast<unsigned>(segs), kPoolThreads, 0, s>>>(mem_state, tot_rows, seg_free);
+  pool_take_kernel<<<static_cast<unsigned>(segs), kPoolThreads, 0, s>>>(mem_state, tot_rows, seg_free, need, out_rows,
+                                                                        status);
+  return check_launch("pool_alloc_rows", 2);
+}
+
+int slora_pool_free_rows(uint8_t* mem_state, int64_t tot_rows, const int64_t* rows, int64_t n, int32_t* status,
+                         void* stream) {
+  if (n == 0) return SLORA_OK;
+  if (!mem_state || !rows) return fail(SLORA_ERR_NULL, "pool_free_rows: null free map or row list");
+  if (tot_rows <= 0 || n < 0) return fail(SLORA_ERR_SHAPE, "pool_free_rows: bad sizes");
+  const int64_t blocks = (n + 255) / 256;
+  pool_free_kernel<<<static_cast<unsigned>(blocks < 1184 ? blocks : 1184), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      mem_state, tot_rows, rows, n, status);
+  return check_launch("pool_free_rows", 1);
+}
+
+int slora_tables_compact(const int64_t* a_start, const int64_t* a_len, const int64_t* a_loc, const void* a_scaling,
+                         const uint8_t* keep, int64_t n_adapters, int64_t loc_len, int64_t* new_start,
+                         int64_t* new_len, int64_t* new_loc, void* new_scaling, int64_t* scratch, int64_t* counts,
+                         uint8_t* mem_state, int64_t tot_rows, int32_t* status, void* stream) {
+  if (n_adapters == 0) return SLORA_OK;
+  if (!a_start || !a_len || !a_loc || !a_scaling || !keep || !new_start || !new_len || !new_loc || !new_scaling ||
+      !scratch)
+    return fail(SLORA_ERR_NULL, "tables_compact: null table, output or scratch");
+  if (n_adapters < 0 || loc_len < 0 || (mem_state != nullptr && tot_rows <= 0))
+    return fail(SLORA_ERR_SHAPE, "tables_compact: bad sizes");
+  if (new_loc == a_loc || new_start == a_start || new_len == a_len || new_scaling == a_scaling)
+    return fail(SLORA_ERR_SHAPE, "tables_compact: the new tables must not be the old ones");
+  CompactArgs a;
+  a.a_start = a_start;
+  a.a_len = a_len;
+  a.a_loc = a_loc;
+  a.a_scaling = static_cast<const uint16_t*>(a_scaling);
+  a.keep = keep;
+  a.n_adapters = n_adapters;
+  a.loc_len = loc_len;
+  a.new_start = new_start;
+  a.new_len = new_len;
+  a.new_loc = new_loc;
+  a.new_scaling = static_cast<uint16_t*>(new_scaling);
+  a.dst_off = scratch;
+  a.counts = counts;
+  a.mem_state = mem_state;
+  a.tot = tot_rows;
+  a.status = status;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  tables_scan_kernel<<<1, kPoolThreads, 0, s>>>(a);
+  tables_move_kernel<<<static_cast<unsigned>((n_adapters + 7) / 8), 256, 0, s>>>(a);
+  return check_launch("tables_compact", 2);
 }
 
 int slora_validate_tables(const int64_t* start, const int64_t* ranks4, const int64_t* loc, const int64_t* ids,

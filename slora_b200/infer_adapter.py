@@ -8,14 +8,16 @@ adapter, ``a_start[i]`` / ``a_len[i]`` (= ``4 * r``) delimit adapter ``i``'s run
 ``w_combined[1]`` (B rows) into ``value_buffer[l]``; ``offload_adapters`` frees rows and compacts the tables.
 
 Mechanism differs from the reference: table entries are assembled on the host and uploaded in one copy per table
-(the reference writes them element by element from Python), and compaction is a single gather with an index vector
-(the reference launches a Triton variable-length copy).  An adapter object needs ``lora_dir``, ``r``, ``scaling``
+(the reference writes them element by element from Python); on a CUDA pool the rows of an adapter go into all layers
+with one launch (``slora_pool_scatter_rows``) and dropping adapters is two launches (``slora_tables_compact``: new
+tables and the freed rows, where the reference runs index gathers, a cumulative sum, a Triton variable-length copy
+and an indexed store) with nothing read back to the host.  A CPU pool does the same with torch index ops.  An adapter object needs ``lora_dir``, ``r``, ``scaling``
 and ``layers[l]`` with ``w_combined`` (``[2, 4r, heads, head_dim]``) plus optional ``load_to_gpu`` /
 ``offload_from_gpu`` (``slora/models/peft/layer_weights/lora_layer_weight.py:230-261``).
 """
 from __future__ import annotations
 
-from dataclasses import dataclass
+from dataclasses import dataclass, field
 from typing import Any, Dict, List
 
 import torch
@@ -33,6 +35,7 @@ class InferAdapter:
     prefetch_tag: Dict[str, int]
     cur_tag: int
     prefetch_stream: Any
+    host_lens: List[int] = field(default_factory=list)   # a_len as the host last wrote it (spares a read-back)
 
     @classmethod
     def init(cls, mem_manager, prefetch_stream=None):
@@ -139,6 +142,8 @@ class InferAdapter:
             starts.append(loc_offset + cum)
             lens.append(adapter.r * 4)
             cum += adapter.r * 4
+        if len(self.host_lens) == len(self.adapter_dirs) - len(new_adapters):
+            self.host_lens = self.host_lens + lens
         self.a_start = torch.cat((self.a_start, torch.tensor(starts, dtype=torch.long, device=dev)))
         self.a_len = torch.cat((self.a_len, torch.tensor(lens, dtype=torch.long, device=dev)))
         self.a_loc = torch.cat((self.a_loc, new_loc.to(torch.long)))
@@ -165,11 +170,17 @@ class InferAdapter:
             self.a_len = torch.empty(0, dtype=torch.long, device=dev)
             self.a_scaling = torch.empty(0, dtype=self.a_scaling.dtype, device=dev)
             self.idx_map = {}
+            self.host_lens = []
             return
         reserve = set(reserve_adapter_dirs)
         keep = [i for i, d in enumerate(self.adapter_dirs)
                 if d in reserve or self.prefetch_tag.get(d, None) == self.cur_tag]
         if len(keep) == len(self.adapter_dirs):
+            return
+        if len(self.host_lens) != len(self.adapter_dirs):    # tables were replaced behind our back: read them
+            self.host_lens = self.a_len.tolist()
+        if dev.type == "cuda" and self.a_scaling.element_size() == 2:
+            self._compact_cuda(keep)
             return
         starts = self.a_start.tolist()
         lens = self.a_len.tolist()
@@ -190,6 +201,40 @@ class InferAdapter:
         self.a_start = torch.tensor(new_starts, dtype=torch.long, device=dev)
         self.adapter_dirs = [self.adapter_dirs[i] for i in keep]
         self.idx_map = {d: i for i, d in enumerate(self.adapter_dirs)}
+        self.host_lens = new_lens
+
+    def _compact_cuda(self, keep):
+        """New tables and freed rows in two launches (C entry ``slora_tables_compact``); sizes come from the host's
+        copy of the lengths, nothing is read back."""
+        from . import _lib
+        mm = self.mem_manager
+        dev = self.a_loc.device
+        n = len(self.adapter_dirs)
+        new_lens = [self.host_lens[i] for i in keep]
+        kept_rows = sum(new_lens)
+        flags = bytearray(n)
+        for i in keep:
+            flags[i] = 1
+        keep_t = torch.frombuffer(flags, dtype=torch.uint8).to(dev, non_blocking=False)
+        new_start = torch.empty((len(keep),), dtype=torch.long, device=dev)
+        new_len = torch.empty((len(keep),), dtype=torch.long, device=dev)
+        new_loc = torch.empty((kept_rows,), dtype=torch.long, device=dev)
+        new_scaling = torch.empty((len(keep),), dtype=self.a_scaling.dtype, device=dev)
+        scratch = torch.empty((n,), dtype=torch.long, device=dev)
+        if getattr(mm, "status", None) is None:
+            mm.status = torch.zeros((1,), dtype=torch.int32, device=dev)
+        a_start, a_len, a_loc, a_scaling = (t.contiguous() for t in (self.a_start, self.a_len, self.a_loc,
+                                                                      self.a_scaling))
+        _lib.check(_lib.lib.slora_tables_compact(
+            a_start.data_ptr(), a_len.data_ptr(), a_loc.data_ptr(), a_scaling.data_ptr(), keep_t.data_ptr(), n,
+            a_loc.numel(), new_start.data_ptr(), new_len.data_ptr(), new_loc.data_ptr(), new_scaling.data_ptr(),
+            scratch.data_ptr(), 0, mm.mem_state.data_ptr(), mm.tot_size, mm.status.data_ptr(),
+            _lib.current_stream_ptr()))
+        mm.can_use_mem_size += sum(self.host_lens) - kept_rows
+        self.a_start, self.a_len, self.a_loc, self.a_scaling = new_start, new_len, new_loc, new_scaling
+        self.adapter_dirs = [self.adapter_dirs[i] for i in keep]
+        self.idx_map = {d: i for i, d in enumerate(self.adapter_dirs)}
+        self.host_lens = new_lens
 
 
 class _NullCtx:
