@@ -60,6 +60,9 @@ def parse_args():
                     help="secondary line: the segment (prefill) API on long sequences, served by the tensor-core kernels")
     ap.add_argument("--prefill-seqs", type=int, default=8)
     ap.add_argument("--prefill-len", type=int, default=512)
+    ap.add_argument("--adapter-swap", action="store_true",
+                    help="secondary line: pool row allocation, adapter load and offload, the library's kernels beside "
+                         "the same steps on torch ops (slora_b200/pool_bench.py)")
     return ap.parse_args()
 
 
@@ -485,6 +488,11 @@ def main():
     peak_gbs, peak_kind = load_peaks()
     if args.prefill:
         prefill_bench(args, device, peak_gbs=load_peaks())
+        return
+    if args.adapter_swap:
+        from slora_b200 import pool_bench
+        if rank == 0:
+            print(json.dumps(pool_bench.run()), flush=True)
         return
     run = Runner(args, args.config, device, seed_shift=rank)
     wl = run.wl

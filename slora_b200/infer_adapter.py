@@ -61,32 +61,40 @@ class InferAdapter:
         from . import _lib
         mm = self.mem_manager
         L = len(adapter.layers)
+        dev, dt = loc.device, mm.key_buffer[0].dtype
         row_bytes = mm.head_num * mm.head_dim * mm.key_buffer[0].element_size()
-        blocks = []
+        n = loc.numel()
+        want = 2 * n * mm.head_num * mm.head_dim
+        blocks, ptrs = [], []
+        ok = row_bytes % 16 == 0
         for layer in adapter.layers:
             if hasattr(layer, "load_to_gpu"):
                 layer.load_to_gpu(prefetch=prefetch)
             w = layer.w_combined
-            if w.device != loc.device:
-                w = w.to(loc.device, non_blocking=True)
-            blocks.append(w.contiguous())
-        n = loc.numel()
-        ok = (row_bytes % 16 == 0 and all(b.dtype == mm.key_buffer[0].dtype and b.numel() == 2 * n * mm.head_num * mm.head_dim
-                                          for b in blocks)
-              and all(mm.key_buffer[l].is_contiguous() and mm.value_buffer[l].is_contiguous() for l in range(L)))
-        if ok:
+            if w.device != dev:
+                w = w.to(dev, non_blocking=True)
+            if not w.is_contiguous():
+                w = w.contiguous()
+            ok = ok and w.dtype == dt and w.numel() == want
+            blocks.append(w)
+            ptrs.append(w.data_ptr())
+        # the pool's pointer tables are rebuilt only when the allocator has new buffer lists (reset_all_pool)
+        cached = getattr(mm, "_pool_ptr_tables", None)
+        if cached is None or cached[0] is not mm.key_buffer or cached[1] is not mm.value_buffer or cached[2] != L:
             arr = ctypes.c_void_p * L
-            loc64 = loc.to(torch.long).contiguous()
-            key = tuple(b.data_ptr() for b in mm.key_buffer[:L]) + tuple(b.data_ptr() for b in mm.value_buffer[:L])
-            cached = getattr(mm, "_pool_ptr_tables", None)
-            if cached is None or cached[0] != key:   # the pool's pointer tables, rebuilt only when the pool changes
-                cached = (key, arr(*key[:L]), arr(*key[L:]))
-                mm._pool_ptr_tables = cached
+            contiguous = all(mm.key_buffer[l].is_contiguous() and mm.value_buffer[l].is_contiguous() for l in range(L))
+            cached = (mm.key_buffer, mm.value_buffer, L, arr(*[b.data_ptr() for b in mm.key_buffer[:L]]),
+                      arr(*[b.data_ptr() for b in mm.value_buffer[:L]]), contiguous, arr)
+            mm._pool_ptr_tables = cached
+        ok = ok and cached[5]
+        if ok:
+            loc64 = loc if loc.dtype == torch.long and loc.is_contiguous() else loc.to(torch.long).contiguous()
             _lib.check(_lib.lib.slora_pool_scatter_rows(
-                cached[1], cached[2], arr(*[b.data_ptr() for b in blocks]), L,
-                loc64.data_ptr(), n, row_bytes, mm.key_buffer[0].size(0), row_bytes, 0, _lib.current_stream_ptr()))
+                cached[3], cached[4], cached[6](*ptrs), L, loc64.data_ptr(), n, row_bytes, mm.key_buffer[0].size(0),
+                row_bytes, 0, _lib.current_stream_ptr()))
+            stream = torch.cuda.current_stream()
             for b in blocks:     # the copies above are asynchronous: keep the sources alive on this stream
-                b.record_stream(torch.cuda.current_stream())
+                b.record_stream(stream)
         for layer in adapter.layers:
             if ok and hasattr(layer, "offload_from_gpu"):
                 layer.offload_from_gpu()
