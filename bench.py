@@ -51,6 +51,8 @@ def parse_args():
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--cpu-seconds", type=float, default=10.0)
     ap.add_argument("--pool-rows", type=int, default=None)
+    ap.add_argument("--adapters", type=int, default=None,
+                    help="resident adapters, when fewer than the configuration's (small cases for the profiler)")
     ap.add_argument("--layers", type=int, default=None,
                     help="override the model's layer count (small cases for profiling; not a benchmark number)")
     ap.add_argument("--tp-exchange", default="fused", choices=["fused", "p2p", "nccl"],
@@ -205,7 +207,8 @@ class Runner:
         from slora_b200.workloads import build_workload
         self.sl = sl
         self.args = args
-        wl = build_workload(cfg, device=device, phys_layers=args.phys_layers, pool_rows=args.pool_rows)
+        wl = build_workload(cfg, device=device, phys_layers=args.phys_layers, pool_rows=args.pool_rows,
+                            n_adapters=args.adapters)
         if seed_shift:
             # replicas serve different batches: redraw the per-token adapter ids
             from slora_b200.workloads import build_batch
