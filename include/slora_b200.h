@@ -61,6 +61,15 @@ extern "C" {
                                    path rounds scale * sum to the I/O type and adds it to y in that type, as the
                                    reference's kernels do). */
 
+#define SLORA_FLAG_EXACT_ITEMS 4u /* planned calls: count each tile's work items from its adapter's rank instead of
+                                    enumerating, per tile, the slots of the widest rank and skipping the empty ones.
+                                    A hint about speed, never about results: worth setting when the batch's adapters
+                                    differ in rank, or are all narrower than the delta buffers (slora_plan_info tells)
+                                    - the CTAs' shares are then equal (measured: 15 % less time per layer on a
+                                    rank-16/32/64 mix, 30 % on a rank-8..64 mix); with one rank that fills the delta
+                                    buffers the plain enumeration is exact already and starts a few hundred
+                                    nanoseconds sooner. */
+
 /* Bits of the device status word (plan header / status argument). */
 #define SLORA_STATUS_BAD_ID 1      /* a token's adapter id was outside [0, n_adapters) - token skipped   */
 #define SLORA_STATUS_BAD_TABLE 2   /* start/ranks4/loc entry out of range - work item skipped            */
@@ -143,6 +152,12 @@ int slora_plan_build(void* workspace, size_t workspace_bytes, const int64_t* ids
  * prefill kernels on the host from the request lengths (lora_unordered_batch_infer.py:127-130).
  */
 int slora_plan_big_tiles(const void* workspace, int* n_big_out, void* stream);
+/*
+ * What a plan holds, for the caller's choice of flags: its 8-token tiles, its 128-token tiles of big groups (as
+ * slora_plan_big_tiles) and the slot rows (rank) shared by every adapter of the batch, 0 when they differ.  Any of
+ * the three pointers may be NULL.  Reads the plan header back: synchronises `stream`.
+ */
+int slora_plan_info(const void* workspace, int* n_tiles_out, int* n_big_out, int* uniform_rank_out, void* stream);
 
 int slora_plan_status(const void* workspace, int* status_out, int* n_tiles_out, void* stream);
 

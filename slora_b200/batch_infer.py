@@ -59,6 +59,14 @@ class BatchPlan:
         _lib.check(_lib.lib.slora_plan_big_tiles(self.ptr, ctypes.byref(n), _lib.current_stream_ptr()))
         return n.value
 
+    def info(self):
+        """``(tiles, big_tiles, uniform_rank)``: 8-token tiles, 128-token tiles of big groups, and the rank shared by
+        every adapter of the batch (0 when they differ) -- synchronises the stream."""
+        nt, nb, ur = ctypes.c_int(0), ctypes.c_int(0), ctypes.c_int(0)
+        _lib.check(_lib.lib.slora_plan_info(self.ptr, ctypes.byref(nt), ctypes.byref(nb), ctypes.byref(ur),
+                                            _lib.current_stream_ptr()))
+        return nt.value, nb.value, ur.value
+
     def check(self):
         st, _ = self.status()
         if st:
@@ -90,7 +98,7 @@ class LoraBatchOps:
         return cls(infer_adapter.a_start, infer_adapter.a_len, infer_adapter.a_loc, infer_adapter.a_scaling,
                    mm.key_buffer, mm.value_buffer, max_lora_dim, use_pdl)
 
-    def prepare(self, token_adapter_ids, use_plan=True, big_groups=None):
+    def prepare(self, token_adapter_ids, use_plan=True, big_groups=None, mixed_ranks=None):
         """Start a forward: ``token_adapter_ids`` is ``req_bins`` (decode) or ``batch_req_bins`` (prefill).
 
         Allocates the three delta buffers the reference allocates in ``forward`` (``:68-69,75-76``) and builds the
@@ -100,6 +108,10 @@ class LoraBatchOps:
         on the tensor cores.  The reference decides the same way on the host (``:127-130``: Triton kernels when
         ``max_len_in_batch >= 200``).  ``None`` asks the plan (one 64-byte read-back and a stream synchronisation,
         only for batches of 128 tokens or more); a scheduler that knows its batch passes ``True`` / ``False``.
+
+        ``mixed_ranks``: do the batch's adapters differ in rank, or are all narrower than ``max_lora_dim``?  Then
+        the kernels count their work items exactly (``SLORA_FLAG_EXACT_ITEMS``; a matter of speed only).  ``None``
+        asks the plan in the same read-back; batches below 128 tokens are not asked and keep the plain enumeration.
         """
         self.ids = token_adapter_ids.contiguous()
         T = self.ids.numel()
@@ -107,11 +119,16 @@ class LoraBatchOps:
         self.delta = [torch.zeros((T, self.max_lora_dim), dtype=dtype, device=self.ids.device) for _ in range(3)]
         self.plan = BatchPlan(self.ids, self.a_start, self.a_len, self.a_loc.numel()) if use_plan else None
         self.flags = self.base_flags
-        if self.plan is not None and T >= 128:
+        if self.plan is not None and T >= 128 and (big_groups is None or mixed_ranks is None):
+            _, n_big, uniform = self.plan.info()
             if big_groups is None:
-                big_groups = self.plan.big_tiles() > 0
-            if big_groups:
-                self.flags |= _lib.FLAG_BIG_GROUPS
+                big_groups = n_big > 0
+            if mixed_ranks is None:
+                mixed_ranks = uniform == 0 or uniform < self.max_lora_dim
+        if self.plan is not None and big_groups:
+            self.flags |= _lib.FLAG_BIG_GROUPS
+        if self.plan is not None and mixed_ranks:
+            self.flags |= _lib.FLAG_EXACT_ITEMS
         return self
 
     def _common(self, layer_id):

@@ -24,13 +24,13 @@ constexpr uint32_t kSpinLimit = 1u << 18;
 //   of 8): such groups are also listed as big tiles of up to 128 tokens for the tensor-core kernels
 // big-tile record: {adapter, first slot in perm, tokens, slot_rows r, first loc entry, 0, 0, 0}
 constexpr int PH_MAGIC = 0, PH_NTILES = 1, PH_STATUS = 2, PH_MAXTILES = 3, PH_T = 4, PH_NADAPTERS = 5, PH_NBIG = 6,
-              PH_BIGOFF = 7, PH_MAXBIG = 8;
+              PH_BIGOFF = 7, PH_MAXBIG = 8, PH_UNIFORM = 9;  // PH_UNIFORM: the slot rows every non-empty tile has, 0 when they differ
 constexpr int kBigGroupTokens = 128;  // planned batches: same-adapter groups at least this long go to the tensor cores
 constexpr int kBigSegmentTokens = 32;  // segment calls: segments at least this long do
 constexpr int kBigTileTokens = 128;
 constexpr int PH_WORDS = 16;
 constexpr int kTileWords = 8;
-constexpr int32_t kPlanMagic = 0x534c5033;  // "SLP3"
+constexpr int32_t kPlanMagic = 0x534c5034;  // "SLP4"
 
 enum TileMode { MODE_TOKEN = 0, MODE_PLAN = 1, MODE_SEGMENT = 2 };
 

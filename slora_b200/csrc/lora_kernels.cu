@@ -642,14 +642,13 @@ int run_shrink(const TileSrc& src, const Tables& tb, const void* w, const void* 
     const int64_t items = static_cast<int64_t>(src.slots) * nproj * a.max_rb;
     const int64_t grid = items < sm_count() * kPipeCtasPerSm ? items : sm_count() * kPipeCtasPerSm;
     const size_t smem = kRingBytes;
-    if (dtype == SLORA_F16) {
-      auto k = lora_shrink_pipe_kernel<__half>;
-      rc = ensure_dyn_smem(k, 2, smem);
-      return rc ? rc : launch(k, grid, kPipeThreads, smem, flags, stream, a, "shrink(pipelined)");
-    }
-    auto k = lora_shrink_pipe_kernel<__nv_bfloat16>;
-    rc = ensure_dyn_smem(k, 3, smem);
-    return rc ? rc : launch(k, grid, kPipeThreads, smem, flags, stream, a, "shrink(pipelined)");
+    const bool exact = (flags & SLORA_FLAG_EXACT_ITEMS) != 0 && src.mode == MODE_PLAN;
+    auto go = [&](auto k, int which) {
+      const int rc2 = ensure_dyn_smem(k, which, smem);
+      return rc2 ? rc2 : launch(k, grid, kPipeThreads, smem, flags, stream, a, "shrink(pipelined)");
+    };
+    if (dtype == SLORA_F16) return exact ? go(lora_shrink_pipe_kernel<__half, true>, 4) : go(lora_shrink_pipe_kernel<__half, false>, 2);
+    return exact ? go(lora_shrink_pipe_kernel<__nv_bfloat16, true>, 5) : go(lora_shrink_pipe_kernel<__nv_bfloat16, false>, 3);
   }
   const size_t row_bytes = static_cast<size_t>(h_in) * 2;
   int rows = static_cast<int>(kShrinkSmemBudget / 2 / row_bytes);
@@ -786,14 +785,13 @@ int run_expand(const TileSrc& src, const Tables& tb, const void* w, const void* 
     const int64_t items = static_cast<int64_t>(src.slots) * a.chunk_begin[nproj];
     const int64_t grid = items < sm_count() * kPipeCtasPerSm ? items : sm_count() * kPipeCtasPerSm;
     const size_t smem = kRingBytes;
-    if (dtype == SLORA_F16) {
-      auto k = lora_expand_pipe_kernel<__half>;
-      rc = ensure_dyn_smem(k, 2, smem);
-      return rc ? rc : launch(k, grid, kPipeThreads, smem, flags, stream, a, "expand(pipelined)");
-    }
-    auto k = lora_expand_pipe_kernel<__nv_bfloat16>;
-    rc = ensure_dyn_smem(k, 3, smem);
-    return rc ? rc : launch(k, grid, kPipeThreads, smem, flags, stream, a, "expand(pipelined)");
+    const bool exact = (flags & SLORA_FLAG_EXACT_ITEMS) != 0 && src.mode == MODE_PLAN;
+    auto go = [&](auto k, int which) {
+      const int rc2 = ensure_dyn_smem(k, which, smem);
+      return rc2 ? rc2 : launch(k, grid, kPipeThreads, smem, flags, stream, a, "expand(pipelined)");
+    };
+    if (dtype == SLORA_F16) return exact ? go(lora_expand_pipe_kernel<__half, true>, 4) : go(lora_expand_pipe_kernel<__half, false>, 2);
+    return exact ? go(lora_expand_pipe_kernel<__nv_bfloat16, true>, 5) : go(lora_expand_pipe_kernel<__nv_bfloat16, false>, 3);
   }
   a.piece = piece;
   set_chunks(kChunk);
@@ -985,6 +983,19 @@ int slora_plan_big_tiles(const void* workspace, int* n_big_out, void* stream) {
   if (e != cudaSuccess) return fail(SLORA_ERR_LAUNCH, "plan_big_tiles: %s", cudaGetErrorString(e));
   if (hdr[PH_MAGIC] != kPlanMagic) return fail(SLORA_ERR_WORKSPACE, "workspace does not hold a plan");
   *n_big_out = hdr[PH_NBIG];
+  return SLORA_OK;
+}
+
+int slora_plan_info(const void* workspace, int* n_tiles_out, int* n_big_out, int* uniform_rank_out, void* stream) {
+  if (!workspace) return fail(SLORA_ERR_NULL, "workspace is null");
+  int32_t hdr[PH_WORDS];
+  cudaError_t e = cudaMemcpyAsync(hdr, workspace, sizeof(hdr), cudaMemcpyDeviceToHost, static_cast<cudaStream_t>(stream));
+  if (e == cudaSuccess) e = cudaStreamSynchronize(static_cast<cudaStream_t>(stream));
+  if (e != cudaSuccess) return fail(SLORA_ERR_LAUNCH, "plan_info: %s", cudaGetErrorString(e));
+  if (hdr[PH_MAGIC] != kPlanMagic) return fail(SLORA_ERR_WORKSPACE, "workspace does not hold a plan");
+  if (n_tiles_out) *n_tiles_out = hdr[PH_NTILES];
+  if (n_big_out) *n_big_out = hdr[PH_NBIG];
+  if (uniform_rank_out) *uniform_rank_out = hdr[PH_UNIFORM];
   return SLORA_OK;
 }
 

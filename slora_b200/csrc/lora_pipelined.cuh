@@ -52,6 +52,7 @@ constexpr int kMaxStageBytes = SLORA_STAGE_KB * 1024;  // a shrink item is cut i
 constexpr int kPipeChunk = 16384;          // flat B elements per expand item (32 KB)
 constexpr int kMaxPieces = 16;  // B copies per expand stage (lanes 0..15); y copies use lanes 16..23, delta 24..31
 constexpr int kSpanRows = 6;    // pool rows a B chunk may touch
+constexpr int kCompactTiles = 768;  // tiles whose item counts fit the control block (two CTAs per SM leave 2 KB)
 
 constexpr int FLAG_FIRST = 1, FLAG_LAST = 2, FLAG_END = 4;
 constexpr uint32_t FULL_MASK = 0xffffffffu;
@@ -90,6 +91,8 @@ struct PipeCtl {
   // shrink only: per-item partial sums of the consumer warps and the arrival counter that elects the last warp
   float red[kSlots][kConsumerWarps][32];
   int red_cnt[kSlots];
+  // planned batches of mixed ranks: items up to and including each tile (see build_item_map)
+  uint16_t item_end[kCompactTiles];
 };
 
 // Producer-side ring state (identical in all 32 lanes).
@@ -265,15 +268,145 @@ __device__ __forceinline__ P pick3(P const (&arr)[3], int p) {
 __device__ __forceinline__ uint32_t round128(uint32_t v) { return (v + 127u) & ~127u; }
 
 // ------------------------------------------------------------------------------------------------------------
+// Which items does a launch have?  A tile yields a number of items that depends on its adapter's rank (row blocks
+// of the shrink, B chunks of the expand).  Enumerating a fixed number of slots per tile, sized for the widest rank,
+// and skipping the empty ones leaves the CTAs (item i belongs to CTA i mod gridDim.x) with unequal shares as soon
+// as ranks differ - the empty slots recur with the period of the slot grid.  With a plan the items are therefore
+// counted exactly: in closed form when every tile has the same rank (the plan's header says so), else through a
+// per-tile running count that the CTA builds in shared memory from the tile records (all threads fetch the
+// records, the producer warp scans the counts; before the grid-dependency wait: the plan is complete by then).  Without a plan, or with more tiles or items than the
+// control block holds, the padded enumeration stays.  The exact count costs the start of a launch a few hundred
+// nanoseconds (its arithmetic sits between the header and the first tile record), which a launch of ten
+// microseconds over same-rank adapters does not earn back: the kernels are therefore built both ways (EXACT) and
+// the caller, who can ask the plan what it holds (slora_plan_info), picks with SLORA_FLAG_EXACT_ITEMS.
+// ------------------------------------------------------------------------------------------------------------
+struct ItemMap {
+  int mode = 0;      // 0 padded slots, 1 same count for every tile, 2 running count in PipeCtl::item_end
+  int per_tile = 0;  // modes 0 and 1
+  int uniform = 0;   // mode 1: the slot rows of every tile
+  int n_tiles = 0;
+  int64_t n_items = 0;
+};
+
+// Does this launch count its items per tile (ranks differ, or big groups go elsewhere), and over how many tiles?
+__device__ __forceinline__ bool needs_item_counts(const TileSrc& src, int& n_tiles, int& uniform) {
+  // the three header words in one go: their loads are on the launch's critical path
+  const int32_t* hdr = src.plan;
+  const int nt = hdr[PH_NTILES], uni = hdr[PH_UNIFORM], nbig = hdr[PH_NBIG];
+  n_tiles = min(nt, src.slots);
+  uniform = uni;
+  const bool some_elsewhere = src.seg_split > 0 && nbig > 0;  // big groups the tensor-core launch serves
+  return !(uni > 0 && !some_elsewhere);
+}
+
+// All threads of the CTA: items of every tile into PipeCtl::item_end (one tile record per thread and round, so the
+// loads overlap); the caller follows with __syncthreads().
+template <typename F>
+__device__ __forceinline__ void fill_item_counts(const TileSrc& src, const Tables& tb, PipeCtl& c, int tid,
+                                                 F items_of_rank) {
+  if (src.mode != MODE_PLAN) return;
+  int n_tiles, uniform;
+  if (!needs_item_counts(src, n_tiles, uniform) || n_tiles > kCompactTiles) return;
+  for (int tile = tid; tile < n_tiles; tile += kPipeThreads) {
+    const int4* rec = reinterpret_cast<const int4*>(src.plan + PH_WORDS + kTileWords * tile);
+    const int4 r0 = rec[0];
+    const int n = r0.z, r = r0.w;
+    bool elsewhere = false;
+    if (src.seg_split > 0) elsewhere = rec[1].y != 0 && r > 0 && tb.pool_stride % r == 0 && r <= src.mma_max_rows;
+    const int cnt = (n > 0 && r > 0 && !elsewhere) ? items_of_rank(r) : 0;
+    c.item_end[tile] = static_cast<uint16_t>(min(cnt, 0xffff));
+  }
+}
+
+// Producer warp, after fill_item_counts and the barrier: the launch's item map; with mixed ranks the counts in
+// item_end become running counts (each lane sums a contiguous run, the warp scans the lane sums).
+template <typename F>
+__device__ __forceinline__ ItemMap build_item_map(const TileSrc& src, int padded_per_tile, PipeCtl& c, int lane,
+                                                  F items_of_rank) {
+  ItemMap m;
+  m.per_tile = padded_per_tile;
+  if (src.mode != MODE_PLAN) {
+    m.n_tiles = src.slots;
+    m.n_items = static_cast<int64_t>(m.n_tiles) * padded_per_tile;
+    return m;
+  }
+  int uniform;
+  const bool counted = needs_item_counts(src, m.n_tiles, uniform);
+  m.n_items = static_cast<int64_t>(m.n_tiles) * padded_per_tile;
+  if (!counted) {
+    m.mode = 1;
+    m.uniform = uniform;
+    m.per_tile = items_of_rank(uniform);
+    m.n_items = static_cast<int64_t>(m.n_tiles) * m.per_tile;
+    return m;
+  }
+  if (m.n_tiles > kCompactTiles) return m;
+  const int per = (m.n_tiles + 31) / 32;
+  const int lo = min(lane * per, m.n_tiles), hi = min(lo + per, m.n_tiles);
+  int sum = 0;
+  for (int i = lo; i < hi; ++i) sum += c.item_end[i];
+  int incl = sum;
+#pragma unroll
+  for (int d = 1; d < 32; d <<= 1) {
+    const int v = __shfl_up_sync(FULL_MASK, incl, d);
+    if (lane >= d) incl += v;
+  }
+  const int total = __shfl_sync(FULL_MASK, incl, 31);
+  if (total > 0xffff) return m;  // too many items for 16-bit counts (same decision in every lane)
+  int run = incl - sum;
+  for (int i = lo; i < hi; ++i) {
+    run += c.item_end[i];
+    c.item_end[i] = static_cast<uint16_t>(run);
+  }
+  __syncwarp();
+  m.mode = 2;
+  m.n_items = total;
+  return m;
+}
+
+// The padded enumeration alone: nothing but the tile count is read from the plan.
+__device__ __forceinline__ ItemMap padded_item_map(const TileSrc& src, int padded_per_tile) {
+  ItemMap m;
+  m.per_tile = padded_per_tile;
+  m.n_tiles = tile_count(src);
+  m.n_items = static_cast<int64_t>(m.n_tiles) * padded_per_tile;
+  return m;
+}
+
+// Item q -> its tile and its index among that tile's items.
+__device__ __forceinline__ void item_to_tile(const ItemMap& m, const PipeCtl& c, int64_t q, int& tile, int& local) {
+  if (m.mode != 2) {
+    tile = static_cast<int>(q / m.per_tile);
+    local = static_cast<int>(q - static_cast<int64_t>(tile) * m.per_tile);
+    return;
+  }
+  int lo = 0, hi = m.n_tiles - 1;  // first tile whose running count exceeds q
+  while (lo < hi) {
+    const int mid = (lo + hi) >> 1;
+    if (static_cast<int64_t>(c.item_end[mid]) > q) {
+      hi = mid;
+    } else {
+      lo = mid + 1;
+    }
+  }
+  tile = lo;
+  local = static_cast<int>(q) - (lo > 0 ? c.item_end[lo - 1] : 0);
+}
+
+// ------------------------------------------------------------------------------------------------------------
 // shrink
 // stage meta: [0] flags [1] nrows [2] n [3] j0 [4] projection [5] klen [6] ring offset, [8..15] token ids
 // stage bytes: nrows chunks of klen elements (adapter rows), then n chunks of klen elements (token rows)
 // ------------------------------------------------------------------------------------------------------------
-template <typename T>
+// Row blocks a tile of rr slot rows has per projection, and its items.
+__device__ __forceinline__ int shrink_blocks_of(const ShrinkArgs& a, int rr) {
+  return min(a.max_rb, (rr * a.rank_mult + kMaxRows - 1) / kMaxRows);
+}
+__device__ __forceinline__ int shrink_items_of(const ShrinkArgs& a, int rr) { return a.nproj * shrink_blocks_of(a, rr); }
+
+template <typename T, bool EXACT>
 __device__ __forceinline__ void shrink_producer(const ShrinkArgs& a, unsigned char* ring_mem, PipeCtl& c, int lane,
                                                 int role) {
-  const int per_tile = a.nproj * a.max_rb;
-  const int64_t n_items = static_cast<int64_t>(tile_count(a.src)) * per_tile;
   const int h_in = a.h_in;
   const int64_t S = a.tb.pool_stride;
   const T* w = reinterpret_cast<const T*>(a.w);
@@ -283,20 +416,29 @@ __device__ __forceinline__ void shrink_producer(const ShrinkArgs& a, unsigned ch
   PipeCtl::Prod& pp = c.prod[role];
   Ring r;
   r.role = role;
+  auto blocks_of = [&](int rr) { return shrink_blocks_of(a, rr); };
+  const ItemMap map = EXACT ? build_item_map(a.src, a.nproj * a.max_rb, c, lane,
+                                             [&](int rr) { return shrink_items_of(a, rr); })
+                            : padded_item_map(a.src, a.nproj * a.max_rb);
+  const int mode = EXACT ? map.mode : 0;
+  const int64_t n_items = map.n_items;
 
   for (int64_t batch0 = blockIdx.x; batch0 < n_items && !r.dead; batch0 += 32 * G) {
     // ---- 32 items resolved in parallel, one per lane; d_i[lane] = {valid, n, nrows, j0, p, -, -, -, tok[8]} ----
     const int64_t item = batch0 + lane * G;
     int valid = 0;
     if (item < n_items) {
-      const int tile = static_cast<int>(item / per_tile);
-      const int rem = static_cast<int>(item - static_cast<int64_t>(tile) * per_tile);
-      const int p = rem / a.max_rb, rb = rem - p * a.max_rb;
+      int tile, rem;
+      item_to_tile(map, c, item, tile, rem);
+      // projection and row block: known before the tile record arrives unless ranks are mixed
+      int nb = mode == 0 ? a.max_rb : blocks_of(map.uniform);
       TileInfo t;
       if (lookup_tile(a.src, a.tb, tile, t, a.status)) {
+        if (mode == 2) nb = blocks_of(t.r);
+        const int p = rem / nb, rb = rem - p * nb;
         const int j0 = rb * kMaxRows;
         const int rows_total = t.r * a.rank_mult;  // A rows of the projection (rows may be shorter than a pool row)
-        if (j0 < rows_total) {
+        if (p < a.nproj && j0 < rows_total) {
           const int nrows = min(kMaxRows, rows_total - j0);
           const int64_t base = t.loc_base + static_cast<int64_t>(t.r) * pick3(a.qkvo, p);
           bool ok = true;
@@ -521,15 +663,19 @@ __device__ __forceinline__ void shrink_consumer(const ShrinkArgs& a, const unsig
   }
 }
 
-template <typename T>
+template <typename T, bool EXACT>
 __global__ void __launch_bounds__(kPipeThreads) lora_shrink_pipe_kernel(const ShrinkArgs a) {
   extern __shared__ __align__(128) unsigned char ring_mem[];
   __shared__ __align__(16) PipeCtl ctl;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   pipe_init(ctl, tid);
   pdl_launch_dependents();
+  if (EXACT) {
+    fill_item_counts(a.src, a.tb, ctl, tid, [&](int rr) { return shrink_items_of(a, rr); });
+    __syncthreads();
+  }
   if (warp < kProducerWarps) {
-    shrink_producer<T>(a, ring_mem, ctl, lane, warp);
+    shrink_producer<T, EXACT>(a, ring_mem, ctl, lane, warp);
   } else {
     shrink_consumer<T>(a, ring_mem, ctl, lane, warp - kProducerWarps);
   }
@@ -542,11 +688,28 @@ __global__ void __launch_bounds__(kPipeThreads) lora_shrink_pipe_kernel(const Sh
 //             [8..15] token ids
 // stage bytes: B chunk (clen elements), then n y segments of clen / r elements, then n delta rows of r elements
 // ------------------------------------------------------------------------------------------------------------
-template <typename T>
+// The expand takes ranks 8..128 in powers of two that the delta buffers hold; B chunks of projection p for rank rk;
+// items of a tile of rr slot rows.
+__device__ __forceinline__ bool expand_rank_ok(const ExpandArgs& a, int rk) {
+  return (rk == 8 || rk == 16 || rk == 32 || rk == 64 || rk == 128) && rk <= a.max_rank;
+}
+__device__ __forceinline__ int expand_chunks_of(const ExpandArgs& a, int p, int rk) {
+  const int64_t flat = static_cast<int64_t>(pick3(a.h_out, p)) * rk;
+  return static_cast<int>(min(static_cast<int64_t>(a.chunk_begin[p + 1] - a.chunk_begin[p]),
+                              (flat + kPipeChunk - 1) / kPipeChunk));
+}
+__device__ __forceinline__ int expand_items_of(const ExpandArgs& a, int rr) {
+  const int rk = rr * a.rank_mult;
+  if (!expand_rank_ok(a, rk)) return 1;  // one item, which reports the rank
+  int n = 0;
+  for (int p = 0; p < a.nproj; ++p) n += expand_chunks_of(a, p, rk);
+  return n;
+}
+
+template <typename T, bool EXACT>
 __device__ __forceinline__ void expand_producer(const ExpandArgs& a, unsigned char* ring_mem, PipeCtl& c, int lane,
                                                 int role) {
   const int total_chunks = a.chunk_begin[a.nproj];
-  const int64_t n_items = static_cast<int64_t>(tile_count(a.src)) * total_chunks;
   const int64_t S = a.tb.pool_stride;
   const T* w = reinterpret_cast<const T*>(a.w);
   const int64_t G = gridDim.x;
@@ -556,6 +719,12 @@ __device__ __forceinline__ void expand_producer(const ExpandArgs& a, unsigned ch
   r.role = role;
   r.tp = a.tp.enabled ? &a.tp : nullptr;
   r.status = a.status;
+  auto rank_ok = [&](int rk) { return expand_rank_ok(a, rk); };
+  auto chunks_of = [&](int p, int rk) { return expand_chunks_of(a, p, rk); };
+  const ItemMap map = EXACT ? build_item_map(a.src, total_chunks, c, lane, [&](int rr) { return expand_items_of(a, rr); })
+                            : padded_item_map(a.src, total_chunks);
+  const int mode = EXACT ? map.mode : 0;
+  const int64_t n_items = map.n_items;
 
   for (int64_t batch0 = blockIdx.x; batch0 < n_items && !r.dead; batch0 += 32 * G) {
     // d_i[lane] = {valid, n, r, p, clen, first output, scale bits, c0, tok[8]}, d_l[lane][j] = pool row of slot row
@@ -563,19 +732,31 @@ __device__ __forceinline__ void expand_producer(const ExpandArgs& a, unsigned ch
     const int64_t item = batch0 + lane * G;
     int valid = 0;
     if (item < n_items) {
-      const int tile = static_cast<int>(item / total_chunks);
-      int ch = static_cast<int>(item - static_cast<int64_t>(tile) * total_chunks);
+      int tile, ch;
+      item_to_tile(map, c, item, tile, ch);
+      // projection and chunk: known before the tile record arrives unless ranks are mixed
       int p = 0;
-      while (p + 1 < a.nproj && ch >= a.chunk_begin[p + 1]) ++p;
-      ch -= a.chunk_begin[p];
+      auto split = [&](int rk) {
+        while (p + 1 < a.nproj && ch >= chunks_of(p, rk)) {
+          ch -= chunks_of(p, rk);
+          ++p;
+        }
+      };
+      if (mode == 0) {
+        while (p + 1 < a.nproj && ch >= a.chunk_begin[p + 1]) ++p;
+        ch -= a.chunk_begin[p];
+      } else if (mode == 1 && rank_ok(map.uniform * a.rank_mult)) {
+        split(map.uniform * a.rank_mult);
+      }
       TileInfo t;
       if (lookup_tile(a.src, a.tb, tile, t, a.status)) {
         const int rk = t.r * a.rank_mult;
+        if (mode == 2 && rank_ok(rk)) split(rk);
         const int h_out = pick3(a.h_out, p);
         const int64_t flat_total = static_cast<int64_t>(h_out) * rk;
         const int64_t c0 = static_cast<int64_t>(ch) * kPipeChunk;
         if (c0 < flat_total) {
-          if ((rk != 8 && rk != 16 && rk != 32 && rk != 64 && rk != 128) || rk > a.max_rank) {
+          if (!rank_ok(rk)) {
             set_status(a.status, SLORA_STATUS_BAD_RANK);
           } else {
             const int clen = static_cast<int>(min(static_cast<int64_t>(kPipeChunk), flat_total - c0));
@@ -770,15 +951,19 @@ __device__ __forceinline__ void expand_consumer(const ExpandArgs& a, const unsig
   }
 }
 
-template <typename T>
+template <typename T, bool EXACT>
 __global__ void __launch_bounds__(kPipeThreads) lora_expand_pipe_kernel(const ExpandArgs a) {
   extern __shared__ __align__(128) unsigned char ring_mem[];
   __shared__ __align__(16) PipeCtl ctl;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   pipe_init(ctl, tid);
   pdl_launch_dependents();
+  if (EXACT) {
+    fill_item_counts(a.src, a.tb, ctl, tid, [&](int rr) { return expand_items_of(a, rr); });
+    __syncthreads();
+  }
   if (warp < kProducerWarps) {
-    expand_producer<T>(a, ring_mem, ctl, lane, warp);
+    expand_producer<T, EXACT>(a, ring_mem, ctl, lane, warp);
   } else {
     expand_consumer<T>(a, ring_mem, ctl, lane, warp - kProducerWarps);
   }

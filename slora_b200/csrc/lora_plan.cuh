@@ -22,11 +22,15 @@ __global__ void __launch_bounds__(1024) plan_build_kernel(int32_t* ws, const int
   const int big_off = (PH_WORDS + kTileWords * max_tiles + 2 * T + n_adapters + 3) & ~3;  // 16-byte aligned records
   int32_t* big = ws + big_off;
   __shared__ int s_tok[32], s_tile[32], s_big[32];
-  __shared__ int s_status;
+  __shared__ int s_status, s_rmin, s_rmax;
   const int tid = threadIdx.x, nthr = blockDim.x, lane = tid & 31, warp = tid >> 5;
 
   for (int i = tid; i < n_adapters; i += nthr) cnt[i] = 0;
-  if (tid == 0) s_status = 0;
+  if (tid == 0) {
+    s_status = 0;
+    s_rmin = 0x7fffffff;
+    s_rmax = 0;
+  }
   __syncthreads();
   for (int t = tid; t < T; t += nthr) {
     const int64_t a = ids[t];
@@ -107,6 +111,10 @@ __global__ void __launch_bounds__(1024) plan_build_kernel(int32_t* ws, const int
       const bool good = r4 >= 0 && st >= 0 && st + r4 <= loc_len && r4 <= (int64_t(1) << 20) && st < 0x7fffffffLL;
       if (!good) atomicOr(&s_status, SLORA_STATUS_BAD_TABLE);
       const bool bigg = good && is_big(a, c);
+      if (good) {
+        atomicMin(&s_rmin, static_cast<int>(r4 >> 2));
+        atomicMax(&s_rmax, static_cast<int>(r4 >> 2));
+      }
       for (int i = 0; i * kTileTokens < c; ++i) {
         if (tile_off < max_tiles) {
           int4* rec = reinterpret_cast<int4*>(tiles + kTileWords * tile_off);
@@ -143,6 +151,7 @@ __global__ void __launch_bounds__(1024) plan_build_kernel(int32_t* ws, const int
     hdr[PH_NADAPTERS] = n_adapters;
     hdr[PH_BIGOFF] = big_off;
     hdr[PH_MAXBIG] = max_big;
+    hdr[PH_UNIFORM] = s_rmin == s_rmax ? s_rmax : 0;
   }
 }
 

@@ -235,12 +235,18 @@ class CudaBackend:
 
     def __init__(self, use_pdl=False, fused=True):
         from . import _lib
-        self.flags = _lib.FLAG_PDL if use_pdl else 0
+        self.base_flags = _lib.FLAG_PDL if use_pdl else 0
+        self.flags = self.base_flags
         self.fused = fused   # with a PeerExchange: push from the shrink / wait in the expand, no exchange launch
 
     def make_plan(self, ids, t):
+        from . import _lib
         from .batch_infer import BatchPlan
-        return BatchPlan(ids, t.a_start, t.a_len, t.a_loc.numel())
+        plan = BatchPlan(ids, t.a_start, t.a_len, t.a_loc.numel())
+        self.flags = self.base_flags
+        if ids.numel() >= 128 and plan.info()[2] == 0:   # adapters of different ranks: count the work items exactly
+            self.flags |= _lib.FLAG_EXACT_ITEMS
+        return plan
 
     def shrink(self, plan, ids, qkvo, deltas, x, pool_a, t, rank_mult=1):
         from .batch_infer import shrink_multi

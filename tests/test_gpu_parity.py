@@ -31,9 +31,10 @@ def _dispatch_layer(w, layer=0, y_init=None):
     return outs, deltas
 
 
-def _fused_layer(w, layer=0, use_plan=True, use_pdl=True):
-    ops = sl.LoraBatchOps(w.a_start, w.a_len, w.a_loc, w.a_scaling, w.pools_a, w.pools_b, w.max_rank, use_pdl)
-    ops.prepare(w.ids, use_plan=use_plan)
+def _fused_layer(w, layer=0, use_plan=True, use_pdl=True, max_rank=None, **prepare_kw):
+    ops = sl.LoraBatchOps(w.a_start, w.a_len, w.a_loc, w.a_scaling, w.pools_a, w.pools_b, max_rank or w.max_rank,
+                          use_pdl)
+    ops.prepare(w.ids, use_plan=use_plan, **prepare_kw)
     H, K = w.spec.hidden, w.spec.h_kv
     q = torch.zeros((w.T, H), dtype=w.dtype, device=DEV)
     k = torch.zeros((w.T, K), dtype=w.dtype, device=DEV)
@@ -85,6 +86,48 @@ def test_mixed_ranks_fused(use_plan, use_pdl):
     outs = _fused_layer(wl.to(DEV), use_plan=use_plan, use_pdl=use_pdl)
     for p in range(4):
         assert_parity(outs[p], ref[p], what=f"mixed proj {p}")
+
+
+@pytest.mark.parametrize("case", ["mixed", "narrow", "many_tiles", "bf16_gqa"])
+def test_exact_item_count_gives_the_same_bits_as_the_padded_enumeration(case):
+    """SLORA_FLAG_EXACT_ITEMS only changes which CTA computes which item: outputs are bit-identical with and without
+    it, for mixed ranks (running count per tile), one rank below the delta width (closed form), more tiles than the
+    running count holds (falls back to the padded enumeration) and k/v narrower than q."""
+    kw, dt = dict(hidden=2048), torch.float16
+    if case == "mixed":
+        wl = build_workload(3, pool_rows=16384, n_adapters=60, decode_tokens=150, prefill=("seqs", 3, 5, 40), **kw)
+    elif case == "narrow":
+        wl = build_workload(3, pool_rows=8192, n_adapters=30, decode_tokens=140, prefill=None, rank_choices=(16,), **kw)
+    elif case == "many_tiles":
+        wl = build_workload(3, pool_rows=163840, n_adapters=3000, decode_tokens=3000, prefill=None, hidden=1024,
+                            rank_choices=(8, 16))
+    else:
+        dt = torch.bfloat16
+        wl = build_workload(5, dtype=dt, pool_rows=8192, n_adapters=40, decode_tokens=200, hidden=2048, h_kv=512,
+                            rank_choices=(8, 32, 64))
+    w = wl.to(DEV)
+    if case == "many_tiles":
+        assert sl.BatchPlan(w.ids, w.a_start, w.a_len, w.a_loc.numel()).info()[0] > 768
+    width = 64 if case == "narrow" else None
+    plain = _fused_layer(w, mixed_ranks=False, max_rank=width)
+    exact = _fused_layer(w, mixed_ranks=True, max_rank=width)
+    asked = _fused_layer(w, max_rank=width)          # prepare() reads the plan and decides
+    ref = oracle_layer(wl)
+    for p in range(4):
+        assert torch.equal(plain[p], exact[p]) and torch.equal(plain[p], asked[p]), f"{case} proj {p}"
+        assert_parity(exact[p], ref[p], dt, what=f"exact items {case} proj {p}")
+
+
+def test_plan_info_reports_the_shared_rank():
+    wl = build_workload(3, pool_rows=8192, n_adapters=30, decode_tokens=140, prefill=None, hidden=1024,
+                        rank_choices=(16,)).to(DEV)
+    plan = sl.BatchPlan(wl.ids, wl.a_start, wl.a_len, wl.a_loc.numel())
+    tiles, big, uniform = plan.info()
+    assert tiles >= len(set(wl.ids.tolist())) and big == 0 and uniform == 16
+    wl = build_workload(3, pool_rows=8192, n_adapters=30, decode_tokens=140, prefill=None, hidden=1024).to(DEV)
+    assert sl.BatchPlan(wl.ids, wl.a_start, wl.a_len, wl.a_loc.numel()).info()[2] == 0
+    ops = sl.LoraBatchOps(wl.a_start, wl.a_len, wl.a_loc, wl.a_scaling, wl.pools_a, wl.pools_b, wl.max_rank)
+    assert ops.prepare(wl.ids).flags & 4 and not ops.prepare(wl.ids[:100]).flags & 4    # small batches are not asked
 
 
 def test_config2_shape_small_pool():
