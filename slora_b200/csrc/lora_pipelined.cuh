@@ -52,7 +52,9 @@ constexpr int kMaxStageBytes = SLORA_STAGE_KB * 1024;  // a shrink item is cut i
 constexpr int kPipeChunk = 16384;          // flat B elements per expand item (32 KB)
 constexpr int kMaxPieces = 16;  // B copies per expand stage (lanes 0..15); y copies use lanes 16..23, delta 24..31
 constexpr int kSpanRows = 6;    // pool rows a B chunk may touch
-constexpr int kCompactTiles = 768;  // tiles whose item counts fit the control block (two CTAs per SM leave 2 KB)
+constexpr int kWideRows = 8;    // adapter rows of a shrink item of a tile with at most kWideTokens tokens (EXACT only)
+constexpr int kWideTokens = 4;
+constexpr int kCompactTiles = 640;  // tiles whose item counts fit the control block (two CTAs per SM leave little room)
 
 constexpr int FLAG_FIRST = 1, FLAG_LAST = 2, FLAG_END = 4;
 constexpr uint32_t FULL_MASK = 0xffffffffu;
@@ -85,7 +87,7 @@ struct PipeCtl {
     uint32_t pend_bytes[kPendSlots][32];
     // the 32 items a batch resolves, one per lane, parked here so that the lanes that carry the copies read what
     // they need instead of receiving it through shuffles
-    int64_t d_l[32][kSpanRows];
+    int64_t d_l[32][kWideRows];
     int d_i[32][16];
   } prod[kProducerWarps];
   // shrink only: per-item partial sums of the consumer warps and the arrival counter that elects the last warp
@@ -313,7 +315,7 @@ __device__ __forceinline__ void fill_item_counts(const TileSrc& src, const Table
     const int n = r0.z, r = r0.w;
     bool elsewhere = false;
     if (src.seg_split > 0) elsewhere = rec[1].y != 0 && r > 0 && tb.pool_stride % r == 0 && r <= src.mma_max_rows;
-    const int cnt = (n > 0 && r > 0 && !elsewhere) ? items_of_rank(r) : 0;
+    const int cnt = (n > 0 && r > 0 && !elsewhere) ? items_of_rank(r, n) : 0;
     c.item_end[tile] = static_cast<uint16_t>(min(cnt, 0xffff));
   }
 }
@@ -336,7 +338,7 @@ __device__ __forceinline__ ItemMap build_item_map(const TileSrc& src, int padded
   if (!counted) {
     m.mode = 1;
     m.uniform = uniform;
-    m.per_tile = items_of_rank(uniform);
+    m.per_tile = items_of_rank(uniform, kTileTokens);
     m.n_items = static_cast<int64_t>(m.n_tiles) * m.per_tile;
     return m;
   }
@@ -398,11 +400,20 @@ __device__ __forceinline__ void item_to_tile(const ItemMap& m, const PipeCtl& c,
 // stage meta: [0] flags [1] nrows [2] n [3] j0 [4] projection [5] klen [6] ring offset, [8..15] token ids
 // stage bytes: nrows chunks of klen elements (adapter rows), then n chunks of klen elements (token rows)
 // ------------------------------------------------------------------------------------------------------------
-// Row blocks a tile of rr slot rows has per projection, and its items.
-__device__ __forceinline__ int shrink_blocks_of(const ShrinkArgs& a, int rr) {
-  return min(a.max_rb, (rr * a.rank_mult + kMaxRows - 1) / kMaxRows);
+// Row blocks a tile of rr slot rows has per projection (blocks of kWideRows rows when `wide`, else kMaxRows; rows
+// beyond the delta buffers' width are not enumerated), and its items.
+__device__ __forceinline__ int shrink_rows_of(const ShrinkArgs& a, int rr) {
+  return min(rr * a.rank_mult, a.max_rb * kMaxRows);
 }
-__device__ __forceinline__ int shrink_items_of(const ShrinkArgs& a, int rr) { return a.nproj * shrink_blocks_of(a, rr); }
+__device__ __forceinline__ int shrink_blocks_of(const ShrinkArgs& a, int rr, bool wide) {
+  const int per = wide ? kWideRows : kMaxRows;
+  return (shrink_rows_of(a, rr) + per - 1) / per;
+}
+// With per-tile counts (ranks differ) a tile of few tokens takes its rows eight at a time: its token rows are then
+// staged once per eight adapter rows instead of once per four.
+__device__ __forceinline__ int shrink_items_of(const ShrinkArgs& a, int rr, int n) {
+  return a.nproj * shrink_blocks_of(a, rr, n <= kWideTokens);
+}
 
 template <typename T, bool EXACT>
 __device__ __forceinline__ void shrink_producer(const ShrinkArgs& a, unsigned char* ring_mem, PipeCtl& c, int lane,
@@ -416,9 +427,9 @@ __device__ __forceinline__ void shrink_producer(const ShrinkArgs& a, unsigned ch
   PipeCtl::Prod& pp = c.prod[role];
   Ring r;
   r.role = role;
-  auto blocks_of = [&](int rr) { return shrink_blocks_of(a, rr); };
+  constexpr int RMAX = EXACT ? kWideRows : kMaxRows;  // rows of the widest item = lane of the first token row
   const ItemMap map = EXACT ? build_item_map(a.src, a.nproj * a.max_rb, c, lane,
-                                             [&](int rr) { return shrink_items_of(a, rr); })
+                                             [&](int rr, int) { return a.nproj * shrink_blocks_of(a, rr, false); })
                             : padded_item_map(a.src, a.nproj * a.max_rb);
   const int mode = EXACT ? map.mode : 0;
   const int64_t n_items = map.n_items;
@@ -431,19 +442,21 @@ __device__ __forceinline__ void shrink_producer(const ShrinkArgs& a, unsigned ch
       int tile, rem;
       item_to_tile(map, c, item, tile, rem);
       // projection and row block: known before the tile record arrives unless ranks are mixed
-      int nb = mode == 0 ? a.max_rb : blocks_of(map.uniform);
+      int nb = mode == 0 ? a.max_rb : shrink_blocks_of(a, map.uniform, false);
       TileInfo t;
       if (lookup_tile(a.src, a.tb, tile, t, a.status)) {
-        if (mode == 2) nb = blocks_of(t.r);
+        const bool wide = mode == 2 && t.n <= kWideTokens;
+        if (mode == 2) nb = shrink_blocks_of(a, t.r, wide);
+        const int per = wide ? kWideRows : kMaxRows;
         const int p = rem / nb, rb = rem - p * nb;
-        const int j0 = rb * kMaxRows;
-        const int rows_total = t.r * a.rank_mult;  // A rows of the projection (rows may be shorter than a pool row)
+        const int j0 = rb * per;
+        const int rows_total = shrink_rows_of(a, t.r);  // A rows of the projection (rows may be shorter than a pool row)
         if (p < a.nproj && j0 < rows_total) {
-          const int nrows = min(kMaxRows, rows_total - j0);
+          const int nrows = min(per, rows_total - j0);
           const int64_t base = t.loc_base + static_cast<int64_t>(t.r) * pick3(a.qkvo, p);
           bool ok = true;
 #pragma unroll
-          for (int j = 0; j < kMaxRows; ++j) {
+          for (int j = 0; j < RMAX; ++j) {
             if (j < nrows) {
               const int64_t f = static_cast<int64_t>(j0 + j) * h_in;
               const int64_t pr = f / S, col = f - pr * S;
@@ -470,16 +483,16 @@ __device__ __forceinline__ void shrink_producer(const ShrinkArgs& a, unsigned ch
     const uint32_t valid_mask = __ballot_sync(FULL_MASK, valid != 0);
     __syncwarp();
 
-    // ---- feed the ring, item by item (lane j < 4 carries adapter row j, lane 4 + i carries token i) ----
+    // ---- feed the ring, item by item (lane j < RMAX carries adapter row j, lane RMAX + i carries token i) ----
     for (uint32_t left = valid_mask; left != 0 && !r.dead; left &= left - 1) {
       const int k = __ffs(left) - 1;
       const int* di = pp.d_i[k];
       const int n = di[1], nrows = di[2];
       const bool is_w = lane < nrows;
-      const bool is_x = lane >= kMaxRows && lane < kMaxRows + n;
-      const int mytok = (lane >= kMaxRows && lane < kMaxRows + kTileTokens) ? di[8 + lane - kMaxRows] : 0;
-      const T* src0 = is_w ? w + pp.d_l[k][lane & (kMaxRows - 1)] : x + static_cast<int64_t>(mytok) * a.x_stride;
-      const int myslot = is_w ? lane : nrows + (lane - kMaxRows);  // position of this lane's chunk in the stage
+      const bool is_x = lane >= RMAX && lane < RMAX + n;
+      const int mytok = (lane >= RMAX && lane < RMAX + kTileTokens) ? di[8 + lane - RMAX] : 0;
+      const T* src0 = is_w ? w + pp.d_l[k][lane & (RMAX - 1)] : x + static_cast<int64_t>(mytok) * a.x_stride;
+      const int myslot = is_w ? lane : nrows + (lane - RMAX);  // position of this lane's chunk in the stage
       // cut the item into K-chunks that are multiples of 2048 elements (so the element -> consumer lane mapping, and
       // with it the summation order, does not depend on how many tokens share the tile) and, where that allows,
       // no larger than kMaxStageBytes
@@ -509,8 +522,8 @@ __device__ __forceinline__ void shrink_producer(const ShrinkArgs& a, unsigned ch
           c.meta[slot][5] = klen;
           c.meta[slot][6] = static_cast<int>(off);
           c.meta[slot][7] = di[5];  // slot rows of the adapter
-        } else if (lane >= kMaxRows && lane < kMaxRows + kTileTokens) {
-          c.meta[slot][8 + lane - kMaxRows] = mytok;
+        } else if (lane >= RMAX && lane < RMAX + kTileTokens) {
+          c.meta[slot][8 + lane - RMAX] = mytok;
         }
         __syncwarp();  // the arrive below publishes every lane's part of the stage record
         if (lane == 0) mbar_expect_tx(&c.full[slot], static_cast<uint32_t>(nrows + n) * bytes);
@@ -566,12 +579,45 @@ __device__ __forceinline__ void shrink_accumulate(float (&acc)[kMaxRows][kTileTo
   }
 }
 
+// The same two steps for an item of kWideRows rows and at most kWideTokens tokens (NT in 1, 2, 4): the 32
+// accumulators are the same registers, indexed [row * NT + token].
+#define SLORA_ACC(idx) acc[(idx) >> 3][(idx) & 7]
+template <typename T, int NT>
+__device__ __forceinline__ void shrink_accumulate_wide(float (&acc)[kMaxRows][kTileTokens], const T* st, int nrows,
+                                                       int n, int klen, int cw, int lane) {
+  const T* xs = st + nrows * klen;
+#pragma unroll 1
+  for (int k = cw * 256 + lane * 8; k < klen; k += kConsumerWarps * 256) {
+    uint4 xv[NT];
+#pragma unroll
+    for (int i = 0; i < NT; ++i) xv[i] = *reinterpret_cast<const uint4*>(xs + min(i, n - 1) * klen + k);
+#pragma unroll
+    for (int j = 0; j < kWideRows; ++j) {
+      const uint4 wv = *reinterpret_cast<const uint4*>(st + min(j, nrows - 1) * klen + k);
+#pragma unroll
+      for (int i = 0; i < NT; ++i) dot8<T>(SLORA_ACC(j * NT + i), wv, xv[i]);
+    }
+  }
+}
+template <int NT>
+__device__ __forceinline__ void shrink_warp_reduce_wide(const float (&acc)[kMaxRows][kTileTokens], float* red_row,
+                                                        int lane) {
+  constexpr int V = kWideRows * NT;
+  float v[V];
+#pragma unroll
+  for (int q = 0; q < V; ++q) v[q] = SLORA_ACC(q);
+  const float tot = warp_reduce_scatter<V>(v, lane);
+  constexpr int SH = V == 32 ? 0 : (V == 16 ? 1 : 2);
+  if ((lane & ((1 << SH) - 1)) == 0) red_row[lane >> SH] = tot;
+}
+#undef SLORA_ACC
+
 // Consumer warp cw owns the K-slice [cw*256, +256) of every chunk: one 16-byte vector per lane per row / token, so a
 // stage is straight-line code with 4 * n independent FMA chains.  At the item's last chunk the warps' partial sums
 // meet in shared memory; the warp that arrives last (an atomic counter, no waiting) adds them in a fixed order and
 // writes delta.  A reduction buffer is reused only kSlots items later, which the ring guarantees to be after the
 // last warp released the stage it was summing in.
-template <typename T>
+template <typename T, bool EXACT>
 __device__ __forceinline__ void shrink_consumer(const ShrinkArgs& a, const unsigned char* ring_mem, PipeCtl& c,
                                                 int lane, int cw) {
   pdl_wait();
@@ -600,7 +646,16 @@ __device__ __forceinline__ void shrink_consumer(const ShrinkArgs& a, const unsig
       }
     }
     const T* st = reinterpret_cast<const T*>(ring_mem + m[6]);
-    if (n <= 1) {
+    const bool wide = EXACT && nrows > kMaxRows;  // an item of up to kWideRows rows (the tile has <= kWideTokens tokens)
+    if (wide) {
+      if (n <= 1) {
+        shrink_accumulate_wide<T, 1>(acc, st, nrows, n, klen, cw, lane);
+      } else if (n <= 2) {
+        shrink_accumulate_wide<T, 2>(acc, st, nrows, n, klen, cw, lane);
+      } else {
+        shrink_accumulate_wide<T, 4>(acc, st, nrows, n, klen, cw, lane);
+      }
+    } else if (n <= 1) {
       shrink_accumulate<T, 1>(acc, st, nrows, n, klen, cw, lane);
     } else if (n <= 2) {
       shrink_accumulate<T, 2>(acc, st, nrows, n, klen, cw, lane);
@@ -614,7 +669,18 @@ __device__ __forceinline__ void shrink_consumer(const ShrinkArgs& a, const unsig
       ++item_seq;
       float* red_row = c.red[buf][cw];
       int nt;  // tokens rounded up to a power of two
-      if (n <= 1) {
+      if (wide) {
+        if (n <= 1) {
+          shrink_warp_reduce_wide<1>(acc, red_row, lane);
+          nt = 1;
+        } else if (n <= 2) {
+          shrink_warp_reduce_wide<2>(acc, red_row, lane);
+          nt = 2;
+        } else {
+          shrink_warp_reduce_wide<4>(acc, red_row, lane);
+          nt = 4;
+        }
+      } else if (n <= 1) {
         shrink_warp_reduce<1>(acc, red_row, lane);
         nt = 1;
       } else if (n <= 2) {
@@ -637,7 +703,7 @@ __device__ __forceinline__ void shrink_consumer(const ShrinkArgs& a, const unsig
       if (old == kConsumerWarps - 1) {
         __threadfence_block();
         const int j = lane / nt, i = lane - j * nt;  // red_row index = row * nt + token
-        if (lane < kMaxRows * nt) {
+        if (lane < (wide ? kWideRows : kMaxRows) * nt) {
           float sum = 0.f;
 #pragma unroll
           for (int w = 0; w < kConsumerWarps; ++w) sum += c.red[buf][w][lane];
@@ -671,13 +737,13 @@ __global__ void __launch_bounds__(kPipeThreads) lora_shrink_pipe_kernel(const Sh
   pipe_init(ctl, tid);
   pdl_launch_dependents();
   if (EXACT) {
-    fill_item_counts(a.src, a.tb, ctl, tid, [&](int rr) { return shrink_items_of(a, rr); });
+    fill_item_counts(a.src, a.tb, ctl, tid, [&](int rr, int n) { return shrink_items_of(a, rr, n); });
     __syncthreads();
   }
   if (warp < kProducerWarps) {
     shrink_producer<T, EXACT>(a, ring_mem, ctl, lane, warp);
   } else {
-    shrink_consumer<T>(a, ring_mem, ctl, lane, warp - kProducerWarps);
+    shrink_consumer<T, EXACT>(a, ring_mem, ctl, lane, warp - kProducerWarps);
   }
   if (a.tp.enabled) tp_link_finish(a.tp, true);
 }
@@ -721,7 +787,7 @@ __device__ __forceinline__ void expand_producer(const ExpandArgs& a, unsigned ch
   r.status = a.status;
   auto rank_ok = [&](int rk) { return expand_rank_ok(a, rk); };
   auto chunks_of = [&](int p, int rk) { return expand_chunks_of(a, p, rk); };
-  const ItemMap map = EXACT ? build_item_map(a.src, total_chunks, c, lane, [&](int rr) { return expand_items_of(a, rr); })
+  const ItemMap map = EXACT ? build_item_map(a.src, total_chunks, c, lane, [&](int rr, int) { return expand_items_of(a, rr); })
                             : padded_item_map(a.src, total_chunks);
   const int mode = EXACT ? map.mode : 0;
   const int64_t n_items = map.n_items;
@@ -959,7 +1025,7 @@ __global__ void __launch_bounds__(kPipeThreads) lora_expand_pipe_kernel(const Ex
   pipe_init(ctl, tid);
   pdl_launch_dependents();
   if (EXACT) {
-    fill_item_counts(a.src, a.tb, ctl, tid, [&](int rr) { return expand_items_of(a, rr); });
+    fill_item_counts(a.src, a.tb, ctl, tid, [&](int rr, int) { return expand_items_of(a, rr); });
     __syncthreads();
   }
   if (warp < kProducerWarps) {

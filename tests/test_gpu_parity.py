@@ -107,7 +107,7 @@ def test_exact_item_count_gives_the_same_bits_as_the_padded_enumeration(case):
                             rank_choices=(8, 32, 64))
     w = wl.to(DEV)
     if case == "many_tiles":
-        assert sl.BatchPlan(w.ids, w.a_start, w.a_len, w.a_loc.numel()).info()[0] > 768
+        assert sl.BatchPlan(w.ids, w.a_start, w.a_len, w.a_loc.numel()).info()[0] > 640
     width = 64 if case == "narrow" else None
     plain = _fused_layer(w, mixed_ranks=False, max_rank=width)
     exact = _fused_layer(w, mixed_ranks=True, max_rank=width)
