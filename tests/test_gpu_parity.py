@@ -301,15 +301,18 @@ def test_unsupported_inputs_raise():
         sl.dispatch_bgmv(d, x_odd, ka, w.a_start, w.a_len, w.a_loc, w.ids, 0, w.a_scaling)
 
 
-def test_adapter_wider_than_the_delta_buffers_is_refused_not_overread():
+@pytest.mark.parametrize("exact_items", [False, True])
+def test_adapter_wider_than_the_delta_buffers_is_refused_not_overread(exact_items):
     """Delta buffers of 16 columns, one adapter of rank 64 in the batch: its tokens are skipped by the expand and the
-    status word says so; nothing is read past a delta row; the other tokens are right."""
+    status word says so; nothing is read past a delta row; the other tokens are right (with the padded and with the
+    exact enumeration of work items)."""
     wl = build_workload(3, pool_rows=4096, n_adapters=6, decode_tokens=40, prefill=None, hidden=1024,
                         rank_choices=(16, 64))
     assert 64 in [wl.ranks[int(a)] for a in wl.ids] and 16 in [wl.ranks[int(a)] for a in wl.ids]
     w = wl.to(DEV)
     ops = sl.LoraBatchOps(w.a_start, w.a_len, w.a_loc, w.a_scaling, w.pools_a, w.pools_b, 16)
-    ops.prepare(w.ids)
+    ops.prepare(w.ids, mixed_ranks=exact_items)
+    assert bool(ops.flags & 4) == exact_items
     q, k, v = (torch.zeros((wl.T, 1024), dtype=wl.dtype, device=DEV) for _ in range(3))
     ops.lora_get_qkv(0, w.x_qkv[0], q, k, v)
     torch.cuda.synchronize()
