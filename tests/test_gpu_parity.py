@@ -324,12 +324,13 @@ def test_adapter_wider_than_the_delta_buffers_is_refused_not_overread(exact_item
     assert_parity(q[narrow.to(DEV)], ref[0][narrow.numpy()], what="rank-16 tokens beside a refused adapter")
 
 
-def test_tensor_parallel_shards_on_one_gpu():
+@pytest.mark.parametrize("T", [24, 200])
+def test_tensor_parallel_shards_on_one_gpu(T):
     """The per-rank shard layout of slora_b200.tp through the real kernels: the N ranks are run one after the other on
     one GPU, their intermediates concatenated the way the all-gather would, and the output slices compared with the
-    single-rank formula."""
+    single-rank formula.  (200 tokens: the backend turns on the exact work-item count for the mixed ranks.)"""
     from slora_b200 import tp
-    H, N, T = 1024, 4, 24
+    H, N = 1024, 4
     ranks = [8, 16, 32, 8]
     g = torch.Generator().manual_seed(21)
     ads = [([torch.randn((r, H), generator=g) / 32 for _ in range(4)],
@@ -356,6 +357,7 @@ def test_tensor_parallel_shards_on_one_gpu():
         gathered = torch.zeros((N, 1, T, Rl), dtype=torch.float16, device=DEV)
         for rank, (t, pa, pb) in enumerate(shards):
             plan = be.make_plan(idd, t)
+            assert bool(be.flags & 4) == (T >= 128)
             be.shrink(plan, idd, [p], [gathered[rank, 0]], xd, pa, t)
         slices = []
         for rank, (t, pa, pb) in enumerate(shards):

@@ -203,7 +203,9 @@ def _worker(rank, world, port, result_dir):
     torch.cuda.set_device(rank)
     dev = torch.device("cuda", rank)
     dist.init_process_group("nccl", device_id=dev)
-    H, T = 4096, 48                            # pool rows of 4096 elements: every kernel of the pipelined family fits
+    # pool rows of 4096 elements: every kernel of the pipelined family fits; 160 tokens of mixed ranks: the backend
+    # asks the plan and turns on the exact work-item count
+    H, T = 4096, 160
     ranks = [8, 16, 32, 16]
     g = torch.Generator().manual_seed(33)
     ads = [([torch.randn((r, H), generator=g) / 32 for _ in range(4)],
