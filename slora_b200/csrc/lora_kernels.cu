@@ -784,8 +784,8 @@ int run_expand(const TileSrc& src, const Tables& tb, const void* w, const void* 
     set_chunks(kPipeChunk);
     const int64_t items = static_cast<int64_t>(src.slots) * a.chunk_begin[nproj];
     const int64_t grid = items < sm_count() * kPipeCtasPerSm ? items : sm_count() * kPipeCtasPerSm;
-    const size_t smem = kRingBytes;
     const bool exact = (flags & SLORA_FLAG_EXACT_ITEMS) != 0 && src.mode == MODE_PLAN;
+    const size_t smem = exact ? kExpandRingBytes : kRingBytes;
     auto go = [&](auto k, int which) {
       const int rc2 = ensure_dyn_smem(k, which, smem);
       return rc2 ? rc2 : launch(k, grid, kPipeThreads, smem, flags, stream, a, "expand(pipelined)");

@@ -43,6 +43,14 @@ constexpr int kSlots = 8;  // stage descriptors (barrier pairs) in flight
 #define SLORA_STAGE_KB 48
 #endif
 constexpr int kRingBytes = SLORA_RING_KB * 1024;  // ring + control block stay below half an SM's shared memory
+#ifndef SLORA_EXPAND_RING_KB
+#define SLORA_EXPAND_RING_KB 104
+#endif
+// The expand's control block is 8 KB smaller (no reduction buffers): with 104 KB three of its ~34 KB stages (a B chunk
+// and one token's y segment and delta row) are in flight instead of two.  Used by the EXACT instantiation (long
+// launches over mixed ranks: measured -4 % on its q,k,v launch); the short launches of a same-rank decode batch
+// measured 2 % slower with it and keep kRingBytes.
+constexpr int kExpandRingBytes = SLORA_EXPAND_RING_KB * 1024;
 constexpr int kPipeCtasPerSm = 2;      // persistent CTAs per SM
 constexpr int kPendSlots = 4;           // stages that may be issued before the grid-dependency wait
 constexpr int kProducerWarps = 1;  // stage g is fed by producer warp g % kProducerWarps
@@ -90,11 +98,15 @@ struct PipeCtl {
     int64_t d_l[32][kWideRows];
     int d_i[32][16];
   } prod[kProducerWarps];
-  // shrink only: per-item partial sums of the consumer warps and the arrival counter that elects the last warp
-  float red[kSlots][kConsumerWarps][32];
-  int red_cnt[kSlots];
   // planned batches of mixed ranks: items up to and including each tile (see build_item_map)
   uint16_t item_end[kCompactTiles];
+};
+
+// Shrink only: per-item partial sums of the consumer warps and the arrival counter that elects the last warp.  (Kept
+// out of PipeCtl so that the expand, which has no use for it, can give those 8 KB to its ring.)
+struct ShrinkRed {
+  float sum[kSlots][kConsumerWarps][32];
+  int cnt[kSlots];
 };
 
 // Producer-side ring state (identical in all 32 lanes).
@@ -106,6 +118,7 @@ struct Ring {
   bool pre = true;    // still before the grid-dependency wait
   int npend = 0;      // stages with stashed activation copies
   bool dead = false;  // a bounded wait ran out
+  uint32_t cap = kRingBytes;  // bytes of the ring
   const TpLink* tp = nullptr;  // expand under tensor parallelism: flags to wait for before activations are read
   int32_t* status = nullptr;
 };
@@ -187,7 +200,7 @@ __device__ __forceinline__ uint32_t ring_alloc(Ring& r, PipeCtl& c, uint32_t sz,
     } else {
       const uint32_t t = c.prod[r.role].off[r.tail % kSlots];
       if (r.head > t) {
-        if (r.head + sz <= kRingBytes) {
+        if (r.head + sz <= r.cap) {
           cand = r.head;
           ok = true;
         } else {
@@ -254,7 +267,6 @@ __device__ __forceinline__ void pipe_init(PipeCtl& c, int tid) {
     for (int s = 0; s < kSlots; ++s) {
       mbar_init(&c.full[s], 1);
       mbar_init(&c.empty[s], kConsumerWarps);
-      c.red_cnt[s] = 0;
     }
     fence_barrier_init();
     fence_proxy_async();
@@ -619,7 +631,7 @@ __device__ __forceinline__ void shrink_warp_reduce_wide(const float (&acc)[kMaxR
 // last warp released the stage it was summing in.
 template <typename T, bool EXACT>
 __device__ __forceinline__ void shrink_consumer(const ShrinkArgs& a, const unsigned char* ring_mem, PipeCtl& c,
-                                                int lane, int cw) {
+                                                ShrinkRed& red, int lane, int cw) {
   pdl_wait();
   float acc[kMaxRows][kTileTokens];
 #pragma unroll
@@ -667,7 +679,7 @@ __device__ __forceinline__ void shrink_consumer(const ShrinkArgs& a, const unsig
     if (flags & FLAG_LAST) {
       const uint32_t buf = item_seq % kSlots;
       ++item_seq;
-      float* red_row = c.red[buf][cw];
+      float* red_row = red.sum[buf][cw];
       int nt;  // tokens rounded up to a power of two
       if (wide) {
         if (n <= 1) {
@@ -697,7 +709,7 @@ __device__ __forceinline__ void shrink_consumer(const ShrinkArgs& a, const unsig
       int old = 0;
       if (lane == 0) {
         __threadfence_block();
-        old = atomicAdd(&c.red_cnt[buf], 1);
+        old = atomicAdd(&red.cnt[buf], 1);
       }
       old = __shfl_sync(FULL_MASK, old, 0);
       if (old == kConsumerWarps - 1) {
@@ -706,7 +718,7 @@ __device__ __forceinline__ void shrink_consumer(const ShrinkArgs& a, const unsig
         if (lane < (wide ? kWideRows : kMaxRows) * nt) {
           float sum = 0.f;
 #pragma unroll
-          for (int w = 0; w < kConsumerWarps; ++w) sum += c.red[buf][w][lane];
+          for (int w = 0; w < kConsumerWarps; ++w) sum += red.sum[buf][w][lane];
           if (j < nrows && i < n && m[3] + j < a.delta_width) {
             if (a.tp.enabled) {
               // tensor parallelism: this rank's rows go straight into every rank's delta buffer (NVLink stores)
@@ -721,7 +733,7 @@ __device__ __forceinline__ void shrink_consumer(const ShrinkArgs& a, const unsig
             }
           }
         }
-        if (lane == 0) c.red_cnt[buf] = 0;
+        if (lane == 0) red.cnt[buf] = 0;
       }
     }
     __syncwarp();
@@ -733,7 +745,9 @@ template <typename T, bool EXACT>
 __global__ void __launch_bounds__(kPipeThreads) lora_shrink_pipe_kernel(const ShrinkArgs a) {
   extern __shared__ __align__(128) unsigned char ring_mem[];
   __shared__ __align__(16) PipeCtl ctl;
+  __shared__ __align__(16) ShrinkRed red;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  if (tid < kSlots) red.cnt[tid] = 0;
   pipe_init(ctl, tid);
   pdl_launch_dependents();
   if (EXACT) {
@@ -743,7 +757,7 @@ __global__ void __launch_bounds__(kPipeThreads) lora_shrink_pipe_kernel(const Sh
   if (warp < kProducerWarps) {
     shrink_producer<T, EXACT>(a, ring_mem, ctl, lane, warp);
   } else {
-    shrink_consumer<T, EXACT>(a, ring_mem, ctl, lane, warp - kProducerWarps);
+    shrink_consumer<T, EXACT>(a, ring_mem, ctl, red, lane, warp - kProducerWarps);
   }
   if (a.tp.enabled) tp_link_finish(a.tp, true);
 }
@@ -783,6 +797,7 @@ __device__ __forceinline__ void expand_producer(const ExpandArgs& a, unsigned ch
   PipeCtl::Prod& pp = c.prod[role];
   Ring r;
   r.role = role;
+  r.cap = EXACT ? kExpandRingBytes : kRingBytes;  // see kExpandRingBytes
   r.tp = a.tp.enabled ? &a.tp : nullptr;
   r.status = a.status;
   auto rank_ok = [&](int rk) { return expand_rank_ok(a, rk); };
