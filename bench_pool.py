@@ -4,7 +4,7 @@ ops on the same GPU (``slora/common/mem_allocator.py:30-39``, ``slora/server/rou
 and ``:186-250``).  Times are per call: ``gpu_us`` from CUDA events, ``host_us`` the wall clock until the call returns
 (a call that reads a size back from the device blocks the host for the whole of it).
 
-    python -m slora_b200.pool_bench [--layers 32] [--pool-rows 65536] [--map-rows 262144] [--rank 64]
+    python bench_pool.py [--layers 32] [--pool-rows 65536] [--map-rows 262144] [--rank 64]
 
 Prints one JSON line.
 """
@@ -16,8 +16,8 @@ import time
 
 import torch
 
-from .infer_adapter import InferAdapter
-from .mem_allocator import MemoryAllocator
+from slora_b200.infer_adapter import InferAdapter
+from slora_b200.mem_allocator import MemoryAllocator
 
 
 class _Layer:

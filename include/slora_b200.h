@@ -208,21 +208,28 @@ int slora_batch_lora_o(const void* plan, const int64_t* ids, void* o, int64_t o_
 /*
  * No counterpart in the reference.  The o-projection LoRA delta (same result as slora_batch_lora_o) for callers that
  * must not allocate device memory: code running inside someone else's memory budget or allocator -- a serving process
- * whose pool already owns the whole GPU, a plugin called where cudaMalloc is forbidden (mid-capture, or from a
- * real-time path that may not block on the driver's allocation lock).  The batch plan and the rank-r intermediate live
- * in an array built into the library (320 KB per GPU, held from library load to process exit) instead of
- * caller-provided workspace and delta buffers; the caller passes only inputs and outputs.
+ * whose pool already owns the whole GPU, a plugin called from a real-time path that may not block on the driver's
+ * allocation lock.  The batch plan and the rank-r intermediate live in an array built into the library (320 KB per
+ * GPU, held from library load to process exit) instead of caller-provided workspace and delta buffers; the caller
+ * passes only inputs and outputs.
  * Limits: T <= 1024 tokens, n_adapters <= 4096, max_rank a multiple of 8 up to 128; beyond them the call fails with
  * SLORA_ERR_WORKSPACE / SLORA_ERR_RANK and launches nothing.  The call never calls cudaMalloc, cudaFree or any
- * allocating routine.  Its first call on a device looks up the array's device address (cudaGetSymbolAddress): make
- * that first call outside any stream capture.  All calls on one GPU share the array: calls whose kernels may overlap
- * on the GPU (different streams without ordering) race on it; calls on one stream are safe back to back.
+ * allocating routine; SLORA_FLAG_BIG_GROUPS is ignored here (that route may create a side stream at first use).
+ * Its first call on a device looks up the array's device address (cudaGetSymbolAddress), which may also make the
+ * CUDA runtime load the library's kernels: make that first call outside any stream capture, and before the host
+ * hands the rest of the GPU's memory to its own pool.  All calls on one GPU share the array, which keeps the last
+ * call's plan: calls whose kernels may overlap on the GPU (different streams without ordering) race on it; calls on
+ * one stream are safe back to back.
+ * The kernels' status word (SLORA_STATUS_*: a token with an adapter id outside the tables, a bad table entry, an
+ * adapter wider than max_rank -- whose tokens are skipped --, a wait that ran out) lives in that array too;
+ * slora_noalloc_status reads the word the latest call on the current device left (synchronises `stream`).
  */
 int slora_batch_lora_o_noalloc(const int64_t* ids, void* o, int64_t o_stride, int h_out, const void* x,
                                int64_t x_stride, int h_in, const void* pool_a, const void* pool_b, int64_t pool_rows,
                                int64_t pool_stride, const int64_t* start, const int64_t* ranks4, const int64_t* loc,
                                const void* scales, int64_t n_adapters, int64_t loc_len, int max_rank, int64_t T,
                                int dtype, unsigned flags, void* stream);
+int slora_noalloc_status(int* status_out, void* stream);
 
 /*
  * Debug check of the tables (the reference has none; its kernels read whatever the tables say).

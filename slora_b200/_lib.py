@@ -64,6 +64,7 @@ _SIGS = {
                                    _P, _P, c_int64, c_int64, _P, c_int64, c_int, c_int64, c_int, c_uint, _P]),
     "slora_batch_lora_o_noalloc": (c_int, [_P, _P, c_int64, c_int, _P, c_int64, c_int, _P, _P, c_int64, c_int64, _P, _P,
                                            _P, _P, c_int64, c_int64, c_int, c_int64, c_int, c_uint, _P]),
+    "slora_noalloc_status": (c_int, [POINTER(c_int), _P]),
     "slora_validate_tables": (c_int, [_P, _P, _P, _P, c_int64, c_int64, c_int64, c_int64, _P, _P]),
     "slora_tp_regroup": (c_int, [_P, _P, _P, _P, c_int, c_int, c_int64, c_int, c_int64, c_int64, c_int, _P]),
     "slora_tp_exchange": (c_int, [_P, _P, _P, _P, _P, _P, _P, c_int, c_int, c_int, c_int64, c_int64, c_int, c_int64,

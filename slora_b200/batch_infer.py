@@ -98,7 +98,7 @@ class LoraBatchOps:
         return cls(infer_adapter.a_start, infer_adapter.a_len, infer_adapter.a_loc, infer_adapter.a_scaling,
                    mm.key_buffer, mm.value_buffer, max_lora_dim, use_pdl)
 
-    def prepare(self, token_adapter_ids, use_plan=True, big_groups=None, mixed_ranks=None):
+    def prepare(self, token_adapter_ids, use_plan=True, big_groups=None, mixed_ranks=None, fused=None):
         """Start a forward: ``token_adapter_ids`` is ``req_bins`` (decode) or ``batch_req_bins`` (prefill).
 
         Allocates the three delta buffers the reference allocates in ``forward`` (``:68-69,75-76``) and builds the
@@ -205,9 +205,34 @@ def lora_o_noalloc(ids, x, o, pool_a, pool_b, a_start, a_len, a_loc, a_scaling, 
     follow each other; calls that could overlap on the GPU would race on the shared scratch.
     """
     _lib.require_cuda(ids, x, o, pool_a, pool_b, a_start, a_len, a_loc, a_scaling)
+    # the C entry takes raw pointers: everything it will index is checked here, before anything is launched
+    for name, t in (("ids", ids), ("a_start", a_start), ("a_len", a_len), ("a_loc", a_loc)):
+        if t.dtype != torch.int64 or t.dim() != 1 or not t.is_contiguous():
+            raise RuntimeError(f"{name} must be a contiguous 1-D int64 tensor")
+    if x.dim() != 2 or o.dim() != 2 or ids.numel() != x.size(0) or o.size(0) != x.size(0):
+        raise RuntimeError("x and o must be 2-D with one row per entry of ids")
+    if not (x.dtype == o.dtype == pool_a.dtype == pool_b.dtype == a_scaling.dtype):
+        raise RuntimeError("x, o, the pools and a_scaling must share one dtype")
+    if x.stride(1) != 1 or o.stride(1) != 1 or x.stride(0) % 8 or o.stride(0) % 8:
+        raise RuntimeError("x and o need unit column stride and rows that start on 16-byte boundaries")
+    if a_start.numel() != a_len.numel() or a_scaling.numel() != a_start.numel() or not a_scaling.is_contiguous():
+        raise RuntimeError("a_start, a_len and a_scaling must have one entry per adapter")
+    pa, pb = pool_a.reshape(pool_a.size(0), -1) if pool_a.is_contiguous() else pool_a, \
+        pool_b.reshape(pool_b.size(0), -1) if pool_b.is_contiguous() else pool_b
+    if pa.dim() != 2 or pb.dim() != 2 or pa.stride(1) != 1 or pb.stride(1) != 1 or pa.stride(0) != pb.stride(0) \
+            or pa.size(0) != pb.size(0):
+        raise RuntimeError("A and B pools must be 2-D views with one shape and one row stride")
     _lib.check(_lib.lib.slora_batch_lora_o_noalloc(
-        ids.data_ptr(), o.data_ptr(), o.stride(0), o.size(1), x.data_ptr(), x.stride(0), x.size(1), pool_a.data_ptr(),
-        pool_b.data_ptr(), pool_a.size(0), pool_a.stride(0), a_start.data_ptr(), a_len.data_ptr(), a_loc.data_ptr(),
+        ids.data_ptr(), o.data_ptr(), o.stride(0), o.size(1), x.data_ptr(), x.stride(0), x.size(1), pa.data_ptr(),
+        pb.data_ptr(), pa.size(0), pa.stride(0), a_start.data_ptr(), a_len.data_ptr(), a_loc.data_ptr(),
         a_scaling.data_ptr(), a_start.numel(), a_loc.numel(), int(max_rank), x.size(0), _lib.dtype_code(x.dtype), flags,
         _lib.current_stream_ptr()))
     return o
+
+
+def noalloc_status() -> int:
+    """Status bits (``_lib.STATUS_BITS``) the latest :func:`lora_o_noalloc` call on the current device left in the
+    built-in scratch -- synchronises the current stream (C entry ``slora_noalloc_status``)."""
+    st = ctypes.c_int(0)
+    _lib.check(_lib.lib.slora_noalloc_status(ctypes.byref(st), _lib.current_stream_ptr()))
+    return st.value

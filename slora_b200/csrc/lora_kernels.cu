@@ -1270,25 +1270,29 @@ constexpr size_t kNoAllocDeltaBytes = static_cast<size_t>(kNoAllocMaxTokens) * 1
 static __device__ __align__(256) unsigned char g_noalloc_scratch[kNoAllocPlanBytes + kNoAllocDeltaBytes];
 
 // Device address of the scratch array on the current device.  In host code the array's name is only a handle; the
-// address a kernel can use comes from cudaGetSymbolAddress, asked once per device with that device current.
+// address a kernel can use comes from cudaGetSymbolAddress, asked once per device with that device current.  The
+// per-device cache is a set of atomics: two host threads that make the first call on a device at the same time both
+// look the address up and store the same value.
 static int noalloc_scratch(unsigned char** out) {
-  static unsigned char* addr[64];
+  static std::atomic<unsigned char*> addr[64];
   int dev = 0;
   cudaError_t e = cudaGetDevice(&dev);
   if (e != cudaSuccess || dev < 0 || dev >= 64) {
     cudaGetLastError();
     return fail(SLORA_ERR_LAUNCH, "cudaGetDevice: %s", e == cudaSuccess ? "device index out of range" : cudaGetErrorString(e));
   }
-  if (addr[dev] == nullptr) {
+  unsigned char* known = addr[dev].load(std::memory_order_acquire);
+  if (known == nullptr) {
     void* p = nullptr;
     e = cudaGetSymbolAddress(&p, g_noalloc_scratch);
     if (e != cudaSuccess || p == nullptr) {
       cudaGetLastError();
       return fail(SLORA_ERR_LAUNCH, "cudaGetSymbolAddress(scratch): %s", cudaGetErrorString(e));
     }
-    addr[dev] = static_cast<unsigned char*>(p);
+    known = static_cast<unsigned char*>(p);
+    addr[dev].store(known, std::memory_order_release);
   }
-  *out = addr[dev];
+  *out = known;
   return SLORA_OK;
 }
 
@@ -1312,12 +1316,30 @@ int slora_batch_lora_o_noalloc(const int64_t* ids, void* o, int64_t o_stride, in
   int rc = noalloc_scratch(&scratch);
   if (rc) return rc;
   if (T == 0) return SLORA_OK;
+  // Routing big same-adapter groups to the tensor-core kernels may fork to a library-owned side stream, which is
+  // created (stream and events) at first use: not in a call that promises to allocate nothing.  The bit is dropped;
+  // such groups run on the CUDA-core kernels here.
+  flags &= ~static_cast<unsigned>(SLORA_FLAG_BIG_GROUPS);
   // the plan kernel clears its own counters; the intermediate needs no clearing (only columns < r are written and read)
   rc = slora_plan_build(scratch, kNoAllocPlanBytes, ids, T, start, ranks4, n_adapters, loc_len, stream);
   if (rc) return rc;
   return slora_batch_lora_o(scratch, ids, o, o_stride, h_out, x, x_stride, h_in, pool_a, pool_b, pool_rows, pool_stride,
                             start, ranks4, loc, scales, n_adapters, loc_len, scratch + kNoAllocPlanBytes, max_rank,
                             max_rank, T, dtype, flags, stream);
+}
+
+int slora_noalloc_status(int* status_out, void* stream) {
+  if (!status_out) return fail(SLORA_ERR_NULL, "status_out is null");
+  unsigned char* scratch = nullptr;
+  int rc = noalloc_scratch(&scratch);
+  if (rc) return rc;
+  int32_t hdr[PH_WORDS];
+  cudaError_t e = cudaMemcpyAsync(hdr, scratch, sizeof(hdr), cudaMemcpyDeviceToHost, static_cast<cudaStream_t>(stream));
+  if (e == cudaSuccess) e = cudaStreamSynchronize(static_cast<cudaStream_t>(stream));
+  if (e != cudaSuccess) return fail(SLORA_ERR_LAUNCH, "noalloc_status: %s", cudaGetErrorString(e));
+  // before the first call on this device the scratch holds no plan: nothing to report
+  *status_out = hdr[PH_MAGIC] == kPlanMagic ? hdr[PH_STATUS] : 0;
+  return SLORA_OK;
 }
 
 int slora_tp_regroup(void* out, const void* gathered, const int64_t* ids, const int64_t* ranks4, int n_parts,

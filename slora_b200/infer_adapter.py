@@ -158,6 +158,13 @@ class InferAdapter:
         self.a_scaling = torch.cat((self.a_scaling, torch.tensor([a.scaling for a in new_adapters],
                                                                  dtype=self.a_scaling.dtype, device=dev)))
         use_stream = prefetch and self.prefetch_stream is not None and dev.type == "cuda"
+        if use_stream:
+            # The row indices were produced by kernels on the current stream (the allocator reads nothing back, so
+            # the host does not wait for them the way the reference's boolean indexing does): the prefetch stream
+            # must not read them, nor the tables' uploads, before those kernels have run; and the allocator's
+            # caching of `new_loc` must know about its second stream.
+            self.prefetch_stream.wait_stream(torch.cuda.current_stream())
+            new_loc.record_stream(self.prefetch_stream)
         ctx = torch.cuda.stream(self.prefetch_stream) if use_stream else _NullCtx()
         with ctx:
             rows = new_loc.clone() if use_stream else new_loc

@@ -107,6 +107,16 @@ class Workload:
         return w + self.T * 2 * self.spec.hidden * esize + self.T * sum(2 * ho * esize for _, ho in dims)
 
 
+def workload_config(wl: "Workload", layers=None, world=1):
+    """The ``config`` object of a benchmark line for this workload (identical for every arm that runs it)."""
+    spec = wl.spec
+    return {"workload": spec.name, "tokens": wl.T, "layers": layers or spec.layers, "hidden": spec.hidden,
+            "kv_width": spec.h_kv, "adapters": spec.n_adapters, "ranks": sorted(set(spec.rank_choices)),
+            "max_rank": wl.max_rank, "pool_rows": spec.pool_rows,
+            "distinct_adapters_in_batch": len(set(wl.ids.tolist())),
+            "parallelism": "1 gpu" if world == 1 else f"slora-tp{world}"}
+
+
 def zipf_probs(n, alpha):
     p = torch.arange(1, n + 1, dtype=torch.float64) ** (-alpha)
     return p / p.sum()
@@ -177,12 +187,15 @@ def fill_pool_rows(pool, loc, std, gen, chunk=8192):
 
 def build_workload(cfg: int, device="cpu", dtype=torch.float16, phys_layers=1, pool_rows=None, n_adapters=None,
                    decode_tokens=None, hidden=None, h_kv=None, permute=True, rank_choices=None, prefill="default",
-                   with_activations=True, rank_div=1) -> Workload:
+                   with_activations=True, rank_div=1, fill="all") -> Workload:
     """Build configuration ``cfg`` (1..5), optionally shrunk (fewer adapters / rows / tokens) for tests.
 
     Tables and batch composition are always drawn on CPU; pool contents and activations are drawn on ``device``
     (seeded per device type, so CPU-built and CUDA-built workloads differ in values but not in structure).
     ``rank_div`` > 1 gives the tables and (random) pool contents of one rank of an N-way tensor-parallel group.
+    ``fill="batch"`` writes only the rows of adapters that occur in the batch (the other rows of the full-size pool
+    stay uninitialised: nothing on the path reads them); the host-side timing legs use it to build a full-size pool
+    in seconds.
     """
     base = SPECS[cfg]
     spec = WorkloadSpec(base.name, hidden or base.hidden, h_kv or (hidden if hidden and base.h_kv == base.hidden
@@ -205,11 +218,15 @@ def build_workload(cfg: int, device="cpu", dtype=torch.float16, phys_layers=1, p
     for _ in range(phys_layers):
         pa = torch.empty((spec.pool_rows, spec.hidden), dtype=dtype, device=dev)
         pb = torch.empty((spec.pool_rows, spec.hidden), dtype=dtype, device=dev)
-        if dev.type == "cpu":
+        if dev.type == "cpu" and fill == "all":
             pa.zero_()
             pb.zero_()
-        fill_pool_rows(pa, a_loc, spec.hidden ** -0.5, g_dev)
-        fill_pool_rows(pb, a_loc, 0.02, g_dev)
+        rows = a_loc
+        if fill == "batch":
+            used = sorted(set(ids.tolist()))
+            rows = torch.cat([a_loc[int(a_start[a]): int(a_start[a]) + int(a_len[a])] for a in used]) if used else a_loc[:0]
+        fill_pool_rows(pa, rows, spec.hidden ** -0.5, g_dev)
+        fill_pool_rows(pb, rows, 0.02, g_dev)
         wl.pools_a.append(pa)
         wl.pools_b.append(pb)
         if with_activations:

@@ -17,11 +17,18 @@ sys.path.insert(0, ROOT)
 from slora_b200.workloads import build_workload  # noqa: E402
 
 CASES = {
-    # name: build_workload keyword arguments (both use hidden 4096, the pool row width the reference kernels need)
+    # name: build_workload keyword arguments (pool row width == hidden, which the reference kernels need)
     "cfg1": dict(cfg=1),
     "mixed": dict(cfg=3, pool_rows=4096, n_adapters=6, decode_tokens=24, prefill=None, rank_choices=(16, 64)),
+    # hidden 5120 (the S4 shape; 5120 x 64 is in the reference's shape list, bgmv_config.h:21), ranks 16 / 32 / 64
+    "wide5120": dict(cfg=4, pool_rows=4096, n_adapters=6, decode_tokens=24, prefill=None, rank_choices=(16, 32, 64)),
 }
 COLS = list(range(0, 4096, 64))
+
+
+def cols_of(hidden):
+    """Output columns kept in the fixture (every 64th)."""
+    return list(range(0, hidden, 64))
 
 
 def ref_lib():
@@ -56,7 +63,7 @@ def main(out_path):
         for p in range(4):
             delta, y = run_reference(lib, w, p)
             out[f"{name}_delta_p{p}"] = delta.cpu().numpy()
-            out[f"{name}_y_p{p}"] = y[:, COLS].cpu().numpy()
+            out[f"{name}_y_p{p}"] = y[:, cols_of(w.spec.hidden)].cpu().numpy()
             out[f"{name}_rowabs_p{p}"] = y.float().abs().sum(dim=1).cpu().numpy()
     np.savez_compressed(out_path, **out)
     print("wrote", out_path)

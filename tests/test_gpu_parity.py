@@ -373,7 +373,7 @@ def test_tensor_parallel_shards_on_one_gpu(T):
         assert_parity(got, want.numpy(), what=f"tp proj {p}")
 
 
-@pytest.mark.parametrize("case", ["cfg1", "mixed"])
+@pytest.mark.parametrize("case", ["cfg1", "mixed", "wide5120"])
 def test_against_outputs_of_the_reference_kernels(case):
     """This library against tests/golden/ref_kernels.npz (outputs of the reference's own CUDA kernels on a B200)."""
     import importlib.util, os
@@ -388,4 +388,4 @@ def test_against_outputs_of_the_reference_kernels(case):
     for p in range(4):
         ref_d = torch.from_numpy(g[f"{case}_delta_p{p}"].astype(np.float32))
         assert (deltas[p].float().cpu() - ref_d).abs().max() <= 2e-3 * ref_d.abs().max()
-        assert_parity(outs[p][:, mod.COLS], g[f"{case}_y_p{p}"].astype(np.float32), what=f"ref kernels {case} p{p}")
+        assert_parity(outs[p][:, mod.cols_of(wl.spec.hidden)], g[f"{case}_y_p{p}"].astype(np.float32), what=f"ref kernels {case} p{p}")

@@ -249,3 +249,42 @@ def test_infer_adapter_load_offload_cycles_on_the_gpu_match_the_cpu_pool():
         rows = ic.a_loc
         assert torch.equal(mc.key_buffer[l][rows], mg.key_buffer[l].cpu()[rows])
         assert torch.equal(mc.value_buffer[l][rows], mg.value_buffer[l].cpu()[rows])
+
+
+@pytest.mark.parametrize("name", ["small", "ragged"])
+def test_device_pool_reproduces_the_reference_traces(name):
+    """Traces of the reference's own MemoryAllocator / InferAdapter (tests/golden/ref_pool.npz) replayed on a CUDA
+    pool: row allocation, release, adapter load and table compaction by the library's kernels, bit-exact after every
+    step, pool contents included."""
+    from tests import pool_replay
+    assert pool_replay.replay_host_mirror(name, DEV) >= 40
+
+
+def test_prefetch_on_a_side_stream_loads_the_same_rows_as_a_synchronous_load():
+    """load_adapters(prefetch=True) with a real prefetch stream: the row indices come from kernels on the current
+    stream and are consumed on the prefetch stream, which has to wait for them."""
+    H, heads, L = 1024, 8, 4
+    ads = [_Adapter(f"a{i}", r, H, heads, L, 90 + i) for i, r in enumerate([64, 8, 32, 16, 64])]
+    pools = []
+    for side in (False, True):
+        mm = _pool(DEV, 3000, L, heads, H // heads)
+        for l in range(L):
+            mm.key_buffer[l].zero_()
+            mm.value_buffer[l].zero_()
+        stream = torch.cuda.Stream() if side else None
+        ia = sl.InferAdapter.init(mm, stream)
+        mm.alloc(13)
+        # keep the current stream busy so that an unordered prefetch stream would run ahead of the allocation kernels
+        busy = torch.empty((8192, 8192), device=DEV)
+        for _ in range(4):
+            busy.normal_()
+        ia.load_adapters(ads, prefetch=side)
+        if side:
+            torch.cuda.current_stream().wait_stream(stream)
+        torch.cuda.synchronize()
+        pools.append((mm, ia))
+    (m0, i0), (m1, i1) = pools
+    assert i0.a_loc.tolist() == i1.a_loc.tolist() and i0.a_start.tolist() == i1.a_start.tolist()
+    for l in range(L):
+        assert torch.equal(m0.key_buffer[l], m1.key_buffer[l]) and torch.equal(m0.value_buffer[l], m1.value_buffer[l])
+    assert float(m1.key_buffer[0][i1.a_loc].abs().max()) > 0

@@ -141,17 +141,18 @@ def _ref_cases():
     spec = importlib.util.spec_from_file_location("make_ref_golden", os.path.join(GOLDEN, "make_ref_golden.py"))
     mod = importlib.util.module_from_spec(spec)
     spec.loader.exec_module(mod)
-    return mod.CASES, mod.COLS
+    return mod.CASES, mod.cols_of
 
 
-@pytest.mark.parametrize("case", ["cfg1", "mixed"])
+@pytest.mark.parametrize("case", ["cfg1", "mixed", "wide5120"])
 def test_oracle_against_outputs_of_the_reference_kernels(case):
     """tests/golden/ref_kernels.npz holds what the reference's own BGMV CUDA kernels (compiled from the reference tree,
     run on a B200) produced on these seeded inputs; the oracle must agree within fp16 rounding of the stored values."""
-    cases, cols = _ref_cases()
+    cases, cols_of = _ref_cases()
     g = np.load(os.path.join(GOLDEN, "ref_kernels.npz"))
     wl = build_workload(**cases[case])
     H = wl.spec.hidden
+    cols = cols_of(H)
     for p in range(4):
         x = wl.x_o[0] if p == 3 else wl.x_qkv[0]
         d = orc.lora_shrink_ref(x, wl.pools_a[0], wl.a_start, wl.a_len, wl.a_loc, wl.ids, p, out_width=wl.max_rank)

@@ -52,3 +52,21 @@ def test_host_allocator_on_a_cpu_pool_follows_the_oracle():
             held.append(got)
         assert mm.mem_state.numpy().tolist() == state.tolist()
         assert mm.can_use_mem_size == int(state.sum())
+
+
+# ---------------------------------------------------------------------------------------------------------------
+# pinned to the reference: traces of its own MemoryAllocator / InferAdapter (tests/golden/make_pool_golden.py)
+# ---------------------------------------------------------------------------------------------------------------
+import pytest  # noqa: E402
+
+from tests import pool_replay  # noqa: E402
+
+
+@pytest.mark.parametrize("name", ["small", "ragged"])
+def test_oracle_reproduces_every_step_of_the_reference_traces(name):
+    assert pool_replay.replay_oracle(name) >= 20
+
+
+@pytest.mark.parametrize("name", ["small", "ragged"])
+def test_host_mirror_on_a_cpu_pool_reproduces_the_reference_traces(name):
+    assert pool_replay.replay_host_mirror(name, "cpu") >= 40
