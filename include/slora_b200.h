@@ -69,6 +69,18 @@ extern "C" {
                                     rank-16/32/64 mix, 30 % on a rank-8..64 mix); with one rank that fills the delta
                                     buffers the plain enumeration is exact already and starts a few hundred
                                     nanoseconds sooner. */
+#define SLORA_FLAG_FUSED 8u /* slora_batch_lora_qkv / slora_batch_lora_o: run the call's shrink and expand as ONE
+                              launch in which the CTA that shrinks a (tile, projection) also expands it, the
+                              intermediate staying in shared memory (the caller's delta buffers are then not
+                              written).  Same bits in y as the two launches.  Worth it when the adapters of the
+                              batch are small (a rank-8 decode batch: the fixed part of a launch is as long as its
+                              streaming); with large or mixed ranks the two launches balance their work items
+                              better.  Ignored (two launches) where the fused kernel does not apply: segment calls,
+                              SLORA_FLAG_BIG_GROUPS, layouts the pipelined kernels do not take. */
+#define SLORA_FLAG_ONLY_BIG 16u /* with SLORA_FLAG_BIG_GROUPS on a planned call: EVERY group of the plan is a big
+                                  group that the tensor-core kernels serve (slora_plan_header: no small tiles, every big
+                                  group's rank a power of two that divides pool_stride and fits the delta buffers), so
+                                  the call's CUDA-core launch would find nothing and is left out. */
 
 /* Bits of the device status word (plan header / status argument). */
 #define SLORA_STATUS_BAD_ID 1      /* a token's adapter id was outside [0, n_adapters) - token skipped   */
@@ -160,6 +172,13 @@ int slora_plan_big_tiles(const void* workspace, int* n_big_out, void* stream);
 int slora_plan_info(const void* workspace, int* n_tiles_out, int* n_big_out, int* uniform_rank_out, void* stream);
 
 int slora_plan_status(const void* workspace, int* status_out, int* n_tiles_out, void* stream);
+/*
+ * The plan's 16 header words, for callers that choose flags from them: [1] 8-token tiles, [2] status bits, [4] tokens,
+ * [5] adapters, [6] 128-token tiles of big groups, [9] the slot rows (rank) every group shares or 0, [10] 8-token tiles
+ * of groups that are not big, [11] widest rank among the big groups, [12] 1 when every big group's rank is a power
+ * of two.  Reads the header back: synchronises `stream`.  No counterpart in the reference.
+ */
+int slora_plan_header(const void* workspace, int32_t out[16], void* stream);
 
 /*
  * Planned multi-projection calls.  nproj in 1..3 projections share the activations x (shrink) and the tables.

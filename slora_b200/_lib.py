@@ -17,6 +17,8 @@ F16, BF16 = 0, 1
 FLAG_PDL = 1
 FLAG_BIG_GROUPS = 2
 FLAG_EXACT_ITEMS = 4
+FLAG_FUSED = 8
+FLAG_ONLY_BIG = 16
 
 STATUS_BITS = {1: "bad adapter id", 2: "bad table entry", 4: "unsupported rank", 8: "bulk-copy wait timed out"}
 
@@ -86,6 +88,7 @@ _SIGS = {
     "slora_tables_compact": (c_int, [_P, _P, _P, _P, _P, c_int64, c_int64, _P, _P, _P, _P, _P, _P, _P, c_int64, _P,
                                      _P]),
     "slora_plan_info": (c_int, [_P, _P, _P, _P, _P]),
+    "slora_plan_header": (c_int, [_P, _P, _P]),
     "slora_launch_counts": (None, [_P]),
     "slora_plan_big_tiles": (c_int, [_P, _P, _P]),
 }

@@ -11,10 +11,14 @@ embedding stay with the caller, exactly where the reference has them.
 from __future__ import annotations
 
 import ctypes
+import os
 
 import torch
 
 from . import _lib
+
+
+FUSED_MAX_RANK = 16   # delta width up to which prepare() picks the one-launch kernels by itself
 
 
 class BatchPlan:
@@ -67,6 +71,13 @@ class BatchPlan:
                                             _lib.current_stream_ptr()))
         return nt.value, nb.value, ur.value
 
+    def header(self):
+        """The plan's header as a dict -- synchronises the stream (C entry ``slora_plan_header``)."""
+        buf = (ctypes.c_int32 * 16)()
+        _lib.check(_lib.lib.slora_plan_header(self.ptr, buf, _lib.current_stream_ptr()))
+        return {"tiles": buf[1], "status": buf[2], "tokens": buf[4], "adapters": buf[5], "big_tiles": buf[6],
+                "uniform_rank": buf[9], "small_tiles": buf[10], "big_rank_max": buf[11], "big_ranks_pow2": bool(buf[12])}
+
     def check(self):
         st, _ = self.status()
         if st:
@@ -112,6 +123,10 @@ class LoraBatchOps:
         ``mixed_ranks``: do the batch's adapters differ in rank, or are all narrower than ``max_lora_dim``?  Then
         the kernels count their work items exactly (``SLORA_FLAG_EXACT_ITEMS``; a matter of speed only).  ``None``
         asks the plan in the same read-back; batches below 128 tokens are not asked and keep the plain enumeration.
+
+        ``fused``: run the shrink and the expand of a call as one launch (``SLORA_FLAG_FUSED``; same bits, the delta
+        buffers are then not written).  ``None`` picks it for delta widths up to ``FUSED_MAX_RANK`` when neither of
+        the two flags above is set: small adapters, where a launch's fixed cost rivals its streaming time.
         """
         self.ids = token_adapter_ids.contiguous()
         T = self.ids.numel()
@@ -119,16 +134,30 @@ class LoraBatchOps:
         self.delta = [torch.zeros((T, self.max_lora_dim), dtype=dtype, device=self.ids.device) for _ in range(3)]
         self.plan = BatchPlan(self.ids, self.a_start, self.a_len, self.a_loc.numel()) if use_plan else None
         self.flags = self.base_flags
+        only_big = False
         if self.plan is not None and T >= 128 and (big_groups is None or mixed_ranks is None):
-            _, n_big, uniform = self.plan.info()
+            h = self.plan.header()
             if big_groups is None:
-                big_groups = n_big > 0
+                big_groups = h["big_tiles"] > 0
+                # a pure prefill batch: every group is big and of a rank the tensor-core kernels take
+                stride = self.key_buffer[0].stride(0)
+                only_big = (big_groups and h["small_tiles"] == 0 and h["big_ranks_pow2"] and
+                            8 <= h["big_rank_max"] <= min(self.max_lora_dim, 128) and stride % h["big_rank_max"] == 0)
             if mixed_ranks is None:
-                mixed_ranks = uniform == 0 or uniform < self.max_lora_dim
+                mixed_ranks = h["uniform_rank"] == 0 or h["uniform_rank"] < self.max_lora_dim
         if self.plan is not None and big_groups:
             self.flags |= _lib.FLAG_BIG_GROUPS
+            if only_big:
+                self.flags |= _lib.FLAG_ONLY_BIG
         if self.plan is not None and mixed_ranks:
             self.flags |= _lib.FLAG_EXACT_ITEMS
+        if fused is None and os.environ.get("SLORA_FUSED") in ("0", "1"):      # A/B timing from outside
+            fused = os.environ["SLORA_FUSED"] == "1"
+        if fused is None:
+            # one launch per call pays when every adapter is small: its fixed part is then as long as its streaming
+            fused = self.max_lora_dim <= FUSED_MAX_RANK and not big_groups and not mixed_ranks
+        if fused and not big_groups:
+            self.flags |= _lib.FLAG_FUSED
         return self
 
     def _common(self, layer_id):

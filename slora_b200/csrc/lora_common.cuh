@@ -25,6 +25,9 @@ constexpr uint32_t kSpinLimit = 1u << 18;
 // big-tile record: {adapter, first slot in perm, tokens, slot_rows r, first loc entry, 0, 0, 0}
 constexpr int PH_MAGIC = 0, PH_NTILES = 1, PH_STATUS = 2, PH_MAXTILES = 3, PH_T = 4, PH_NADAPTERS = 5, PH_NBIG = 6,
               PH_BIGOFF = 7, PH_MAXBIG = 8, PH_UNIFORM = 9;  // PH_UNIFORM: the slot rows every non-empty tile has, 0 when they differ
+// PH_NSMALL: 8-token tiles of groups that are not big (the CUDA-core kernels' share when big groups go to the tensor
+// cores); PH_BIG_RMAX: widest rank among the big groups; PH_BIG_POW2: 1 when every big group's rank is a power of two
+constexpr int PH_NSMALL = 10, PH_BIG_RMAX = 11, PH_BIG_POW2 = 12;
 constexpr int kBigGroupTokens = 128;  // planned batches: same-adapter groups at least this long go to the tensor cores
 constexpr int kBigSegmentTokens = 32;  // segment calls: segments at least this long do
 constexpr int kBigTileTokens = 128;

@@ -741,12 +741,37 @@ __device__ __forceinline__ void shrink_consumer(const ShrinkArgs& a, const unsig
   }
 }
 
+// A segment call sends its long segments to the tensor-core kernels and launches these kernels beside them for the
+// short ones.  When there are none (a pure prefill batch) the launch has nothing to do: every CTA finds that out from
+// the segment table with one round of loads per table (a thread per segment) and leaves before it sets up its ring,
+// instead of resolving every tile slot of every segment first.  A segment whose table entries look wrong counts as
+// this launch's, whose normal path reports it.
+__device__ __forceinline__ bool segments_all_elsewhere(const TileSrc& s, const Tables& tb) {
+  if (s.mode != MODE_SEGMENT || s.seg_split <= 0) return false;
+  bool mine = false;
+  for (int i = threadIdx.x; i < s.n_seg; i += blockDim.x) {
+    const int64_t len = s.seg_len[i];
+    if (len <= 0) continue;
+    const int64_t ad = s.ids[i];
+    if (len < s.seg_split || ad < 0 || ad >= tb.n_adapters) {
+      mine = true;
+      continue;
+    }
+    const int64_t r4 = tb.ranks4[ad], st = tb.start[ad], r = r4 >> 2;
+    if (r4 < 0 || st < 0 || st + r4 > tb.loc_len ||
+        !(r >= 8 && r <= 128 && r % 8 == 0 && tb.pool_stride % r == 0 && r <= s.mma_max_rows))
+      mine = true;
+  }
+  return __syncthreads_or(mine) == 0;
+}
+
 template <typename T, bool EXACT>
 __global__ void __launch_bounds__(kPipeThreads) lora_shrink_pipe_kernel(const ShrinkArgs a) {
   extern __shared__ __align__(128) unsigned char ring_mem[];
   __shared__ __align__(16) PipeCtl ctl;
   __shared__ __align__(16) ShrinkRed red;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  if (segments_all_elsewhere(a.src, a.tb)) return;
   if (tid < kSlots) red.cnt[tid] = 0;
   pipe_init(ctl, tid);
   pdl_launch_dependents();
@@ -947,7 +972,8 @@ __device__ __forceinline__ void expand_producer(const ExpandArgs& a, unsigned ch
 // [cw*2048, +2048) of the chunk as 8 loads of 256 elements; load m, lane l holds the 8 values of output
 // (cw*8 + m)*(32/LPO) + l/LPO for k in [(l % LPO)*8, +8).
 template <typename T, int LPO, bool FULL>
-__device__ __forceinline__ void expand_stage(const T* bs, const int* m, T* y, int64_t y_stride, int lane, int cw) {
+__device__ __forceinline__ void expand_stage(const T* bs, const int* m, T* y, int64_t y_stride, int lane, int cw,
+                                             const T* ds_ext = nullptr, int ds_ext_stride = 0) {
   constexpr int OPL = 32 / LPO;
   constexpr int NV = LPO >= 8 ? 1 : 8 / LPO;
   constexpr int R = LPO * 8;
@@ -957,7 +983,9 @@ __device__ __forceinline__ void expand_stage(const T* bs, const int* m, T* y, in
   const int nout = clen / R;
   const float scale = __int_as_float(m[6]);
   const T* ys = bs + clen;
-  const T* ds = ys + n * nout;
+  // the tokens' delta rows: behind the y segments in the stage, or (fused kernel) wherever the shrink phase left them
+  const T* ds = ds_ext ? ds_ext : ys + n * nout;
+  const int dstr = ds_ext ? ds_ext_stride : R;
   uint4 bv[8];
 #pragma unroll
   for (int mm = 0; mm < 8; ++mm) {
@@ -973,7 +1001,7 @@ __device__ __forceinline__ void expand_stage(const T* bs, const int* m, T* y, in
   for (int i = 0; i < NV; ++i) o_loc[i] = (cw * 8 + m_base + i) * OPL + g;  // output index inside the chunk
 
   for (int tt = 0; tt < n; ++tt) {
-    const uint4 dv = *reinterpret_cast<const uint4*>(ds + tt * R + kp);
+    const uint4 dv = *reinterpret_cast<const uint4*>(ds + tt * dstr + kp);
     float yv[NV];
 #pragma unroll
     for (int i = 0; i < NV; ++i) {
@@ -1037,6 +1065,7 @@ __global__ void __launch_bounds__(kPipeThreads) lora_expand_pipe_kernel(const Ex
   extern __shared__ __align__(128) unsigned char ring_mem[];
   __shared__ __align__(16) PipeCtl ctl;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  if (segments_all_elsewhere(a.src, a.tb)) return;
   pipe_init(ctl, tid);
   pdl_launch_dependents();
   if (EXACT) {

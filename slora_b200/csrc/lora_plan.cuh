@@ -22,7 +22,7 @@ __global__ void __launch_bounds__(1024) plan_build_kernel(int32_t* ws, const int
   const int big_off = (PH_WORDS + kTileWords * max_tiles + 2 * T + n_adapters + 3) & ~3;  // 16-byte aligned records
   int32_t* big = ws + big_off;
   __shared__ int s_tok[32], s_tile[32], s_big[32];
-  __shared__ int s_status, s_rmin, s_rmax;
+  __shared__ int s_status, s_rmin, s_rmax, s_nsmall, s_big_rmax, s_big_pow2;
   const int tid = threadIdx.x, nthr = blockDim.x, lane = tid & 31, warp = tid >> 5;
 
   for (int i = tid; i < n_adapters; i += nthr) cnt[i] = 0;
@@ -30,6 +30,9 @@ __global__ void __launch_bounds__(1024) plan_build_kernel(int32_t* ws, const int
     s_status = 0;
     s_rmin = 0x7fffffff;
     s_rmax = 0;
+    s_nsmall = 0;
+    s_big_rmax = 0;
+    s_big_pow2 = 1;
   }
   __syncthreads();
   for (int t = tid; t < T; t += nthr) {
@@ -115,6 +118,13 @@ __global__ void __launch_bounds__(1024) plan_build_kernel(int32_t* ws, const int
         atomicMin(&s_rmin, static_cast<int>(r4 >> 2));
         atomicMax(&s_rmax, static_cast<int>(r4 >> 2));
       }
+      if (bigg) {
+        const int rr = static_cast<int>(r4 >> 2);
+        atomicMax(&s_big_rmax, rr);
+        if (rr & (rr - 1)) s_big_pow2 = 0;
+      } else if (good) {
+        atomicAdd(&s_nsmall, (c + kTileTokens - 1) / kTileTokens);
+      }
       for (int i = 0; i * kTileTokens < c; ++i) {
         if (tile_off < max_tiles) {
           int4* rec = reinterpret_cast<int4*>(tiles + kTileWords * tile_off);
@@ -152,6 +162,9 @@ __global__ void __launch_bounds__(1024) plan_build_kernel(int32_t* ws, const int
     hdr[PH_BIGOFF] = big_off;
     hdr[PH_MAXBIG] = max_big;
     hdr[PH_UNIFORM] = s_rmin == s_rmax ? s_rmax : 0;
+    hdr[PH_NSMALL] = s_nsmall;
+    hdr[PH_BIG_RMAX] = s_big_rmax;
+    hdr[PH_BIG_POW2] = s_big_pow2;
   }
 }
 

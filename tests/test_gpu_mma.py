@@ -194,3 +194,40 @@ def test_empty_and_out_of_range_segments_are_ignored():
     torch.cuda.synchronize()
     assert float(guard.min()) == 9.0
     assert_parity(y, _oracle(wl, 0), what="ragged segment table")
+
+
+def test_pure_prefill_batch_launches_no_cuda_core_kernel():
+    """Every group of the plan is a big group the tensor-core kernels serve (sequences of 128 tokens or more, ranks
+    that are powers of two): prepare() finds that in the plan header and the four calls launch the four tensor-core
+    kernels only.  One short sequence more and the CUDA-core launches are back."""
+    wl = build_workload(3, pool_rows=8192, n_adapters=16, decode_tokens=0, prefill=("seqs", 4, 130, 400), hidden=1024)
+    w = wl.to(DEV)
+    before = sl.launch_counts()
+    outs = _planned_layer(wl, w)
+    after = sl.launch_counts()
+    assert after["tensor_core"] - before["tensor_core"] == 4
+    assert sum(after[k] - before[k] for k in ("pipelined", "simple")) == 0
+    for p in range(4):
+        assert_parity(outs[p], _oracle(wl, p), what=f"pure prefill proj {p}")
+    h = sl.BatchPlan(w.ids, w.a_start, w.a_len, w.a_loc.numel()).header()
+    assert h["small_tiles"] == 0 and h["big_tiles"] > 0 and h["big_ranks_pow2"] and h["tokens"] == wl.T
+    wl2 = build_workload(3, pool_rows=8192, n_adapters=16, decode_tokens=1, prefill=("seqs", 4, 130, 400), hidden=1024)
+    w2 = wl2.to(DEV)
+    before = sl.launch_counts()
+    outs = _planned_layer(wl2, w2)
+    after = sl.launch_counts()
+    assert sum(after[k] - before[k] for k in ("pipelined", "simple")) == 4
+    for p in range(4):
+        assert_parity(outs[p], _oracle(wl2, p), what=f"prefill + one decode token proj {p}")
+
+
+def test_segment_call_without_short_segments_leaves_its_cuda_core_launch_early():
+    """Segments of 32 tokens or more only: the accompanying CUDA-core launch finds nothing to do (its early exit);
+    results are those of the tensor-core kernels.  With one short segment added its rows are computed as well."""
+    for short in (0, 1):
+        wl = build_workload(3, pool_rows=8192, n_adapters=12, decode_tokens=short, prefill=("seqs", 3, 40, 200),
+                            hidden=1024)
+        w = wl.to(DEV)
+        for p in (0, 3):
+            _, y = _run_segments(wl, w, p)
+            assert_parity(y, _oracle(wl, p), what=f"segments, {short} short, proj {p}")
