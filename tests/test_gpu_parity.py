@@ -400,7 +400,7 @@ def test_one_launch_per_call_gives_the_same_bits_as_two(case):
     if case == "s1":
         wl = build_workload(2, pool_rows=65536)
     elif case == "rank16_gqa":
-        wl = build_workload(5, pool_rows=8192, n_adapters=50, decode_tokens=300, hidden=2048, h_kv=512,
+        wl = build_workload(5, pool_rows=8192, n_adapters=50, decode_tokens=300, hidden=4096, h_kv=512,
                             rank_choices=(16,))
     elif case == "tokens":
         wl = build_workload(2, pool_rows=8192, n_adapters=20, decode_tokens=70, hidden=1024)
