@@ -72,7 +72,6 @@ def parse_args(argv=None):
     ap.add_argument("--no-decode-extra", action="store_true",
                     help="leave out the configuration-2 figures that the default single-GPU line carries")
     ap.add_argument("--no-gpu-reference", action="store_true")
-    ap.add_argument("--no-fused", action="store_true", help="keep shrink and expand as separate launches")
     ap.add_argument("--replays", type=int, default=100, help="graph replays behind the median figure")
     ap.add_argument("--cpu-seconds", type=float, default=10.0)
     ap.add_argument("--pool-rows", type=int, default=None)
@@ -90,6 +89,9 @@ def parse_args(argv=None):
                     help="secondary line: long same-adapter sequences, served by the tensor-core kernels")
     ap.add_argument("--prefill-seqs", type=int, default=8)
     ap.add_argument("--prefill-len", type=int, default=512)
+    ap.add_argument("--scheduler", action="store_true",
+                    help="secondary line: what the adapter-clustering request queue is worth on the LoRA path "
+                         "(bench_sched.py)")
     ap.add_argument("--adapter-swap", action="store_true",
                     help="secondary line: pool row allocation, adapter load and offload, the library's kernels beside "
                          "the same steps on torch ops (bench_pool.py)")
@@ -284,7 +286,7 @@ class Runner:
         self.o = [torch.zeros((wl.T, H), dtype=dt, device=device) for _ in range(self.P)]
         self.ops = sl.LoraBatchOps(wl.a_start, wl.a_len, wl.a_loc, wl.a_scaling, wl.pools_a, wl.pools_b, wl.max_rank,
                                    use_pdl=not args.no_pdl)
-        self.ops.prepare(wl.ids, use_plan=not args.no_plan, **({"fused": False} if args.no_fused else {}))
+        self.ops.prepare(wl.ids, use_plan=not args.no_plan)
         self.launches_per_step = 4 * self.L  # replaced by the library's own count of the first eager step
         self.graph = None
 
@@ -367,8 +369,7 @@ NCU_TRAFFIC_RATIO = {
 
 def kernel_roofline(run, peak_gbs, peak_kind):
     """Average duration of the q/k/v expand launch (the largest kernel of the step) and of the q/k/v shrink launch:
-    a CUDA graph holding one launch per layer of that kernel alone, CUDA-event timed.  When the step runs shrink and
-    expand of a call as one launch (same-rank decode batches), that launch is timed the same way as well."""
+    a CUDA graph holding one launch per layer of that kernel alone, CUDA-event timed."""
     from slora_b200 import batch_infer
     wl, ops = run.wl, run.ops
     dims = wl.proj_dims()
@@ -378,7 +379,7 @@ def kernel_roofline(run, peak_gbs, peak_kind):
     y_bytes = wl.T * sum(2 * dims[p][1] * es for p in range(3))
     a_bytes = sum(wl.ranks[a] * dims[p][0] * es for a in distinct for p in range(3))
     x_bytes = wl.T * dims[0][0] * es
-    flags = ops.flags & ~getattr(batch_infer._lib, "FLAG_FUSED", 0)
+    flags = ops.flags  # programmatic launch, exact item count and tensor-core routing as the step itself uses them
 
     def shrinks():
         for l in range(run.L):
@@ -393,19 +394,11 @@ def kernel_roofline(run, peak_gbs, peak_kind):
                                      wl.pools_b[p], wl.a_start, wl.a_len, wl.a_loc, wl.a_scaling,
                                      ops.delta[0].stride(0), wl.max_rank, flags=flags)
 
-    def fused_calls():
-        for l in range(run.L):
-            p = l % run.P
-            ops.lora_get_qkv(p, wl.x_qkv[p], run.q[p], run.k[p], run.v[p])
-
     t_shrink = _graph_time(shrinks, run.L) * 1e-6
     t_expand = _graph_time(expands, run.L) * 1e-6
     out = {}
     rows = [("lora_expand_pipe_kernel(qkv)", "expand", t_expand, b_bytes + y_bytes),
             ("lora_shrink_pipe_kernel(qkv)", "shrink", t_shrink, a_bytes + x_bytes)]
-    if ops.flags & getattr(batch_infer._lib, "FLAG_FUSED", 0):
-        t_fused = _graph_time(fused_calls, run.L) * 1e-6
-        rows.insert(0, ("lora_fused_pipe_kernel(qkv)", "fused", t_fused, a_bytes + x_bytes + b_bytes + y_bytes))
     for name, kind, t, nbytes in rows:
         ratio = NCU_TRAFFIC_RATIO.get((wl.spec.cfg, kind))
         out[kind] = {"bound": "hbm", "achieved": nbytes / t / 1e9, "peak": peak_gbs, "unit": "GB/s",
@@ -552,7 +545,6 @@ def e2e_measure(run, steps, warmup):
     s_in, s_out = torch.cuda.Stream(), torch.cuda.Stream()
     ev_in = [torch.cuda.Event() for _ in range(L)]
     ev_done = [torch.cuda.Event() for _ in range(L)]
-    kw = {"fused": False} if run.args.no_fused else {}
     times = []
     for it in range(warmup + steps):
         y_dev.zero_()
@@ -567,7 +559,7 @@ def e2e_measure(run, steps, warmup):
                 x_dev[l].copy_(x_host[l], non_blocking=True)
                 ev_in[l].record(s_in)
         ids_dev.copy_(ids_host, non_blocking=True)
-        ops.prepare(ids_dev, use_plan=not run.args.no_plan, **kw)
+        ops.prepare(ids_dev, use_plan=not run.args.no_plan)
         for l in range(L):
             p = l % run.P
             yl = y_dev[l]
@@ -646,7 +638,7 @@ def measure_single(args, cfg, device, rank, world, dist, peak, extras=True):
         med["tokens_per_s_median"] = wl.T / med["ms_per_step_median"] * 1e3
         out["replay_median"] = med
     roof = kernel_roofline(run, peak_gbs, peak_kind)
-    out["roofline"] = roof.get("fused") or roof["expand"]
+    out["roofline"] = roof["expand"]
     out["roofline_kernels"] = roof
     if extras and not args.no_e2e:
         e_steps = max(3, min(args.steps, 10))
@@ -780,6 +772,11 @@ def main():
         return
     if args.prefill:
         prefill_bench(args, device, peak)
+        return
+    if args.scheduler:
+        import bench_sched
+        if rank == 0:
+            print(json.dumps(bench_sched.run(device)), flush=True)
         return
     if args.adapter_swap:
         import bench_pool

@@ -69,14 +69,6 @@ extern "C" {
                                     rank-16/32/64 mix, 30 % on a rank-8..64 mix); with one rank that fills the delta
                                     buffers the plain enumeration is exact already and starts a few hundred
                                     nanoseconds sooner. */
-#define SLORA_FLAG_FUSED 8u /* slora_batch_lora_qkv / slora_batch_lora_o: run the call's shrink and expand as ONE
-                              launch in which the CTA that shrinks a (tile, projection) also expands it, the
-                              intermediate staying in shared memory (the caller's delta buffers are then not
-                              written).  Same bits in y as the two launches.  Worth it when the adapters of the
-                              batch are small (a rank-8 decode batch: the fixed part of a launch is as long as its
-                              streaming); with large or mixed ranks the two launches balance their work items
-                              better.  Ignored (two launches) where the fused kernel does not apply: segment calls,
-                              SLORA_FLAG_BIG_GROUPS, layouts the pipelined kernels do not take. */
 #define SLORA_FLAG_ONLY_BIG 16u /* with SLORA_FLAG_BIG_GROUPS on a planned call: EVERY group of the plan is a big
                                   group that the tensor-core kernels serve (slora_plan_header: no small tiles, every big
                                   group's rank a power of two that divides pool_stride and fits the delta buffers), so

@@ -11,13 +11,12 @@ import os
 from ctypes import c_int, c_int32, c_int64, c_size_t, c_uint, c_void_p, c_char_p, POINTER
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_HERE, "libslora_b200.so")
+LIB_PATH = os.environ.get("SLORA_B200_LIB") or os.path.join(_HERE, "libslora_b200.so")   # override: a development build
 
 F16, BF16 = 0, 1
 FLAG_PDL = 1
 FLAG_BIG_GROUPS = 2
 FLAG_EXACT_ITEMS = 4
-FLAG_FUSED = 8
 FLAG_ONLY_BIG = 16
 
 STATUS_BITS = {1: "bad adapter id", 2: "bad table entry", 4: "unsupported rank", 8: "bulk-copy wait timed out"}

@@ -11,14 +11,10 @@ embedding stay with the caller, exactly where the reference has them.
 from __future__ import annotations
 
 import ctypes
-import os
 
 import torch
 
 from . import _lib
-
-
-FUSED_MAX_RANK = 16   # delta width up to which prepare() picks the one-launch kernels by itself
 
 
 class BatchPlan:
@@ -109,7 +105,7 @@ class LoraBatchOps:
         return cls(infer_adapter.a_start, infer_adapter.a_len, infer_adapter.a_loc, infer_adapter.a_scaling,
                    mm.key_buffer, mm.value_buffer, max_lora_dim, use_pdl)
 
-    def prepare(self, token_adapter_ids, use_plan=True, big_groups=None, mixed_ranks=None, fused=None):
+    def prepare(self, token_adapter_ids, use_plan=True, big_groups=None, mixed_ranks=None):
         """Start a forward: ``token_adapter_ids`` is ``req_bins`` (decode) or ``batch_req_bins`` (prefill).
 
         Allocates the three delta buffers the reference allocates in ``forward`` (``:68-69,75-76``) and builds the
@@ -124,9 +120,6 @@ class LoraBatchOps:
         the kernels count their work items exactly (``SLORA_FLAG_EXACT_ITEMS``; a matter of speed only).  ``None``
         asks the plan in the same read-back; batches below 128 tokens are not asked and keep the plain enumeration.
 
-        ``fused``: run the shrink and the expand of a call as one launch (``SLORA_FLAG_FUSED``; same bits, the delta
-        buffers are then not written).  ``None`` picks it for delta widths up to ``FUSED_MAX_RANK`` when neither of
-        the two flags above is set: small adapters, where a launch's fixed cost rivals its streaming time.
         """
         self.ids = token_adapter_ids.contiguous()
         T = self.ids.numel()
@@ -151,13 +144,6 @@ class LoraBatchOps:
                 self.flags |= _lib.FLAG_ONLY_BIG
         if self.plan is not None and mixed_ranks:
             self.flags |= _lib.FLAG_EXACT_ITEMS
-        if fused is None and os.environ.get("SLORA_FUSED") in ("0", "1"):      # A/B timing from outside
-            fused = os.environ["SLORA_FUSED"] == "1"
-        if fused is None:
-            # one launch per call pays when every adapter is small: its fixed part is then as long as its streaming
-            fused = self.max_lora_dim <= FUSED_MAX_RANK and not big_groups and not mixed_ranks
-        if fused and not big_groups:
-            self.flags |= _lib.FLAG_FUSED
         return self
 
     def _common(self, layer_id):

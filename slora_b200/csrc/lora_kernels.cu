@@ -16,7 +16,6 @@
 
 #include "lora_common.cuh"
 #include "lora_pipelined.cuh"
-#include "lora_fused.cuh"
 #include "lora_mma.cuh"
 #include "lora_plan.cuh"
 #include "lora_simple.cuh"
@@ -510,7 +509,7 @@ int make_tmap(CUtensorMap* map, int dtype, const void* base, int64_t inner, int6
 // (Kernels with sizeable static shared memory pass static_bytes: the 48 KB default limit covers both kinds.)
 template <typename K>
 int ensure_dyn_smem(K kernel, int which, size_t smem, size_t static_bytes = 0) {
-  static int high_water[8][64];
+  static int high_water[12][64];  // one row per kernel template (`which`)
   if (smem + static_bytes <= 48 * 1024) return SLORA_OK;
   int dev = 0;
   cudaGetDevice(&dev);
@@ -804,74 +803,6 @@ int run_expand(const TileSrc& src, const Tables& tb, const void* w, const void* 
   return launch(lora_expand_kernel<__nv_bfloat16>, grid, kThreads, 0, flags, stream, a, "expand");
 }
 
-// Shrink and expand of one call as one launch (lora_fused.cuh).  Returns kNotFused, having launched nothing, when the
-// call is not one the fused kernel takes (the caller then issues the two launches); an error code for bad arguments.
-constexpr int kNotFused = 1;
-int run_fused(const TileSrc& src, const Tables& tb, const void* pool_a, const void* pool_b, const void* scales,
-              const void* x, int64_t x_stride, int h_in, int nproj, const int* qkvo, void* const* y,
-              const int64_t* y_stride, const int* h_out, int delta_width, int dtype, unsigned flags, int32_t* status,
-              cudaStream_t stream) {
-  if (kernel_choice() == CHOOSE_SIMPLE) return kNotFused;
-  if (src.mode == MODE_SEGMENT || src.seg_split > 0) return kNotFused;  // big groups go to the tensor cores
-  int rc = check_common(dtype, tb, pool_a);
-  if (!rc) rc = check_common(dtype, tb, pool_b);
-  if (rc) return rc;
-  if (!x || !scales) return fail(SLORA_ERR_NULL, "x or scales is null");
-  if (nproj < 1 || nproj > 3) return fail(SLORA_ERR_SHAPE, "nproj=%d outside 1..3", nproj);
-  if (h_in <= 0 || h_in % 8 != 0 || h_in >= 65536 * 8)
-    return fail(SLORA_ERR_SHAPE, "No suitable kernel. h_in=%d must be a positive multiple of 8", h_in);
-  if (delta_width <= 0 || delta_width > 128) return kNotFused;
-  if (!aligned16(x) || x_stride % 8 != 0) return fail(SLORA_ERR_ALIGN, "x rows are not 16-byte aligned");
-  const int64_t S = tb.pool_stride;
-  if (S % h_in != 0) return kNotFused;
-  const int pipe_piece = pow2_divisor(S, kPipeChunk);
-  if (pipe_piece * kMaxPieces < kPipeChunk || (kPipeChunk - 1) / S + 2 > kSpanRows) return kNotFused;
-  if (src.T <= 0) return SLORA_OK;
-  FusedArgs a;
-  memset(&a, 0, sizeof(a));
-  a.s.src = a.e.src = src;
-  a.s.tb = a.e.tb = tb;
-  a.s.w = pool_a;
-  a.s.x = x;
-  a.s.x_stride = x_stride;
-  a.s.h_in = h_in;
-  a.s.nproj = a.e.nproj = nproj;
-  a.s.delta_width = delta_width;
-  a.s.rank_mult = a.e.rank_mult = 1;
-  a.s.rows_per_cta = kMaxRows;
-  a.s.max_rb = (delta_width + kMaxRows - 1) / kMaxRows;
-  a.s.status = a.e.status = status;
-  a.e.w = pool_b;
-  a.e.scales = scales;
-  a.e.delta_parts = 1;
-  a.e.max_rank = delta_width;
-  a.e.piece = pipe_piece;
-  a.e.chunk_begin[0] = 0;
-  for (int p = 0; p < nproj; ++p) {
-    if (!y[p]) return fail(SLORA_ERR_NULL, "y[%d] is null", p);
-    if (qkvo[p] < 0 || qkvo[p] > 3) return fail(SLORA_ERR_QKVO, "qkvo=%d outside 0..3", qkvo[p]);
-    if (h_out[p] <= 0 || h_out[p] % 8 != 0 || h_out[p] >= 65536 * 8)
-      return fail(SLORA_ERR_SHAPE, "No suitable kernel. h_out=%d must be a positive multiple of 8", h_out[p]);
-    if (!aligned16(y[p]) || y_stride[p] % 8 != 0) return kNotFused;
-    a.s.qkvo[p] = a.e.qkvo[p] = qkvo[p];
-    a.e.y[p] = y[p];
-    a.e.y_stride[p] = y_stride[p];
-    a.e.h_out[p] = h_out[p];
-    const int64_t chunks = (static_cast<int64_t>(h_out[p]) * delta_width + kPipeChunk - 1) / kPipeChunk;
-    a.e.chunk_begin[p + 1] = a.e.chunk_begin[p] + static_cast<int>(chunks);
-    if (chunks > a.e_max) a.e_max = static_cast<int>(chunks);
-  }
-  a.ipu = a.s.max_rb + a.e_max;
-  const int64_t units = static_cast<int64_t>(src.slots) * nproj;
-  const int64_t grid = units < sm_count() * kPipeCtasPerSm ? units : sm_count() * kPipeCtasPerSm;
-  const size_t smem = kFusedRingBytes;
-  auto go = [&](auto k, int which) {
-    const int rc2 = ensure_dyn_smem(k, which, smem);
-    return rc2 ? rc2 : launch(k, grid, kPipeThreads, smem, flags, stream, a, "fused(pipelined)");
-  };
-  return dtype == SLORA_F16 ? go(lora_fused_pipe_kernel<__half>, 6) : go(lora_fused_pipe_kernel<__nv_bfloat16>, 7);
-}
-
 int make_src(const void* plan, const int64_t* ids, int64_t T, int64_t n_adapters, unsigned flags, TileSrc* src,
              int32_t** status) {
   memset(src, 0, sizeof(*src));
@@ -935,7 +866,8 @@ Tables make_tables(const int64_t* start, const int64_t* ranks4, const int64_t* l
 // ------------------------------------------------------------------------------------------------------------
 extern "C" {
 
-int slora_version(void) { return 102; }
+int slora_version(void) { return 103; }
+
 
 void slora_launch_counts(int64_t out[4]) {
   for (int i = 0; i < 4; ++i) out[i] = g_launches[i].load(std::memory_order_relaxed);
@@ -1308,19 +1240,6 @@ int slora_batch_lora_qkv(const void* plan, const int64_t* ids, void* q, void* k,
                          unsigned flags, void* stream) {
   const int qkvo[3] = {0, 1, 2};
   void* d[3] = {delta_q, delta_k, delta_v};
-  if (flags & SLORA_FLAG_FUSED) {
-    TileSrc src;
-    int32_t* status;
-    int rc0 = make_src(plan, ids, T, n_adapters, flags, &src, &status);
-    if (rc0) return rc0;
-    void* yf[3] = {q, k, v};
-    const int64_t ysf[3] = {q_stride, k_stride, v_stride};
-    const int hof[3] = {h_out_q, h_out_kv, h_out_kv};
-    rc0 = run_fused(src, make_tables(start, ranks4, loc, n_adapters, loc_len, pool_rows, pool_stride), pool_a, pool_b,
-                    scales, x, x_stride, h_in, 3, qkvo, yf, ysf, hof, delta_width, dtype, flags, status,
-                    static_cast<cudaStream_t>(stream));
-    if (rc0 != kNotFused) return rc0;
-  }
   int rc = slora_lora_shrink_multi(plan, ids, 3, qkvo, d, delta_stride, delta_width, x, x_stride, h_in, pool_a,
                                    pool_rows, pool_stride, start, ranks4, loc, n_adapters, loc_len, T, dtype, flags,
                                    stream);
@@ -1341,19 +1260,6 @@ int slora_batch_lora_o(const void* plan, const int64_t* ids, void* o, int64_t o_
                        int delta_width, int64_t T, int dtype, unsigned flags, void* stream) {
   const int qkvo[1] = {3};
   void* d[1] = {delta};
-  if (flags & SLORA_FLAG_FUSED) {
-    TileSrc src;
-    int32_t* status;
-    int rc0 = make_src(plan, ids, T, n_adapters, flags, &src, &status);
-    if (rc0) return rc0;
-    void* yf[1] = {o};
-    const int64_t ysf[1] = {o_stride};
-    const int hof[1] = {h_out};
-    rc0 = run_fused(src, make_tables(start, ranks4, loc, n_adapters, loc_len, pool_rows, pool_stride), pool_a, pool_b,
-                    scales, x, x_stride, h_in, 1, qkvo, yf, ysf, hof, delta_width, dtype, flags, status,
-                    static_cast<cudaStream_t>(stream));
-    if (rc0 != kNotFused) return rc0;
-  }
   int rc = slora_lora_shrink_multi(plan, ids, 1, qkvo, d, delta_stride, delta_width, x, x_stride, h_in, pool_a,
                                    pool_rows, pool_stride, start, ranks4, loc, n_adapters, loc_len, T, dtype, flags,
                                    stream);

@@ -972,8 +972,7 @@ __device__ __forceinline__ void expand_producer(const ExpandArgs& a, unsigned ch
 // [cw*2048, +2048) of the chunk as 8 loads of 256 elements; load m, lane l holds the 8 values of output
 // (cw*8 + m)*(32/LPO) + l/LPO for k in [(l % LPO)*8, +8).
 template <typename T, int LPO, bool FULL>
-__device__ __forceinline__ void expand_stage(const T* bs, const int* m, T* y, int64_t y_stride, int lane, int cw,
-                                             const T* ds_ext = nullptr, int ds_ext_stride = 0) {
+__device__ __forceinline__ void expand_stage(const T* bs, const int* m, T* y, int64_t y_stride, int lane, int cw) {
   constexpr int OPL = 32 / LPO;
   constexpr int NV = LPO >= 8 ? 1 : 8 / LPO;
   constexpr int R = LPO * 8;
@@ -983,9 +982,7 @@ __device__ __forceinline__ void expand_stage(const T* bs, const int* m, T* y, in
   const int nout = clen / R;
   const float scale = __int_as_float(m[6]);
   const T* ys = bs + clen;
-  // the tokens' delta rows: behind the y segments in the stage, or (fused kernel) wherever the shrink phase left them
-  const T* ds = ds_ext ? ds_ext : ys + n * nout;
-  const int dstr = ds_ext ? ds_ext_stride : R;
+  const T* ds = ys + n * nout;
   uint4 bv[8];
 #pragma unroll
   for (int mm = 0; mm < 8; ++mm) {
@@ -1001,7 +998,7 @@ __device__ __forceinline__ void expand_stage(const T* bs, const int* m, T* y, in
   for (int i = 0; i < NV; ++i) o_loc[i] = (cw * 8 + m_base + i) * OPL + g;  // output index inside the chunk
 
   for (int tt = 0; tt < n; ++tt) {
-    const uint4 dv = *reinterpret_cast<const uint4*>(ds + tt * dstr + kp);
+    const uint4 dv = *reinterpret_cast<const uint4*>(ds + tt * R + kp);
     float yv[NV];
 #pragma unroll
     for (int i = 0; i < NV; ++i) {

@@ -390,56 +390,3 @@ def test_against_outputs_of_the_reference_kernels(case):
         assert (deltas[p].float().cpu() - ref_d).abs().max() <= 2e-3 * ref_d.abs().max()
         assert_parity(outs[p][:, mod.cols_of(wl.spec.hidden)], g[f"{case}_y_p{p}"].astype(np.float32), what=f"ref kernels {case} p{p}")
 
-
-@pytest.mark.parametrize("case", ["s1", "rank16_gqa", "tokens", "bf16", "bad_row"])
-def test_one_launch_per_call_gives_the_same_bits_as_two(case):
-    """SLORA_FLAG_FUSED (shrink and expand of a call in one launch, the intermediate kept in shared memory) against
-    the two-launch path: bit-identical outputs, for the S1-shaped decode batch, rank 16 with k/v narrower than q,
-    per-token groups (no plan), bf16, and a bad table entry (the affected adapter's tokens get +0 either way)."""
-    dt, kw, bad = torch.float16, {}, False
-    if case == "s1":
-        wl = build_workload(2, pool_rows=65536)
-    elif case == "rank16_gqa":
-        wl = build_workload(5, pool_rows=8192, n_adapters=50, decode_tokens=300, hidden=4096, h_kv=512,
-                            rank_choices=(16,))
-    elif case == "tokens":
-        wl = build_workload(2, pool_rows=8192, n_adapters=20, decode_tokens=70, hidden=1024)
-        kw = dict(use_plan=False)
-    elif case == "bf16":
-        dt = torch.bfloat16
-        wl = build_workload(2, dtype=dt, pool_rows=8192, n_adapters=40, decode_tokens=200, hidden=5120)
-    else:
-        wl = build_workload(2, pool_rows=4096, n_adapters=4, decode_tokens=40, hidden=1024)
-        bad = True
-    w = wl.to(DEV)
-    if bad:
-        a = int(wl.ids[0])
-        w.a_loc = w.a_loc.clone()
-        w.a_loc[int(wl.a_start[a]) + 8 + 5] = 1 << 40       # a k row of that adapter
-    before = sl.launch_counts()["pipelined"]
-
-    def run(fused):
-        ops = sl.LoraBatchOps(w.a_start, w.a_len, w.a_loc, w.a_scaling, w.pools_a, w.pools_b, w.max_rank)
-        ops.prepare(w.ids, fused=fused, **kw)
-        assert bool(ops.flags & 8) == fused
-        H, K = w.spec.hidden, w.spec.h_kv
-        outs = [torch.zeros((w.T, n), dtype=w.dtype, device=DEV) for n in (H, K, K, H)]
-        ops.lora_get_qkv(0, w.x_qkv[0], outs[0], outs[1], outs[2])
-        ops.lora_get_o(0, w.x_o[0], outs[3])
-        torch.cuda.synchronize()
-        if ops.plan is not None:
-            assert (ops.plan.status()[0] != 0) == bad
-        return outs
-    two = run(False)
-    assert sl.launch_counts()["pipelined"] - before == 4
-    one = run(True)
-    assert sl.launch_counts()["pipelined"] - before == 6
-    ref = oracle_layer(wl)
-    for p in range(4):
-        assert torch.equal(one[p], two[p]), f"{case} proj {p}"
-        if not bad:
-            assert_parity(one[p], ref[p], dt, what=f"fused {case} proj {p}")
-    if bad:
-        hit = torch.tensor([int(i) == a for i in wl.ids])
-        assert float(one[1][hit.to(DEV)].abs().max()) == 0.0 and float(one[1][~hit.to(DEV)].abs().max()) > 0
-        assert_parity(one[0], ref[0], what="q is untouched by a bad k row")
