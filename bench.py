@@ -84,7 +84,7 @@ def parse_args(argv=None):
                          "expand kernels (fused), by one kernel over peer memory (p2p), or with NCCL all-gather")
     ap.add_argument("--tp-o", default="both", choices=["both", "replicated", "sharded"],
                     help="tensor-parallel runs: input of the o projection replicated, head-sharded (the rule of the "
-                         "reference's figure for a row-parallel projection), or both measured (headline: sharded)")
+                         "reference's figure for a row-parallel projection), or both measured (headline: replicated)")
     ap.add_argument("--prefill", action="store_true",
                     help="secondary line: long same-adapter sequences, served by the tensor-core kernels")
     ap.add_argument("--prefill-seqs", type=int, default=8)

@@ -7,7 +7,7 @@ over NVLink from inside the kernels (peer-memory stores and flags; ``--tp-exchan
 exchange or NCCL all-gather + regroup).  The o projection runs by either rule: input replicated (the q/k/v rule), or
 input head-sharded ``[T, H/N]`` with the partial intermediates summed over the ranks, which is what a tensor-parallel
 base model hands over (the rule of the reference's figure for a row-parallel projection, ``figures/slora_tp.png``);
-the headline is the head-sharded rule, the other figure sits beside it.
+the headline is the replicated-input rule (every intermediate all-gathered), the other figure sits beside it.
 
 Time is CUDA-event time of K graph replays, maximum over ranks; tokens/s counts the batch once (strong scaling).
 The line also carries: per-rank roofline of the largest kernel, the cost of the exchange (step time minus the same
@@ -85,15 +85,26 @@ def tp_parity(ops, wl, world, rank, dist, q, k, v, o, o_rule):
     for p in range(3):
         ref = orc.lora_shrink_ref(wl.x_qkv[0], wl.pools_a[0], t.a_start, t.a_len, t.a_loc, ops.ids, p, out_width=Rl)
         note(local[p], ref)
-    # (2) the real call: shrink + exchange + expand
-    ops.lora_qkv(0, wl.x_qkv[0], q, k, v)
+    # (2) the real call: shrink + exchange + expand.  With the exchange fused into the kernels the two halves of the
+    # call are issued apart, so that the delta buffer can be looked at in between (with in-band signalling the expand
+    # empties it again): every rank's shrink has completed and been synchronised with before anybody reads.
+    fused = ops.px is not None and getattr(be, "fused", False)
+    if fused:
+        be.shrink_push(ops.px, ops.plan, ops.ids, [0, 1, 2], wl.x_qkv[0], wl.pools_a[0], t, Rl, 0)
+        torch.cuda.synchronize()
+        dist.barrier()
+        full = ops.px.full[0][:, :T].clone()          # [3, T, R] as this rank's expand is about to read it
+        be.expand_wait(ops.px, ops.plan, ops.ids, [0, 1, 2], [q, k, v], wl.pools_b[0], t, Rl, 0)
+    else:
+        ops.lora_qkv(0, wl.x_qkv[0], q, k, v)
     torch.cuda.synchronize()
     dist.barrier()
     exchange_exact = None
     if ops.px is not None:
         everyone = torch.zeros((N, 3, T, Rl), dtype=wl.dtype, device=q.device)
         dist.all_gather_into_tensor(everyone.view(-1), local.view(-1))
-        full = ops.px.full[0][:, :T].clone()          # [3, T, R] as this rank's expand read it
+        if not fused:
+            full = ops.px.full[0][:, :T].clone()      # [3, T, R] as this rank's expand read it
         ev, full_np = everyone.cpu().numpy(), full.cpu().numpy()
         rows_per_rank = (np.asarray(wl.ranks)[ops.ids.cpu().numpy()] // N).tolist()
         exchange_exact = True
@@ -230,7 +241,9 @@ def run(args, dist, rank, world, device, peak):
         del graph, lgraph
         torch.cuda.synchronize()
         dist.barrier()
-    head_rule = "sharded_o" if True in rules else "replicated_o"
+    # headline: the rule the task's statement of the scheme gives (rank-r intermediates all-gathered for all four
+    # projections, i.e. replicated inputs); the head-sharded o rule of the reference's figure is reported beside it
+    head_rule = "replicated_o" if False in rules else "sharded_o"
     head = results[head_rule]
 
     # per-rank roofline of the largest kernel (the q/k/v expand of this rank's output slice), timed alone

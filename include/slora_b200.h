@@ -322,19 +322,27 @@ int slora_tp_allsum(const void* local, void* const* peer_parts, int32_t* const* 
  *     as done in seq_state.
  * Buffers, flags, seq_state, half: as for slora_tp_exchange; counter: one zero-initialised int32 per entry point.
  * The two calls of one exchange must both be made (a rank that pushes must also wait).  T == 0 returns at once.
+ *
+ * inband != 0 (both calls of an exchange alike): no flag, no fence.  The delta buffers must start out filled with the
+ * 16-bit pattern 0xffff (a NaN that no float-to-16-bit conversion produces); the shrink stores its results with
+ * plain stores and signals nothing; the expand starts as soon as this rank's own shrink has finished, and a consumer
+ * lane that finds the pattern among the eight delta values it is about to use re-reads them from this rank's buffer
+ * until the other rank's store has landed (bounded, ~2 s, then SLORA_STATUS_TIMEOUT and zeros).  The expand's last
+ * CTA refills the half it consumed with the pattern.  Only the pipelined kernels do this: a layout they do not take
+ * is an error in this mode.
  */
 int slora_tp_shrink_push(const void* plan, const int64_t* ids, int nproj, const int* qkvo, int part_width,
                          const void* x, int64_t x_stride, int h_in, const void* pool_a, int64_t pool_rows,
                          int64_t pool_stride, const int64_t* start, const int64_t* ranks4, const int64_t* loc,
                          int64_t n_adapters, int64_t loc_len, int64_t T, void* const* peer_full,
                          int32_t* const* peer_flags, int32_t* counter, int32_t* seq_state, int my_part, int n_parts,
-                         int half, int64_t full_tokens, int dtype, unsigned flags, void* stream);
+                         int half, int64_t full_tokens, int inband, int dtype, unsigned flags, void* stream);
 int slora_tp_expand_wait(const void* plan, const int64_t* ids, int nproj, const int* qkvo, void* const* y,
                          const int64_t* y_stride, const int* h_out, const void* pool_b, int64_t pool_rows,
                          int64_t pool_stride, const int64_t* start, const int64_t* ranks4, const int64_t* loc,
                          const void* scales, int64_t n_adapters, int64_t loc_len, int64_t T, void* my_full,
                          int32_t* my_flags, int32_t* counter, int32_t* seq_state, int my_part, int n_parts, int half,
-                         int64_t full_tokens, int part_width, int dtype, unsigned flags, void* stream);
+                         int64_t full_tokens, int part_width, int inband, int dtype, unsigned flags, void* stream);
 
 /*
  * Adapter load into the Unified-Paging pool: replaces the per-layer indexed copies of InferAdapter.load_lora_A /

@@ -72,10 +72,10 @@ _SIGS = {
                                   c_int, _P, c_int, c_int, c_uint, _P]),
     "slora_tp_shrink_push": (c_int, [_P, _P, c_int, _P, c_int, _P, c_int64, c_int, _P, c_int64, c_int64, _P, _P, _P,
                                      c_int64, c_int64, c_int64, _P, _P, _P, _P, c_int, c_int, c_int, c_int64, c_int,
-                                     c_uint, _P]),
+                                     c_int, c_uint, _P]),
     "slora_tp_expand_wait": (c_int, [_P, _P, c_int, _P, _P, _P, _P, _P, c_int64, c_int64, _P, _P, _P, _P, c_int64,
                                      c_int64, c_int64, _P, _P, _P, _P, c_int, c_int, c_int, c_int64, c_int, c_int,
-                                     c_uint, _P]),
+                                     c_int, c_uint, _P]),
     "slora_pool_scatter_rows": (c_int, [_P, _P, _P, c_int, _P, c_int64, c_int64, c_int64, c_int64, _P, _P]),
     "slora_lora_shrink_rows": (c_int, [_P, _P, c_int, _P, _P, c_int64, c_int, c_int, _P, c_int64, c_int, _P, c_int64,
                                        c_int64, _P, _P, _P, c_int64, c_int64, c_int64, c_int, c_uint, _P]),

@@ -84,6 +84,7 @@ struct TpLink {
   int64_t full_tokens;
   int my_part, n_parts, half;
   int enabled;
+  int inband;  // 1: no flags; the expand recognises delta values that have not arrived yet (see tp_has_empty)
 };
 
 struct ShrinkArgs {

@@ -1142,7 +1142,7 @@ int slora_tp_shrink_push(const void* plan, const int64_t* ids, int nproj, const 
                          int64_t pool_stride, const int64_t* start, const int64_t* ranks4, const int64_t* loc,
                          int64_t n_adapters, int64_t loc_len, int64_t T, void* const* peer_full,
                          int32_t* const* peer_flags, int32_t* counter, int32_t* seq_state, int my_part, int n_parts,
-                         int half, int64_t full_tokens, int dtype, unsigned flags, void* stream) {
+                         int half, int64_t full_tokens, int inband, int dtype, unsigned flags, void* stream) {
   if (!qkvo || !peer_full || !peer_flags || !counter || !seq_state) return fail(SLORA_ERR_NULL, "null argument");
   if (n_parts < 1 || n_parts > kTpMaxParts || my_part < 0 || my_part >= n_parts || half < 0 || half > 1 ||
       full_tokens < T || part_width < 1)
@@ -1160,6 +1160,7 @@ int slora_tp_shrink_push(const void* plan, const int64_t* ids, int nproj, const 
   tp.my_part = my_part;
   tp.n_parts = n_parts;
   tp.half = half;
+  tp.inband = inband ? 1 : 0;
   TileSrc src;
   int32_t* status;
   int rc = make_src(plan, ids, T, n_adapters, 0, &src, &status);
@@ -1176,7 +1177,7 @@ int slora_tp_expand_wait(const void* plan, const int64_t* ids, int nproj, const 
                          int64_t pool_stride, const int64_t* start, const int64_t* ranks4, const int64_t* loc,
                          const void* scales, int64_t n_adapters, int64_t loc_len, int64_t T, void* my_full,
                          int32_t* my_flags, int32_t* counter, int32_t* seq_state, int my_part, int n_parts, int half,
-                         int64_t full_tokens, int part_width, int dtype, unsigned flags, void* stream) {
+                         int64_t full_tokens, int part_width, int inband, int dtype, unsigned flags, void* stream) {
   if (!qkvo || !y || !y_stride || !h_out || !my_full || !my_flags || !counter || !seq_state)
     return fail(SLORA_ERR_NULL, "null argument");
   if (n_parts < 1 || n_parts > kTpMaxParts || my_part < 0 || my_part >= n_parts || half < 0 || half > 1 ||
@@ -1191,6 +1192,7 @@ int slora_tp_expand_wait(const void* plan, const int64_t* ids, int nproj, const 
   tp.my_part = my_part;
   tp.n_parts = n_parts;
   tp.half = half;
+  tp.inband = inband ? 1 : 0;
   const int R = n_parts * part_width;
   const void* d[3];
   for (int p = 0; p < 3; ++p)
@@ -1203,7 +1205,7 @@ int slora_tp_expand_wait(const void* plan, const int64_t* ids, int nproj, const 
   const Tables tb = make_tables(start, ranks4, loc, n_adapters, loc_len, pool_rows, pool_stride);
   rc = run_expand(src, tb, pool_b, scales, nproj, qkvo, y, y_stride, h_out, d, R, R, 1, 0, n_parts, dtype, flags,
                   status, static_cast<cudaStream_t>(stream), &tp);
-  if ((rc == SLORA_ERR_ALIGN || rc == SLORA_ERR_SHAPE) && strstr(g_err, "No suitable kernel")) {
+  if ((rc == SLORA_ERR_ALIGN || rc == SLORA_ERR_SHAPE) && strstr(g_err, "No suitable kernel") && !inband) {
     // a layout the pipelined expand does not take: nothing has been launched yet; wait for the flags with a
     // one-CTA launch of the exchange kernel (mode 2), then expand with whatever kernel family fits
     TpExchangeArgs w;

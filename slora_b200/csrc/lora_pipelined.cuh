@@ -100,6 +100,7 @@ struct PipeCtl {
   } prod[kProducerWarps];
   // planned batches of mixed ranks: items up to and including each tile (see build_item_map)
   uint16_t item_end[kCompactTiles];
+  int tp_gave_up;  // in-band signalling: a wait for another rank's values ran out; nobody in this CTA waits again
 };
 
 // Shrink only: per-item partial sums of the consumer warps and the arrival counter that elects the last warp.  (Kept
@@ -144,18 +145,31 @@ __device__ __forceinline__ bool tp_link_wait(const TpLink& tp, int lane) {
   return __all_sync(0xffffffffu, seen);
 }
 
-// End of a linked launch: the last CTA to get here either raises this rank's flag on every rank (shrink: all its
-// columns have been written and fenced) or counts the exchange as done (expand: every CTA has read its number).
+// End of a linked launch (whole-launch flags): the last CTA to get here either raises this rank's flag on every rank
+// (shrink: all its columns have been written and fenced) or counts the exchange as done (expand: every CTA has read
+// its number).  One system-scope fence per CTA, by the thread that then bumps the arrival counter: the CTA barrier
+// before it orders every thread's stores before that fence, and a fence is cumulative.  (A fence by each of the CTA's
+// 288 threads, as this was first written, serialises in the memory system: measured, it cost more than the exchange
+// itself.)  The expand's bookkeeping stays on this GPU and needs no system-scope fence at all.
 __device__ __forceinline__ void tp_link_finish(const TpLink& tp, bool is_shrink) {
   __shared__ int s_last;
-  __threadfence_system();
   __syncthreads();
-  if (threadIdx.x == 0) s_last = atomicAdd(tp.counter, 1) == static_cast<int>(gridDim.x) - 1;
+  if (threadIdx.x == 0) {
+    if (is_shrink) {
+      __threadfence_system();
+    } else {
+      __threadfence();
+    }
+    s_last = atomicAdd(tp.counter, 1) == static_cast<int>(gridDim.x) - 1;
+  }
   __syncthreads();
   if (!s_last) return;
   const int seq = tp.seq_state[tp.half] + 1;
-  if (threadIdx.x == 0) *tp.counter = 0;
-  __threadfence_system();
+  if (threadIdx.x == 0) {
+    *tp.counter = 0;
+    __threadfence();  // the other CTAs' arrivals (device-scope atomics) before what follows
+  }
+  __syncthreads();
   if (is_shrink) {
     if (static_cast<int>(threadIdx.x) < tp.n_parts) {
       asm volatile("st.release.sys.global.b32 [%0], %1;" ::"l"(tp.flags[threadIdx.x] + tp.half * tp.n_parts + tp.my_part),
@@ -167,9 +181,54 @@ __device__ __forceinline__ void tp_link_finish(const TpLink& tp, bool is_shrink)
   }
 }
 
+// ---- in-band signalling (TpLink::inband) ------------------------------------------------------------------------
+// No flag and no fence at all: the delta buffers start out filled with a bit pattern no result can have (kTpEmpty: a
+// NaN that the float-to-16-bit conversion never produces), the shrink stores its results into every rank's buffer
+// with plain stores, and the expand checks the delta values themselves: a consumer lane that finds the pattern among
+// the eight values it is about to use re-reads them from global memory until they have arrived (bounded).  Each
+// 16-bit element is written by one store, so checking every element that is used is enough - no ordering between
+// elements is needed.  The last CTA of the expand refills the half it consumed; no rank can write that half again
+// before this rank has finished its next exchange on the other half, which starts after this kernel.
+constexpr uint32_t kTpEmpty2 = 0xffffffffu;  // two elements of the pattern 0xffff
+__device__ __forceinline__ bool tp_has_empty(const uint4& v) {
+  auto e = [](uint32_t w) { return (w & 0xffffu) == 0xffffu || (w >> 16) == 0xffffu; };
+  return e(v.x) || e(v.y) || e(v.z) || e(v.w);
+}
+// Eight delta values from global memory, polled until none is the empty pattern; false when the wait ran out.
+__device__ __forceinline__ bool tp_poll_delta(const void* src, uint4& v, volatile int* gave_up) {
+  const long long t0 = clock64();
+  for (;;) {
+    asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+                 : "l"(src)
+                 : "memory");
+    if (!tp_has_empty(v)) return true;
+    if (*gave_up != 0) return false;
+    if (clock64() - t0 > kTpLinkWaitCycles) {
+      *gave_up = 1;
+      return false;
+    }
+  }
+}
+// End of an expand with in-band signalling: the last CTA refills the consumed half with the empty pattern.
+__device__ __forceinline__ void tp_inband_finish(const TpLink& tp, void* half_base, int64_t bytes) {
+  __shared__ int s_last;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence();
+    s_last = atomicAdd(tp.counter, 1) == static_cast<int>(gridDim.x) - 1;
+  }
+  __syncthreads();
+  if (!s_last) return;
+  uint4* p = reinterpret_cast<uint4*>(half_base);
+  const uint4 e = make_uint4(kTpEmpty2, kTpEmpty2, kTpEmpty2, kTpEmpty2);
+  for (int64_t i = threadIdx.x; i < bytes / 16; i += blockDim.x) p[i] = e;
+  if (threadIdx.x == 0) *tp.counter = 0;
+}
+
 __device__ __forceinline__ void ring_flush(Ring& r, PipeCtl& c, int lane) {
   pdl_wait();
-  if (r.tp != nullptr && !tp_link_wait(*r.tp, lane)) {
+  if (r.tp != nullptr && !r.tp->inband && !tp_link_wait(*r.tp, lane)) {
     // the copies still go out (the consumers' barriers expect them); the result is flagged as not to be trusted
     if (lane == 0) set_status(r.status, SLORA_STATUS_TIMEOUT);
   }
@@ -263,6 +322,7 @@ __device__ __forceinline__ void ring_finish(Ring& r, PipeCtl& c, int32_t* status
 
 __device__ __forceinline__ void pipe_init(PipeCtl& c, int tid) {
   if (tid == 0) {
+    c.tp_gave_up = 0;
 #pragma unroll
     for (int s = 0; s < kSlots; ++s) {
       mbar_init(&c.full[s], 1);
@@ -784,7 +844,7 @@ __global__ void __launch_bounds__(kPipeThreads) lora_shrink_pipe_kernel(const Sh
   } else {
     shrink_consumer<T, EXACT>(a, ring_mem, ctl, red, lane, warp - kProducerWarps);
   }
-  if (a.tp.enabled) tp_link_finish(a.tp, true);
+  if (a.tp.enabled && !a.tp.inband) tp_link_finish(a.tp, true);
 }
 
 // ------------------------------------------------------------------------------------------------------------
@@ -972,7 +1032,9 @@ __device__ __forceinline__ void expand_producer(const ExpandArgs& a, unsigned ch
 // [cw*2048, +2048) of the chunk as 8 loads of 256 elements; load m, lane l holds the 8 values of output
 // (cw*8 + m)*(32/LPO) + l/LPO for k in [(l % LPO)*8, +8).
 template <typename T, int LPO, bool FULL>
-__device__ __forceinline__ void expand_stage(const T* bs, const int* m, T* y, int64_t y_stride, int lane, int cw) {
+__device__ __forceinline__ void expand_stage(const T* bs, const int* m, T* y, int64_t y_stride, int lane, int cw,
+                                             const T* dglobal = nullptr, int64_t dglobal_stride = 0,
+                                             int32_t* status = nullptr, volatile int* gave_up = nullptr) {
   constexpr int OPL = 32 / LPO;
   constexpr int NV = LPO >= 8 ? 1 : 8 / LPO;
   constexpr int R = LPO * 8;
@@ -998,7 +1060,14 @@ __device__ __forceinline__ void expand_stage(const T* bs, const int* m, T* y, in
   for (int i = 0; i < NV; ++i) o_loc[i] = (cw * 8 + m_base + i) * OPL + g;  // output index inside the chunk
 
   for (int tt = 0; tt < n; ++tt) {
-    const uint4 dv = *reinterpret_cast<const uint4*>(ds + tt * R + kp);
+    uint4 dv = *reinterpret_cast<const uint4*>(ds + tt * R + kp);
+    if (dglobal != nullptr && tp_has_empty(dv)) {
+      // tensor parallelism, in-band signalling: another rank's columns had not landed when the stage was copied
+      if (!tp_poll_delta(dglobal + static_cast<int64_t>(m[8 + tt]) * dglobal_stride + kp, dv, gave_up)) {
+        set_status(status, SLORA_STATUS_TIMEOUT);
+        dv = make_uint4(0u, 0u, 0u, 0u);
+      }
+    }
     float yv[NV];
 #pragma unroll
     for (int i = 0; i < NV; ++i) {
@@ -1035,21 +1104,23 @@ __device__ __forceinline__ void expand_consumer(const ExpandArgs& a, const unsig
     const int p = m[3];
     T* y = reinterpret_cast<T*>(pick3(a.y, p));
     const int64_t ystr = pick3(a.y_stride, p);
+    const T* dg = (a.tp.enabled && a.tp.inband) ? reinterpret_cast<const T*>(pick3(a.delta, p)) : nullptr;
+    const int64_t dgs = a.delta_stride;
     if (m[4] == kPipeChunk) {  // complete chunk: no bounds checks
       switch (m[2]) {
-        case 8: expand_stage<T, 1, true>(bs, m, y, ystr, lane, cw); break;
-        case 16: expand_stage<T, 2, true>(bs, m, y, ystr, lane, cw); break;
-        case 32: expand_stage<T, 4, true>(bs, m, y, ystr, lane, cw); break;
-        case 64: expand_stage<T, 8, true>(bs, m, y, ystr, lane, cw); break;
-        default: expand_stage<T, 16, true>(bs, m, y, ystr, lane, cw); break;
+        case 8: expand_stage<T, 1, true>(bs, m, y, ystr, lane, cw, dg, dgs, a.status, &c.tp_gave_up); break;
+        case 16: expand_stage<T, 2, true>(bs, m, y, ystr, lane, cw, dg, dgs, a.status, &c.tp_gave_up); break;
+        case 32: expand_stage<T, 4, true>(bs, m, y, ystr, lane, cw, dg, dgs, a.status, &c.tp_gave_up); break;
+        case 64: expand_stage<T, 8, true>(bs, m, y, ystr, lane, cw, dg, dgs, a.status, &c.tp_gave_up); break;
+        default: expand_stage<T, 16, true>(bs, m, y, ystr, lane, cw, dg, dgs, a.status, &c.tp_gave_up); break;
       }
     } else {
       switch (m[2]) {
-        case 8: expand_stage<T, 1, false>(bs, m, y, ystr, lane, cw); break;
-        case 16: expand_stage<T, 2, false>(bs, m, y, ystr, lane, cw); break;
-        case 32: expand_stage<T, 4, false>(bs, m, y, ystr, lane, cw); break;
-        case 64: expand_stage<T, 8, false>(bs, m, y, ystr, lane, cw); break;
-        default: expand_stage<T, 16, false>(bs, m, y, ystr, lane, cw); break;
+        case 8: expand_stage<T, 1, false>(bs, m, y, ystr, lane, cw, dg, dgs, a.status, &c.tp_gave_up); break;
+        case 16: expand_stage<T, 2, false>(bs, m, y, ystr, lane, cw, dg, dgs, a.status, &c.tp_gave_up); break;
+        case 32: expand_stage<T, 4, false>(bs, m, y, ystr, lane, cw, dg, dgs, a.status, &c.tp_gave_up); break;
+        case 64: expand_stage<T, 8, false>(bs, m, y, ystr, lane, cw, dg, dgs, a.status, &c.tp_gave_up); break;
+        default: expand_stage<T, 16, false>(bs, m, y, ystr, lane, cw, dg, dgs, a.status, &c.tp_gave_up); break;
       }
     }
     __syncwarp();
@@ -1074,7 +1145,15 @@ __global__ void __launch_bounds__(kPipeThreads) lora_expand_pipe_kernel(const Ex
   } else {
     expand_consumer<T>(a, ring_mem, ctl, lane, warp - kProducerWarps);
   }
-  if (a.tp.enabled) tp_link_finish(a.tp, false);
+  if (a.tp.enabled) {
+    if (a.tp.inband) {
+      // the half of the delta buffer this exchange used: [3][full_tokens][delta_stride] elements from delta[0] on
+      tp_inband_finish(a.tp, const_cast<void*>(a.delta[0]),
+                       3 * a.tp.full_tokens * a.delta_stride * static_cast<int64_t>(sizeof(T)));
+    } else {
+      tp_link_finish(a.tp, false);
+    }
+  }
 }
 
 }  // namespace slora

@@ -81,7 +81,7 @@ class PeerExchange:
     ``all_gather_into_tensor`` + regroup stand otherwise.
     """
 
-    def __init__(self, T, R, world, rank, dtype, device, group=None):
+    def __init__(self, T, R, world, rank, dtype, device, group=None, inband=True):
         import ctypes
         import torch.distributed as dist
         import torch.distributed._symmetric_memory as symm_mem
@@ -90,7 +90,12 @@ class PeerExchange:
         self.full = symm_mem.empty((2, 3, max(T, 1), R), dtype=dtype, device=device)
         self.flags = symm_mem.empty((2, world), dtype=torch.int32, device=device)
         self.parts = symm_mem.empty((world, max(T, 1), R), dtype=dtype, device=device)  # partial sums of the o shrink
-        self.full.zero_()
+        # in-band signalling of the fused exchange: an element that has not arrived yet is the bit pattern 0xffff
+        self.inband = inband
+        if inband:
+            self.full.view(torch.int16).fill_(-1)
+        else:
+            self.full.zero_()
         self.flags.zero_()
         self.parts.zero_()
         h_full = symm_mem.rendezvous(self.full, group.group_name)
@@ -137,7 +142,9 @@ class TpLoraOps:
         self.full = torch.zeros((3, T, self.R), dtype=dt, device=dev) if hasattr(self.backend, "regroup") else None
         self.plan = self.backend.make_plan(self.ids, self.t)
         if self.peer_exchange and (self.px is None or self.px.full.shape[2] < T):
-            self.px = PeerExchange(T, self.R, self.N, self.rank, dt, dev, self.group)
+            fused = getattr(self.backend, "fused", False)
+            self.px = PeerExchange(T, self.R, self.N, self.rank, dt, dev, self.group,
+                                   inband=fused and getattr(self.backend, "inband", True))
         return self
 
     def _exchange(self, nproj):
@@ -233,11 +240,12 @@ class TpLoraOps:
 class CudaBackend:
     """The local operations of :class:`TpLoraOps` on the CUDA kernels."""
 
-    def __init__(self, use_pdl=False, fused=True):
+    def __init__(self, use_pdl=False, fused=True, inband=True):
         from . import _lib
         self.base_flags = _lib.FLAG_PDL if use_pdl else 0
         self.flags = self.base_flags
         self.fused = fused   # with a PeerExchange: push from the shrink / wait in the expand, no exchange launch
+        self.inband = inband  # fused exchange without flags: the expand recognises values that have not arrived
 
     def make_plan(self, ids, t):
         from . import _lib
@@ -301,7 +309,7 @@ class CudaBackend:
             x.stride(0), x.size(1), pool_a.data_ptr(), pool_a.size(0), pool_a.stride(0), t.a_start.data_ptr(),
             t.a_len.data_ptr(), t.a_loc.data_ptr(), t.a_start.numel(), t.a_loc.numel(), ids.numel(), px.full_ptrs,
             px.flag_ptrs, px.counter.data_ptr(), px.seq_state.data_ptr(), px.rank, px.world, half, px.full.shape[2],
-            _lib.dtype_code(x.dtype), self.flags, _lib.current_stream_ptr()))
+            1 if px.inband else 0, _lib.dtype_code(x.dtype), self.flags, _lib.current_stream_ptr()))
 
     def expand_wait(self, px, plan, ids, qkvo, ys, pool_b, t, part_width, half):
         """Expand that waits for every rank's flag, then reads this rank's buffer (``slora_tp_expand_wait``)."""
@@ -315,7 +323,7 @@ class CudaBackend:
             t.a_start.data_ptr(), t.a_len.data_ptr(), t.a_loc.data_ptr(), t.a_scaling.data_ptr(), t.a_start.numel(),
             t.a_loc.numel(), ids.numel(), px.full.data_ptr(), px.flags.data_ptr(), px.counter.data_ptr() + 4,
             px.seq_state.data_ptr(), px.rank, px.world, half, px.full.shape[2], part_width,
-            _lib.dtype_code(ys[0].dtype), self.flags, _lib.current_stream_ptr()))
+            1 if px.inband else 0, _lib.dtype_code(ys[0].dtype), self.flags, _lib.current_stream_ptr()))
 
     def expand(self, plan, ids, qkvo, ys, deltas, pool_b, t, **kw):
         from .batch_infer import expand_multi

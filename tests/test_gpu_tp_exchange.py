@@ -168,6 +168,104 @@ def test_input_sharded_o_projection_emulated_on_one_gpu():
     assert_parity(got, want.numpy(), what="input-sharded o projection")
 
 
+class _EmulatedPeers:
+    """What CudaBackend reads of a PeerExchange, for N ranks that all live on one GPU (plain device tensors)."""
+
+    def __init__(self, N, cap, R, inband):
+        self.fulls = [torch.zeros((2, 3, cap, R), dtype=torch.float16, device=DEV) for _ in range(N)]
+        if inband:
+            for f in self.fulls:
+                f.view(torch.int16).fill_(-1)
+        self.flagss = [torch.zeros((2, N), dtype=torch.int32, device=DEV) for _ in range(N)]
+        self.N, self.inband = N, inband
+
+    def rank(self, r):
+        px = type("Px", (), {})()
+        N = self.N
+        px.full, px.flags = self.fulls[r], self.flagss[r]
+        px.full_ptrs = (ctypes.c_void_p * N)(*[f.data_ptr() for f in self.fulls])
+        px.flag_ptrs = (ctypes.c_void_p * N)(*[f.data_ptr() for f in self.flagss])
+        px.counter = torch.zeros(4, dtype=torch.int32, device=DEV)
+        px.seq_state = torch.zeros(2, dtype=torch.int32, device=DEV)
+        px.rank, px.world, px.inband = r, N, self.inband
+        return px
+
+
+@pytest.mark.parametrize("inband", [True, False])
+@pytest.mark.parametrize("T", [40, 200])
+def test_fused_exchange_emulated_on_one_gpu(T, inband):
+    """slora_tp_shrink_push / slora_tp_expand_wait, four ranks emulated on one GPU: every rank's shrink stores its rows
+    into every rank's buffer; every rank's expand then finds them there (in-band signalling: none of the values it
+    uses is the empty pattern any more, and its last CTA refills the half; else: every rank's flag is up).  Three
+    exchanges (q,k,v; o; q,k,v again) against the formula."""
+    H, N = 4096, 4
+    ranks = [8, 16, 32, 8]
+    g = torch.Generator().manual_seed(23)
+    ads = [([torch.randn((r, H), generator=g) / 64 for _ in range(4)],
+            [torch.randn((H, r), generator=g) * 0.02 for _ in range(4)]) for r in ranks]
+    x = torch.randn((T, H), generator=g).to(torch.float16)
+    ids = torch.randint(0, len(ranks), (T,), generator=g)
+    R, Rl = max(ranks), max(ranks) // N
+    shards = []
+    for rank in range(N):
+        a_start, a_len, a_loc = make_tables([r // N for r in ranks], 512, 300 + rank, True)
+        pa = torch.zeros((512, H), dtype=torch.float16)
+        pb = torch.zeros((512, H), dtype=torch.float16)
+        for i, (A, B) in enumerate(ads):
+            ra, rb = tp.shard_adapter(A, B, rank, N, H)
+            loc = a_loc[a_start[i]: a_start[i] + a_len[i]]
+            pa[loc] = ra.to(torch.float16)
+            pb[loc] = rb.to(torch.float16)
+        t = tp.TpTables(a_start.to(DEV), a_len.to(DEV), a_loc.to(DEV),
+                        torch.tensor([16.0 / r for r in ranks], dtype=torch.float16, device=DEV))
+        shards.append((t, pa.to(DEV), pb.to(DEV)))
+    peers = _EmulatedPeers(N, T, R, inband)
+    pxs = [peers.rank(r) for r in range(N)]
+    be = tp.CudaBackend()
+    xd, idd = x.to(DEV), ids.to(DEV)
+    plans = [be.make_plan(idd, t) for t, _, _ in shards]
+    want = [torch.stack([(x[i].float() @ ads[int(ids[i])][0][p].half().float().T)
+                         @ ads[int(ids[i])][1][p].half().float().T * (16.0 / ranks[int(ids[i])]) for i in range(T)])
+            for p in range(4)]
+    for qkvo, half in (([0, 1, 2], 0), ([3], 1), ([0, 1, 2], 0)):
+        for rank, (t, pa, pb) in enumerate(shards):
+            be.shrink_push(pxs[rank], plans[rank], idd, qkvo, xd, pa, t, Rl, half)
+        ys = []
+        for rank, (t, pa, pb) in enumerate(shards):
+            y = [torch.zeros((T, H // N), dtype=torch.float16, device=DEV) for _ in qkvo]
+            be.expand_wait(pxs[rank], plans[rank], idd, qkvo, y, pb, t, Rl, half)
+            ys.append(y)
+        torch.cuda.synchronize()
+        for rank in range(N):
+            plans[rank].check()
+            if inband:      # the consumed half is empty again
+                assert bool((peers.fulls[rank][half].view(torch.int16) == -1).all())
+        for j, p in enumerate(qkvo):
+            got = torch.cat([ys[rank][j] for rank in range(N)], dim=1)
+            assert_parity(got, want[p].numpy(), what=f"fused exchange proj {p}")
+
+
+def test_in_band_wait_runs_out_without_hanging():
+    """An expand whose delta rows nobody writes (no rank has pushed): the consumers' bounded re-reads give up, the
+    status word says so, the launch ends and the context stays usable."""
+    H, N, T = 4096, 2, 12
+    ranks = [16, 16]
+    a_start, a_len, a_loc = make_tables([r // N for r in ranks], 128, 7, True)
+    t = tp.TpTables(a_start.to(DEV), a_len.to(DEV), a_loc.to(DEV),
+                    torch.tensor([1.0, 1.0], dtype=torch.float16, device=DEV))
+    pb = torch.zeros((128, H), dtype=torch.float16, device=DEV)
+    ids = torch.zeros(T, dtype=torch.int64, device=DEV)
+    peers = _EmulatedPeers(N, T, 16, True)
+    px = peers.rank(0)
+    be = tp.CudaBackend()
+    plan = be.make_plan(ids, t)
+    y = torch.zeros((T, H // N), dtype=torch.float16, device=DEV)
+    be.expand_wait(px, plan, ids, [0], [y], pb, t, 8, 0)
+    torch.cuda.synchronize()
+    assert plan.status()[0] & 8                # SLORA_STATUS_TIMEOUT
+    assert int((y + 1).sum().item()) == y.numel()
+
+
 def test_exchange_wait_runs_out_without_hanging():
     """A flag that nobody raises: the bounded wait gives up, the status word says so, the context stays usable."""
     N, T, Rl = 2, 8, 8
