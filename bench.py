@@ -89,6 +89,9 @@ def parse_args(argv=None):
                     help="secondary line: long same-adapter sequences, served by the tensor-core kernels")
     ap.add_argument("--prefill-seqs", type=int, default=8)
     ap.add_argument("--prefill-len", type=int, default=512)
+    ap.add_argument("--rope", action="store_true",
+                    help="secondary line: rotary embedding and KV-pool scatter in the q/k/v expand's epilogue against "
+                         "the same two steps as a pass of their own (configuration 2)")
     ap.add_argument("--scheduler", action="store_true",
                     help="secondary line: what the adapter-clustering request queue is worth on the LoRA path "
                          "(bench_sched.py)")
@@ -745,6 +748,68 @@ def prefill_bench(args, device, peak):
     print(json.dumps(line), flush=True)
 
 
+def rope_bench(args, device, peak):
+    """What folding the rotary embedding of q, k and the KV-pool scatter of k, v into the q/k/v expand saves
+    (S1-shaped decode batch): per layer, the plain q/k/v call; the call with both steps in the expand's epilogue; the
+    call followed by the two steps as one pass of their own (the reference runs four more launches here: rotary q,
+    rotary k, scatter k, scatter v)."""
+    import subprocess
+    import slora_b200 as sl
+    from slora_b200.workloads import build_workload
+    if os.environ.get("SLORA_ROPE_EPILOGUE") is None and not args.no_graph:
+        # the separate-pass figure needs the library's switch, read once per process: a child process measures it
+        env = dict(os.environ, SLORA_ROPE_EPILOGUE="0")
+        child = subprocess.run([sys.executable, os.path.abspath(__file__), "--rope"], env=env, capture_output=True,
+                               text=True)
+        separate = json.loads(child.stdout.strip().splitlines()[-1]) if child.returncode == 0 else None
+    else:
+        separate = None
+    peak_gbs, _ = peak
+    P = phys_layers_for(args, 2)
+    wl = build_workload(2, device=device, phys_layers=P, pool_rows=args.pool_rows)
+    L, T, H = args.layers or wl.spec.layers, wl.T, wl.spec.hidden
+    dt = wl.dtype
+    ops = sl.LoraBatchOps(wl.a_start, wl.a_len, wl.a_loc, wl.a_scaling, wl.pools_a, wl.pools_b, wl.max_rank,
+                          use_pdl=not args.no_pdl)
+    ops.prepare(wl.ids)
+    q = [torch.zeros((T, H), dtype=dt, device=device) for _ in range(P)]
+    k = [torch.zeros((T, H), dtype=dt, device=device) for _ in range(P)]
+    v = [torch.zeros((T, H), dtype=dt, device=device) for _ in range(P)]
+    kpool = [torch.zeros((4096, H), dtype=dt, device=device) for _ in range(P)]
+    vpool = [torch.zeros((4096, H), dtype=dt, device=device) for _ in range(P)]
+    rows = torch.randperm(4096, device=device)[:T].to(torch.int64)
+    ang = torch.rand((T, 64), device=device) * 6.28
+    cos, sin = torch.cos(ang).to(dt), torch.sin(ang).to(dt)
+
+    def plain():
+        for l in range(L):
+            p = l % P
+            ops.lora_get_qkv(p, wl.x_qkv[p], q[p], k[p], v[p])
+
+    def with_steps():
+        for l in range(L):
+            p = l % P
+            ops.lora_get_qkv(p, wl.x_qkv[p], q[p], k[p], v[p], rope=(cos, sin), kv_dest=(rows, kpool[p], vpool[p]))
+
+    t_plain = _graph_time(plain, L)
+    t_steps = _graph_time(with_steps, L)
+    es = 2
+    extra_bytes = T * (2 * H * es * 2 + 2 * H * es * 2)      # rotary q, k read + write; k, v rows read + written
+    line = {"metric": "rotary_and_kv_scatter_cost_per_layer", "unit": "us per layer (q/k/v call)",
+            "workload": wl.spec.name, "layers": L, "tokens": T,
+            "qkv_call_plain_us": t_plain,
+            "qkv_call_with_both_steps_us": t_steps,
+            "how_the_steps_ran": "a pass of their own after the expand" if os.environ.get("SLORA_ROPE_EPILOGUE") == "0"
+            else "in the expand's epilogue",
+            "bytes_of_a_separate_pass_per_layer": extra_bytes,
+            "separate_pass_at_measured_hbm_peak_us": extra_bytes / peak_gbs / 1e3}
+    if separate is not None:
+        line["qkv_call_with_separate_pass_us"] = separate["qkv_call_with_both_steps_us"]
+        line["value"] = separate["qkv_call_with_both_steps_us"] - t_steps
+        line["value_is"] = "us per layer saved by the epilogue against the separate pass"
+    return line
+
+
 def main():
     args = parse_args()
     if args.impl == "reference":
@@ -772,6 +837,10 @@ def main():
         return
     if args.prefill:
         prefill_bench(args, device, peak)
+        return
+    if args.rope:
+        if rank == 0:
+            print(json.dumps(rope_bench(args, device, peak)), flush=True)
         return
     if args.scheduler:
         import bench_sched

@@ -325,8 +325,11 @@ def e2e_tp(args, ops, wl, world, rank, dist, device, L, P, sharded_o, q, k, v, o
 
     The q/k/v activations are replicated over the ranks.  Pushing the same rows through every GPU's PCIe link would
     multiply the host traffic by N, so each rank uploads rows [rank*T/N, (rank+1)*T/N) and the ranks all-gather them
-    over NVLink (NCCL, on the upload stream); the o input is uploaded as this rank's column slice (head-sharded rule)
-    or the same way (replicated rule)."""
+    over NVLink (NCCL); the o input is uploaded as this rank's column slice (head-sharded rule) or the same way
+    (replicated rule).  The layers are cut into chunks: one upload, one graph replay (the chunk's all-gathers and LoRA
+    calls, captured through the public API) and one download per chunk, on three streams, so that the host issues a
+    few dozen operations per step instead of several hundred - at 8 ranks the step would otherwise be bound by the
+    Python loop, not by PCIe or the GPUs."""
     T, H, K = wl.T, wl.spec.hidden, wl.spec.h_kv
     dt = wl.dtype
     N = world
@@ -334,27 +337,51 @@ def e2e_tp(args, ops, wl, world, rank, dist, device, L, P, sharded_o, q, k, v, o
     Tp = rows * N
     g = torch.Generator().manual_seed(77 + rank)
     Ho = H // N if sharded_o else H
+    orow = T if sharded_o else rows
     x_host = torch.randn((L, rows, H), generator=g, dtype=torch.float32).to(dt).pin_memory()
-    xo_host = (torch.randn((L, T, Ho), generator=g, dtype=torch.float32).to(dt).pin_memory() if sharded_o else
-               torch.randn((L, rows, H), generator=g, dtype=torch.float32).to(dt).pin_memory())
+    xo_host = torch.randn((L, orow, Ho), generator=g, dtype=torch.float32).to(dt).pin_memory()
     x_part = torch.empty((L, rows, H), dtype=dt, device=device)
     x_full = torch.empty((L, Tp, H), dtype=dt, device=device)
-    xo_part = torch.empty_like(xo_host, device=device)
+    xo_part = torch.empty((L, orow, Ho), dtype=dt, device=device)
     xo_full = xo_part if sharded_o else torch.empty((L, Tp, H), dtype=dt, device=device)
     W = (2 * H + 2 * K) // N
     y_dev = torch.zeros((L, T, W), dtype=dt, device=device)
     y_host = torch.empty((L, T, W), dtype=dt).pin_memory()
     h2d = x_host.numel() * 2 + xo_host.numel() * 2
     d2h = y_host.numel() * 2
+    hq, hk = H // N, K // N
+    chunk = 8 if L % 8 == 0 else (5 if L % 5 == 0 else 1)
+    chunks = [(c, min(L, c + chunk)) for c in range(0, L, chunk)]
+
+    def run_layers(lo, hi):
+        for l in range(lo, hi):
+            p = l % P
+            yl = y_dev[l]
+            dist.all_gather_into_tensor(x_full[l].view(-1), x_part[l].view(-1))
+            if not sharded_o:
+                dist.all_gather_into_tensor(xo_full[l].view(-1), xo_part[l].view(-1))
+            ops.lora_qkv(p, x_full[l][:T], yl[:, :hq], yl[:, hq:hq + hk], yl[:, hq + hk:hq + 2 * hk])
+            if sharded_o:
+                ops.lora_o_sharded(p, xo_full[l], yl[:, hq + 2 * hk:])
+            else:
+                ops.lora_o(p, xo_full[l][:T], yl[:, hq + 2 * hk:])
+
+    graphs, how = None, "eager"
+    if ops.px is not None and not args.no_graph:
+        try:
+            graphs = [_capture(lambda lo=lo, hi=hi: run_layers(lo, hi), dist) for lo, hi in chunks]
+            how = "one CUDA graph per chunk of %d layers (NCCL all-gathers of the uploads and the LoRA calls)" % chunk
+        except Exception as e:    # a stack that cannot capture the collectives: issue the same calls eagerly
+            graphs, how = None, "eager (graph capture failed: %s)" % type(e).__name__
+            torch.cuda.synchronize()
+        dist.barrier()
     cur = torch.cuda.current_stream()
     s_in, s_out = torch.cuda.Stream(), torch.cuda.Stream()
-    ev_in = [torch.cuda.Event() for _ in range(L)]
-    ev_done = [torch.cuda.Event() for _ in range(L)]
+    ev_in = [torch.cuda.Event() for _ in chunks]
+    ev_done = [torch.cuda.Event() for _ in chunks]
     steps, warmup = max(3, min(args.steps, 10)), 3
     times = []
-    hq, hk = H // N, K // N
     for it in range(warmup + steps):
-        y_dev.zero_()
         torch.cuda.synchronize()
         dist.barrier()
         t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -362,26 +389,20 @@ def e2e_tp(args, ops, wl, world, rank, dist, device, L, P, sharded_o, q, k, v, o
         s_in.wait_stream(cur)
         s_out.wait_stream(cur)
         with torch.cuda.stream(s_in):
-            for l in range(L):
-                x_part[l].copy_(x_host[l], non_blocking=True)
-                dist.all_gather_into_tensor(x_full[l].view(-1), x_part[l].view(-1))
-                xo_part[l].copy_(xo_host[l], non_blocking=True)
-                if not sharded_o:
-                    dist.all_gather_into_tensor(xo_full[l].view(-1), xo_part[l].view(-1))
-                ev_in[l].record(s_in)
-        for l in range(L):
-            p = l % P
-            yl = y_dev[l]
-            cur.wait_event(ev_in[l])
-            ops.lora_qkv(p, x_full[l][:T], yl[:, :hq], yl[:, hq:hq + hk], yl[:, hq + hk:hq + 2 * hk])
-            if sharded_o:
-                ops.lora_o_sharded(p, xo_full[l], yl[:, hq + 2 * hk:])
+            for c, (lo, hi) in enumerate(chunks):
+                x_part[lo:hi].copy_(x_host[lo:hi], non_blocking=True)
+                xo_part[lo:hi].copy_(xo_host[lo:hi], non_blocking=True)
+                ev_in[c].record(s_in)
+        for c, (lo, hi) in enumerate(chunks):
+            cur.wait_event(ev_in[c])
+            if graphs is not None:
+                graphs[c].replay()
             else:
-                ops.lora_o(p, xo_full[l][:T], yl[:, hq + 2 * hk:])
-            ev_done[l].record(cur)
+                run_layers(lo, hi)
+            ev_done[c].record(cur)
             with torch.cuda.stream(s_out):
-                s_out.wait_event(ev_done[l])
-                y_host[l].copy_(yl, non_blocking=True)
+                s_out.wait_event(ev_done[c])
+                y_host[lo:hi].copy_(y_dev[lo:hi], non_blocking=True)
         cur.wait_stream(s_out)
         t1.record()
         torch.cuda.synchronize()
@@ -390,10 +411,11 @@ def e2e_tp(args, ops, wl, world, rank, dist, device, L, P, sharded_o, q, k, v, o
     el = torch.tensor([sum(times)], dtype=torch.float64, device=device)
     dist.all_reduce(el, op=dist.ReduceOp.MAX)
     e_time = float(el.item())
+    del graphs
     import bench
     return {"value": T * steps / e_time, "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
             "bytes_are": "per rank", "steps": steps, "ms_per_step": e_time / steps * 1e3,
             "h2d_gbs_per_gpu": h2d / (e_time / steps) / 1e9, "d2h_gbs_per_gpu": d2h / (e_time / steps) / 1e9,
-            "host": bench.host_topology(device.index or 0),
+            "host": bench.host_topology(device.index or 0), "issue": how,
             "how": "each rank uploads T/N rows of the replicated activations and the ranks all-gather them over "
                    "NVLink; outputs are this rank's column slices"}

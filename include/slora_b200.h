@@ -217,6 +217,35 @@ int slora_batch_lora_o(const void* plan, const int64_t* ids, void* o, int64_t o_
                        int delta_width, int64_t T, int dtype, unsigned flags, void* stream);
 
 /*
+ * slora_batch_lora_qkv with the two steps that follow it in the reference's layer folded in: the rotary embedding of
+ * q and k (rotary_emb_fwd, slora/models/peft/lora_unordered_batch_infer.py:277,298; kernel
+ * slora/models/llama/triton_kernel/rotary_emb.py:8-71: out0 = x0 cos - x1 sin, out1 = x0 sin + x1 cos over the two
+ * halves of every head) and the scatter of the new k and v rows into the KV pool (destindex_copy_kv,
+ * slora/common/basemodel/layer_infer/template/transformer_layer_infer_template.py:50-62; kernel
+ * slora/common/basemodel/triton_kernel/destindex_copy_kv.py:8-50).
+ *   cos / sin: [T][head_dim / 2] in the I/O type, rows cs_stride elements apart (infer_state.position_cos / _sin).
+ *   q is updated in place: q = rotary(q + lora_q(x)).
+ *   k_out == NULL: k = rotary(k + lora_k(x)) and v = v + lora_v(x) in place.
+ *   k_out != NULL: the results go to rows kv_rows[t] (device int64 [T]; infer_state.prefill_mem_index /
+ *     decode_mem_index) of k_out and v_out, [kv_out_rows][kv_out_stride] with h_out_kv used columns (the pool's
+ *     key_buffer[layer] / value_buffer[layer]); k and v themselves are only read (they hold the base projection).
+ *     A token whose kv_rows entry is outside [0, kv_out_rows) is skipped with SLORA_STATUS_BAD_TABLE.
+ * With head_dim == 128 and the pipelined expand both steps happen in the expand's epilogue (one pass over q, k, v
+ * instead of three); otherwise (tensor-core routing of big groups, other layouts, other head sizes) the expand is
+ * followed by one small launch that does them.  Values are rounded to the I/O type before the rotation, where the
+ * reference stores them; the rotation itself is computed in FP32.
+ */
+int slora_batch_lora_qkv_rope(const void* plan, const int64_t* ids, void* q, void* k, void* v, int64_t q_stride,
+                              int64_t k_stride, int64_t v_stride, int h_out_q, int h_out_kv, const void* x,
+                              int64_t x_stride, int h_in, const void* pool_a, const void* pool_b, int64_t pool_rows,
+                              int64_t pool_stride, const int64_t* start, const int64_t* ranks4, const int64_t* loc,
+                              const void* scales, int64_t n_adapters, int64_t loc_len, void* delta_q, void* delta_k,
+                              void* delta_v, int64_t delta_stride, int delta_width, int64_t T, int dtype,
+                              unsigned flags, void* stream, const void* cos, const void* sin, int64_t cs_stride,
+                              int head_dim, const int64_t* kv_rows, void* k_out, void* v_out, int64_t kv_out_stride,
+                              int64_t kv_out_rows);
+
+/*
  * No counterpart in the reference.  The o-projection LoRA delta (same result as slora_batch_lora_o) for callers that
  * must not allocate device memory: code running inside someone else's memory budget or allocator -- a serving process
  * whose pool already owns the whole GPU, a plugin called from a real-time path that may not block on the driver's

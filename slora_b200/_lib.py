@@ -61,6 +61,10 @@ _SIGS = {
     "slora_batch_lora_qkv": (c_int, [_P, _P, _P, _P, _P, c_int64, c_int64, c_int64, c_int, c_int, _P, c_int64, c_int,
                                      _P, _P, c_int64, c_int64, _P, _P, _P, _P, c_int64, c_int64, _P, _P, _P, c_int64,
                                      c_int, c_int64, c_int, c_uint, _P]),
+    "slora_batch_lora_qkv_rope": (c_int, [_P, _P, _P, _P, _P, c_int64, c_int64, c_int64, c_int, c_int, _P, c_int64,
+                                          c_int, _P, _P, c_int64, c_int64, _P, _P, _P, _P, c_int64, c_int64, _P, _P, _P,
+                                          c_int64, c_int, c_int64, c_int, c_uint, _P, _P, _P, c_int64, c_int, _P, _P,
+                                          _P, c_int64, c_int64]),
     "slora_batch_lora_o": (c_int, [_P, _P, _P, c_int64, c_int, _P, c_int64, c_int, _P, _P, c_int64, c_int64, _P, _P,
                                    _P, _P, c_int64, c_int64, _P, c_int64, c_int, c_int64, c_int, c_uint, _P]),
     "slora_batch_lora_o_noalloc": (c_int, [_P, _P, c_int64, c_int, _P, c_int64, c_int, _P, _P, c_int64, c_int64, _P, _P,

@@ -152,13 +152,52 @@ class LoraBatchOps:
             raise RuntimeError("A and B pools must share one row stride")
         return kb, vb, kb.size(0), kb.stride(0)
 
-    def lora_get_qkv(self, layer_id, x, q, k, v):
-        """``q += lora_q(x)``, ``k += lora_k(x)``, ``v += lora_v(x)`` (2-D views ``[T, h]``), in place."""
+    def lora_get_qkv(self, layer_id, x, q, k, v, rope=None, kv_dest=None, head_dim=128):
+        """``q += lora_q(x)``, ``k += lora_k(x)``, ``v += lora_v(x)`` (2-D views ``[T, h]``), in place.
+
+        ``rope=(cos, sin)`` (``[T, head_dim / 2]`` each, ``infer_state.position_cos / position_sin``) also applies the
+        rotary embedding to q and k, as ``rotary_emb_fwd`` does right after each expand in the reference
+        (``lora_unordered_batch_infer.py:277,298``); ``kv_dest=(rows, k_out, v_out)`` then writes the new k and v rows
+        to rows ``rows[t]`` of the KV-pool buffers ``k_out`` / ``v_out`` instead of updating ``k`` / ``v`` in place
+        (``destindex_copy_kv``, ``transformer_layer_infer_template.py:50-62``).  Both happen in the expand's epilogue
+        where the kernels allow (C entry ``slora_batch_lora_qkv_rope``).
+        """
         kb, vb, rows, stride = self._common(layer_id)
         _lib.require_cuda(x, q, k, v)
         if k.size(1) != v.size(1):
             raise RuntimeError("k and v must have the same width")
         d = self.delta
+        if rope is not None:
+            cos, sin = rope
+            _lib.require_cuda(cos, sin)
+            if cos.shape != sin.shape or cos.dim() != 2 or cos.size(0) != x.size(0) or cos.size(1) * 2 != head_dim \
+                    or cos.dtype != x.dtype or sin.dtype != x.dtype or cos.stride(1) != 1 or sin.stride(1) != 1 \
+                    or cos.stride(0) != sin.stride(0):
+                raise RuntimeError("cos and sin must be [T, head_dim / 2] tensors of the activations' dtype")
+            kv_rows = k_out = v_out = None
+            out_stride = out_rows = 0
+            if kv_dest is not None:
+                kv_rows, k_out, v_out = kv_dest
+                _lib.require_cuda(kv_rows, k_out, v_out)
+                if kv_rows.dtype != torch.int64 or kv_rows.dim() != 1 or kv_rows.numel() != x.size(0) \
+                        or not kv_rows.is_contiguous():
+                    raise RuntimeError("kv_dest rows must be a contiguous int64 tensor with one entry per token")
+                ko, vo = k_out.view(k_out.size(0), -1), v_out.view(v_out.size(0), -1)
+                if ko.shape != vo.shape or ko.stride() != vo.stride() or ko.stride(1) != 1 or ko.size(1) < k.size(1) \
+                        or ko.dtype != x.dtype or vo.dtype != x.dtype:
+                    raise RuntimeError("k_out and v_out must be row-major buffers of one shape, at least as wide as k")
+                out_stride, out_rows = ko.stride(0), ko.size(0)
+            _lib.check(_lib.lib.slora_batch_lora_qkv_rope(
+                0 if self.plan is None else self.plan.ptr, self.ids.data_ptr(), q.data_ptr(), k.data_ptr(),
+                v.data_ptr(), q.stride(0), k.stride(0), v.stride(0), q.size(1), k.size(1), x.data_ptr(), x.stride(0),
+                x.size(1), kb.data_ptr(), vb.data_ptr(), rows, stride, self.a_start.data_ptr(), self.a_len.data_ptr(),
+                self.a_loc.data_ptr(), self.a_scaling.data_ptr(), self.a_start.numel(), self.a_loc.numel(),
+                d[0].data_ptr(), d[1].data_ptr(), d[2].data_ptr(), d[0].stride(0), self.max_lora_dim, x.size(0),
+                _lib.dtype_code(x.dtype), self.flags, _lib.current_stream_ptr(), cos.data_ptr(), sin.data_ptr(),
+                cos.stride(0), int(head_dim), _lib.ptr(kv_rows), _lib.ptr(k_out), _lib.ptr(v_out), out_stride, out_rows))
+            return q
+        if kv_dest is not None:
+            raise RuntimeError("kv_dest needs rope=(cos, sin)")
         _lib.check(_lib.lib.slora_batch_lora_qkv(
             0 if self.plan is None else self.plan.ptr, self.ids.data_ptr(), q.data_ptr(), k.data_ptr(), v.data_ptr(),
             q.stride(0), k.stride(0), v.stride(0), q.size(1), k.size(1), x.data_ptr(), x.stride(0), x.size(1),

@@ -16,6 +16,7 @@
 
 #include "lora_common.cuh"
 #include "lora_pipelined.cuh"
+#include "lora_rope.cuh"
 #include "lora_mma.cuh"
 #include "lora_plan.cuh"
 #include "lora_simple.cuh"
@@ -679,7 +680,8 @@ int run_shrink(const TileSrc& src, const Tables& tb, const void* w, const void* 
 int run_expand(const TileSrc& src, const Tables& tb, const void* w, const void* scales, int nproj, const int* qkvo,
                void* const* y, const int64_t* y_stride, const int* h_out, const void* const* delta,
                int64_t delta_stride, int delta_width, int delta_parts, int64_t delta_part_stride, int rank_mult,
-               int dtype, unsigned flags, int32_t* status, cudaStream_t stream, const TpLink* tp = nullptr) {
+               int dtype, unsigned flags, int32_t* status, cudaStream_t stream, const TpLink* tp = nullptr,
+               const RopeArgs* epi = nullptr) {
   int rc = check_common(dtype, tb, w);
   if (rc) return rc;
   if (!scales) return fail(SLORA_ERR_NULL, "scales is null");
@@ -729,8 +731,8 @@ int run_expand(const TileSrc& src, const Tables& tb, const void* w, const void* 
     a.tp = *tp;
     a.tp.enabled = 1;
   }
-  bool can_mma = !tp && (src.mode == MODE_SEGMENT || src.mode == MODE_PLAN) && src.seg_split > 0 && mma_enabled() &&
-                 delta_parts == 1 && rank_mult == 1 && delta_stride % 8 == 0;
+  bool can_mma = !tp && !epi && (src.mode == MODE_SEGMENT || src.mode == MODE_PLAN) && src.seg_split > 0 &&
+                 mma_enabled() && delta_parts == 1 && rank_mult == 1 && delta_stride % 8 == 0;
   for (int p = 0; p < nproj; ++p)
     can_mma = can_mma && aligned16(y[p]) && y_stride[p] % 8 == 0 && aligned16(delta[p]);
   for (int p = 0; p < nproj; ++p) can_mma = can_mma && h_out[p] >= 64;
@@ -789,6 +791,15 @@ int run_expand(const TileSrc& src, const Tables& tb, const void* w, const void* 
     const int64_t grid = items < sm_count() * kPipeCtasPerSm ? items : sm_count() * kPipeCtasPerSm;
     const bool exact = (flags & SLORA_FLAG_EXACT_ITEMS) != 0 && src.mode == MODE_PLAN;
     const size_t smem = exact ? kExpandRingBytes : kRingBytes;
+    if (epi) {
+      // the expand with rotary embedding / KV-pool scatter in its epilogue (lora_rope.cuh)
+      auto go2 = [&](auto k, int which) {
+        const int rc2 = ensure_dyn_smem(k, which, smem);
+        return rc2 ? rc2 : launch2(k, grid, kPipeThreads, smem, flags, stream, a, *epi, "expand(pipelined, rotary)");
+      };
+      if (dtype == SLORA_F16) return exact ? go2(lora_expand_rope_pipe_kernel<__half, true>, 2) : go2(lora_expand_rope_pipe_kernel<__half, false>, 0);
+      return exact ? go2(lora_expand_rope_pipe_kernel<__nv_bfloat16, true>, 3) : go2(lora_expand_rope_pipe_kernel<__nv_bfloat16, false>, 1);
+    }
     auto go = [&](auto k, int which) {
       const int rc2 = ensure_dyn_smem(k, which, smem);
       return rc2 ? rc2 : launch(k, grid, kPipeThreads, smem, flags, stream, a, "expand(pipelined)");
@@ -796,6 +807,7 @@ int run_expand(const TileSrc& src, const Tables& tb, const void* w, const void* 
     if (dtype == SLORA_F16) return exact ? go(lora_expand_pipe_kernel<__half, true>, 4) : go(lora_expand_pipe_kernel<__half, false>, 2);
     return exact ? go(lora_expand_pipe_kernel<__nv_bfloat16, true>, 5) : go(lora_expand_pipe_kernel<__nv_bfloat16, false>, 3);
   }
+  if (epi) return fail(SLORA_ERR_SHAPE, "No suitable kernel. the expand with a rotary epilogue is pipelined only");
   a.piece = piece;
   set_chunks(kChunk);
   const int64_t grid = static_cast<int64_t>(src.slots) * a.chunk_begin[nproj];
@@ -1273,6 +1285,93 @@ int slora_batch_lora_o(const void* plan, const int64_t* ids, void* o, int64_t o_
   return slora_lora_expand_multi(plan, ids, 1, qkvo, y, ys, ho, dc, delta_stride, delta_width, 1, 0, 1, pool_b,
                                  pool_rows, pool_stride, start, ranks4, loc, scales, n_adapters, loc_len, T, dtype,
                                  flags, stream);
+}
+
+int slora_batch_lora_qkv_rope(const void* plan, const int64_t* ids, void* q, void* k, void* v, int64_t q_stride,
+                              int64_t k_stride, int64_t v_stride, int h_out_q, int h_out_kv, const void* x,
+                              int64_t x_stride, int h_in, const void* pool_a, const void* pool_b, int64_t pool_rows,
+                              int64_t pool_stride, const int64_t* start, const int64_t* ranks4, const int64_t* loc,
+                              const void* scales, int64_t n_adapters, int64_t loc_len, void* delta_q, void* delta_k,
+                              void* delta_v, int64_t delta_stride, int delta_width, int64_t T, int dtype,
+                              unsigned flags, void* stream, const void* cos, const void* sin, int64_t cs_stride,
+                              int head_dim, const int64_t* kv_rows, void* k_out, void* v_out, int64_t kv_out_stride,
+                              int64_t kv_out_rows) {
+  if (!cos || !sin) return fail(SLORA_ERR_NULL, "cos or sin is null");
+  if (head_dim <= 0 || head_dim % 2 != 0 || h_out_q % head_dim != 0 || h_out_kv % head_dim != 0)
+    return fail(SLORA_ERR_SHAPE, "head_dim=%d must be even and divide the q and k/v widths", head_dim);
+  if ((k_out != nullptr) != (v_out != nullptr) || (k_out != nullptr && !kv_rows))
+    return fail(SLORA_ERR_NULL, "k_out, v_out and kv_rows go together");
+  if (k_out && (!aligned16(k_out) || !aligned16(v_out) || kv_out_stride % 8 != 0 || kv_out_rows <= 0))
+    return fail(SLORA_ERR_ALIGN, "the KV destination buffers need 16-byte aligned rows");
+  const int qkvo[3] = {0, 1, 2};
+  void* d[3] = {delta_q, delta_k, delta_v};
+  int rc = slora_lora_shrink_multi(plan, ids, 3, qkvo, d, delta_stride, delta_width, x, x_stride, h_in, pool_a,
+                                   pool_rows, pool_stride, start, ranks4, loc, n_adapters, loc_len, T, dtype, flags,
+                                   stream);
+  if (rc) return rc;
+  if (T == 0) return SLORA_OK;
+  void* y[3] = {q, k, v};
+  const int64_t ys[3] = {q_stride, k_stride, v_stride};
+  const int ho[3] = {h_out_q, h_out_kv, h_out_kv};
+  const void* dc[3] = {delta_q, delta_k, delta_v};
+  RopeArgs e;
+  memset(&e, 0, sizeof(e));
+  e.cos = cos;
+  e.sin = sin;
+  e.cs_stride = cs_stride;
+  e.rope_mask = 3;  // q and k
+  e.out_rows = kv_rows;
+  e.out[1] = k_out;
+  e.out[2] = v_out;
+  e.out_stride[1] = e.out_stride[2] = kv_out_stride;
+  e.out_rows_limit = kv_out_rows;
+  TileSrc src;
+  int32_t* status;
+  rc = make_src(plan, ids, T, n_adapters, flags, &src, &status);
+  if (rc) return rc;
+  const Tables tb = make_tables(start, ranks4, loc, n_adapters, loc_len, pool_rows, pool_stride);
+  // SLORA_ROPE_EPILOGUE=0 keeps the two steps a pass of their own (A/B timing)
+  static const bool epilogue_on = [] {
+    const char* v = getenv("SLORA_ROPE_EPILOGUE");
+    return !(v && strcmp(v, "0") == 0);
+  }();
+  const bool in_epilogue = epilogue_on && head_dim == kRopeHeadDim && h_out_q % kRopeHeadDim == 0 &&
+                           h_out_kv % kRopeHeadDim == 0 && src.seg_split == 0 && kernel_choice() != CHOOSE_SIMPLE;
+  if (in_epilogue) {
+    rc = run_expand(src, tb, pool_b, scales, 3, qkvo, y, ys, ho, dc, delta_stride, delta_width, 1, 0, 1, dtype, flags,
+                    status, static_cast<cudaStream_t>(stream), nullptr, &e);
+    if (!(rc != SLORA_OK && strstr(g_err, "No suitable kernel"))) return rc;
+  }
+  // another kernel family serves this call's expand: the two steps follow as a pass of their own
+  rc = run_expand(src, tb, pool_b, scales, 3, qkvo, y, ys, ho, dc, delta_stride, delta_width, 1, 0, 1, dtype, flags,
+                  status, static_cast<cudaStream_t>(stream));
+  if (rc) return rc;
+  cudaLaunchConfig_t cfg;
+  memset(&cfg, 0, sizeof(cfg));
+  cfg.gridDim = dim3(static_cast<unsigned>(T), 3, 1);
+  cfg.blockDim = dim3(128, 1, 1);
+  cfg.stream = static_cast<cudaStream_t>(stream);
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = (flags & SLORA_FLAG_PDL) ? 1 : 0;
+  cudaError_t err;
+  if (dtype == SLORA_F16) {
+    err = cudaLaunchKernelEx(&cfg, rope_scatter_kernel<__half>, static_cast<__half*>(q), static_cast<__half*>(k),
+                             static_cast<__half*>(v), q_stride, k_stride, v_stride, h_out_q, h_out_kv, h_out_kv, 3,
+                             head_dim, e, status);
+  } else {
+    err = cudaLaunchKernelEx(&cfg, rope_scatter_kernel<__nv_bfloat16>, static_cast<__nv_bfloat16*>(q),
+                             static_cast<__nv_bfloat16*>(k), static_cast<__nv_bfloat16*>(v), q_stride, k_stride,
+                             v_stride, h_out_q, h_out_kv, h_out_kv, 3, head_dim, e, status);
+  }
+  if (err != cudaSuccess) {
+    cudaGetLastError();
+    return fail(SLORA_ERR_LAUNCH, "rope_scatter: %s", cudaGetErrorString(err));
+  }
+  g_launches[0].fetch_add(1, std::memory_order_relaxed);
+  return SLORA_OK;
 }
 
 // ---- entry point that allocates nothing ------------------------------------------------------------------------
