@@ -73,6 +73,10 @@ extern "C" {
                                   group that the tensor-core kernels serve (slora_plan_header: no small tiles, every big
                                   group's rank a power of two that divides pool_stride and fits the delta buffers), so
                                   the call's CUDA-core launch would find nothing and is left out. */
+/* With SLORA_FLAG_BIG_GROUPS: the plan's count of 128-token tiles of big groups (slora_plan_header word 6), when the
+   caller has read it, in bits 16..31 of flags.  The tensor-core launches then enumerate exactly those tiles (and
+   size their K split for them) instead of the most a batch of T tokens could have.  0 = not known. */
+#define SLORA_FLAG_BIG_TILES(n) (((unsigned)(n) & 0xffffu) << 16)
 
 /* Bits of the device status word (plan header / status argument). */
 #define SLORA_STATUS_BAD_ID 1      /* a token's adapter id was outside [0, n_adapters) - token skipped   */

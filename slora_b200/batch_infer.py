@@ -127,9 +127,10 @@ class LoraBatchOps:
         self.delta = [torch.zeros((T, self.max_lora_dim), dtype=dtype, device=self.ids.device) for _ in range(3)]
         self.plan = BatchPlan(self.ids, self.a_start, self.a_len, self.a_loc.numel()) if use_plan else None
         self.flags = self.base_flags
-        only_big = False
+        only_big, n_big_tiles = False, 0
         if self.plan is not None and T >= 128 and (big_groups is None or mixed_ranks is None):
             h = self.plan.header()
+            n_big_tiles = h["big_tiles"]
             if big_groups is None:
                 big_groups = h["big_tiles"] > 0
                 # a pure prefill batch: every group is big and of a rank the tensor-core kernels take
@@ -142,6 +143,8 @@ class LoraBatchOps:
             self.flags |= _lib.FLAG_BIG_GROUPS
             if only_big:
                 self.flags |= _lib.FLAG_ONLY_BIG
+            if n_big_tiles:
+                self.flags |= (min(n_big_tiles, 0xffff) << 16)     # SLORA_FLAG_BIG_TILES: the plan's own count
         if self.plan is not None and mixed_ranks:
             self.flags |= _lib.FLAG_EXACT_ITEMS
         return self

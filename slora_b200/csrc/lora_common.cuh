@@ -49,6 +49,7 @@ struct TileSrc {
   int seg_split;          // > 0 when segments (SEGMENT) / groups (PLAN) at least this long go to the tensor-core kernels
   int mma_tiles_per_seg;  // SEGMENT: 128-token tiles enumerated per segment by the tensor-core kernels
   int big_slots;          // PLAN: big-tile slots the tensor-core launch enumerates
+  int big_exact;          // PLAN: big_slots is the plan's own count (host side), not an upper bound
   int mma_max_rows;       // adapters with more slot rows than this (the call's delta width) stay on the CUDA cores
   int64_t T;
 };

@@ -590,10 +590,18 @@ int run_shrink(const TileSrc& src, const Tables& tb, const void* w, const void* 
     const int64_t mma_tiles = src.mode == MODE_PLAN ? src.big_slots : static_cast<int64_t>(src.n_seg) * src.mma_tiles_per_seg;
     // split K over a cluster of up to 8 CTAs while the launch would otherwise leave SMs idle (a tile alone streams
     // 128 x h_in activations through one SM); a plan enumerates about twice the tiles it can hold
-    const int64_t likely_units = (src.mode == MODE_PLAN ? src.T / kBigTileTokens + 1 : mma_tiles) * m.max_rb;
+    // (when the caller passed the plan's own count of big tiles, SLORA_FLAG_BIG_TILES, big_slots is exact)
+    const int64_t likely_units =
+        (src.mode == MODE_PLAN ? (src.big_exact ? mma_tiles : src.T / kBigTileTokens + 1) : mma_tiles) * m.max_rb;
     const int nkb_total = h_in / kMmaKBlock;
+    // clusters are placed inside one GPC (about 18 SMs): of size 8 two fit a GPC, of size 4 four - a launch that
+    // wants more clusters than fit at once runs in waves, each as long as the whole K loop of a CTA
+    auto fits_one_wave = [&](int k) {
+      const int clusters_at_once = k >= 8 ? sm_count() / 9 : (k == 4 ? sm_count() / 9 * 2 : sm_count() / k);
+      return likely_units <= clusters_at_once;
+    };
     int ks = 8;
-    while (ks > 1 && (nkb_total % ks != 0 || likely_units * ks > sm_count() + sm_count() / 8)) ks >>= 1;
+    while (ks > 1 && (nkb_total % ks != 0 || !fits_one_wave(ks))) ks >>= 1;
     m.mma_ksplit = ks;
     m.mma_stages = (kMmaSmemBudget - 1024) / m.mma_stage_bytes;
     if (m.mma_stages > kMmaMaxStages) m.mma_stages = kMmaMaxStages;
@@ -827,6 +835,12 @@ int make_src(const void* plan, const int64_t* ids, int64_t T, int64_t n_adapters
     src->plan = reinterpret_cast<const int32_t*>(plan);
     src->slots = max_tiles_for(T, n_adapters);
     src->big_slots = max_big_for(T);
+    // the caller read the plan's count of big tiles and passed it on: enumerate exactly those
+    const int hint = static_cast<int>(flags >> 16);
+    if (hint > 0 && hint <= src->big_slots) {
+      src->big_slots = hint;
+      src->big_exact = 1;
+    }
     src->seg_split = ((flags & SLORA_FLAG_BIG_GROUPS) && T >= kBigGroupTokens) ? kBigGroupTokens : 0;
     *status = const_cast<int32_t*>(src->plan) + PH_STATUS;
   } else {
