@@ -858,7 +858,7 @@ def main():
     decode = None
     if cfg == 4 and world == 1 and not args.no_decode_extra and not (args.adapters or args.pool_rows or args.layers):
         decode = measure_single(args, 2, device, rank, world, dist, peak, extras=False)
-    cpu = None
+    cpu, bad = None, []
     if rank == 0 and world == 1 and not args.no_cpu:
         cpu = run_cpu_baseline(cfg, args.cpu_seconds, args.pool_rows, args.adapters)
     if rank == 0:
@@ -881,10 +881,15 @@ def main():
                                                               "replay_median", "clocks")}
             line["decode_cfg2"]["unit"] = "tokens/s"
             line["gpu_launches"] += decode["gpu_launches"]
+        bad = [p for p in (line.get("parity"), (line.get("decode_cfg2") or {}).get("parity")) if p and not p["ok"]]
+        if bad:
+            line["invalid"] = "parity check against the CPU oracle failed; the figures of this line do not count"
         print(json.dumps(line), flush=True)
     if dist is not None:
         dist.barrier()
         dist.destroy_process_group()
+    if rank == 0 and bad:
+        raise SystemExit(4)
 
 
 if __name__ == "__main__":

@@ -314,10 +314,14 @@ def run(args, dist, rank, world, device, peak):
             "gpu_launches": args.steps * launches_per_step, "collectives_per_step": 2 * L, "e2e": e2e,
             "cpu_baseline": None, "clocks": clocks.summary() if clocks is not None else None,
         }
+        if not line["parity"]["ok"]:
+            line["invalid"] = "parity check against the CPU oracle failed; the figures of this line do not count"
         print(json.dumps(line), flush=True)
     torch.cuda.synchronize()
     dist.barrier()
     dist.destroy_process_group()
+    if rank == 0 and not line["parity"]["ok"]:
+        raise SystemExit(4)
 
 
 def e2e_tp(args, ops, wl, world, rank, dist, device, L, P, sharded_o, q, k, v, o):

@@ -15,8 +15,12 @@ What it restates, in numpy, step for step (paths inside the S-LoRA reference tre
   to back (the reference's variable-length copy kernel, ``infer_adapter.py:261-280``), and the dropped adapters' rows
   go back to the free map.
 
-Parity pin: integer work, bit-exact.  The reference holds no stored vectors for these steps (they need its CUDA
-tensors to run); the pin is the formula itself, checked in the tests against hand-worked cases.
+Parity pin: integer work, bit-exact.  The reference holds no stored vectors for these steps, so the pin is the
+reference itself: ``tests/golden/make_pool_golden.py`` runs the reference's own ``MemoryAllocator`` and
+``InferAdapter`` on CPU tensors (its ``device="cuda"`` tensor factories redirected, nothing else changed) through
+seeded scenarios of allocations, releases, adapter loads and offloads and records every returned index tensor, the
+free map, the four tables and checksums of the pool rows (``tests/golden/ref_pool.npz``);
+``tests/test_pool_oracle.py`` replays those traces through this file.
 """
 from __future__ import annotations
 
