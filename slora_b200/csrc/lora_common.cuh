@@ -152,17 +152,19 @@ __device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
 __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
-// One non-blocking probe of a barrier phase.  (mbarrier.try_wait may suspend the thread for a system-dependent time;
-// the pipelines here poll with test_wait instead so that a waiting warp resumes as soon as the phase flips.)
+// One probe of a barrier phase.  mbarrier.try_wait lets the hardware park the warp for a short, system-dependent time
+// when the phase has not flipped yet, so a waiting warp takes few issue slots from the warps that share its
+// scheduler (with test_wait, which never parks, three quarters of a decode launch's instructions were spin-loop
+// instructions; measured 1 to 3 % less time per layer with try_wait).  SLORA_WAIT_SPIN builds the test_wait form.
 __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
   uint32_t ok;
   asm volatile(
       "{\n"
       ".reg .pred p;\n"
-#ifdef SLORA_WAIT_SUSPEND
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
-#else
+#ifdef SLORA_WAIT_SPIN
       "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+#else
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
 #endif
       "selp.u32 %0, 1, 0, p;\n"
       "}\n"
@@ -171,10 +173,13 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
       : "memory");
   return ok != 0;
 }
-// Bounded wait: true when the phase completed within the limit.
+// Bounded wait: true when the phase completed within the limit (a number of probes and, because a probe may park the
+// warp for a while, a span of the SM clock as well: about 0.2 s).
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
+  const long long t0 = clock64();
   for (uint32_t i = 0; i < kSpinLimit; ++i) {
     if (mbar_try_wait(bar, parity)) return true;
+    if ((i & 255u) == 255u && clock64() - t0 > 400000000ll) return false;
   }
   return false;
 }

@@ -826,7 +826,7 @@ __device__ __forceinline__ bool segments_all_elsewhere(const TileSrc& s, const T
 }
 
 template <typename T, bool EXACT>
-__global__ void __launch_bounds__(kPipeThreads) lora_shrink_pipe_kernel(const ShrinkArgs a) {
+__global__ void __launch_bounds__(kPipeThreads, kPipeCtasPerSm) lora_shrink_pipe_kernel(const ShrinkArgs a) {
   extern __shared__ __align__(128) unsigned char ring_mem[];
   __shared__ __align__(16) PipeCtl ctl;
   __shared__ __align__(16) ShrinkRed red;
