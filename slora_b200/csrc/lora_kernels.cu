@@ -784,6 +784,7 @@ int run_expand(const TileSrc& src, const Tables& tb, const void* w, const void* 
   }
   const int pipe_piece = pow2_divisor(tb.pool_stride, kPipeChunk);
   bool can_pipe = delta_parts == 1 && delta_stride % 8 == 0 && pipe_piece * kMaxPieces >= kPipeChunk &&
+                  tb.pool_stride < (int64_t(1) << 30) &&
                   (kPipeChunk - 1) / tb.pool_stride + 2 <= kSpanRows;
   for (int p = 0; p < nproj; ++p)
     can_pipe = can_pipe && aligned16(y[p]) && y_stride[p] % 8 == 0 && aligned16(delta[p]);

@@ -565,6 +565,7 @@ __device__ __forceinline__ void shrink_producer(const ShrinkArgs& a, unsigned ch
       const int mytok = (lane >= RMAX && lane < RMAX + kTileTokens) ? di[8 + lane - RMAX] : 0;
       const T* src0 = is_w ? w + pp.d_l[k][lane & (RMAX - 1)] : x + static_cast<int64_t>(mytok) * a.x_stride;
       const int myslot = is_w ? lane : nrows + (lane - RMAX);  // position of this lane's chunk in the stage
+      const int m_j0 = di[3], m_p = di[4], m_rows = di[5];
       // cut the item into K-chunks that are multiples of 2048 elements (so the element -> consumer lane mapping, and
       // with it the summation order, does not depend on how many tokens share the tile) and, where that allows,
       // no larger than kMaxStageBytes
@@ -585,15 +586,10 @@ __device__ __forceinline__ void shrink_producer(const ShrinkArgs& a, unsigned ch
           ring_issue(r, c, slot, 0, nullptr, 0u, false, lane);
           continue;
         }
-        if (lane == 0) {
-          c.meta[slot][0] = (k0 == 0 ? FLAG_FIRST : 0) | (k0 + klen >= h_in ? FLAG_LAST : 0);
-          c.meta[slot][1] = nrows;
-          c.meta[slot][2] = n;
-          c.meta[slot][3] = di[3];
-          c.meta[slot][4] = di[4];
-          c.meta[slot][5] = klen;
-          c.meta[slot][6] = static_cast<int>(off);
-          c.meta[slot][7] = di[5];  // slot rows of the adapter
+        if (lane == 0) {  // the stage record in two 16-byte stores; [7] = slot rows of the adapter
+          int4* mrec = reinterpret_cast<int4*>(c.meta[slot]);
+          mrec[0] = make_int4((k0 == 0 ? FLAG_FIRST : 0) | (k0 + klen >= h_in ? FLAG_LAST : 0), nrows, n, m_j0);
+          mrec[1] = make_int4(m_p, klen, static_cast<int>(off), m_rows);
         } else if (lane >= RMAX && lane < RMAX + kTileTokens) {
           c.meta[slot][8 + lane - RMAX] = mytok;
         }
@@ -893,8 +889,8 @@ __device__ __forceinline__ void expand_producer(const ExpandArgs& a, unsigned ch
   const int64_t n_items = map.n_items;
 
   for (int64_t batch0 = blockIdx.x; batch0 < n_items && !r.dead; batch0 += 32 * G) {
-    // d_i[lane] = {valid, n, r, p, clen, first output, scale bits, c0, tok[8]}, d_l[lane][j] = pool row of slot row
-    // pr0 + j; d_i[lane][0] doubles as pr0
+    // d_i[lane] = {pr0, n, r, p, clen, first output, scale bits, chunk start inside pool row pr0, tok[8]},
+    // d_l[lane][j] = pool row of slot row pr0 + j
     const int64_t item = batch0 + lane * G;
     int valid = 0;
     if (item < n_items) {
@@ -949,7 +945,7 @@ __device__ __forceinline__ void expand_producer(const ExpandArgs& a, unsigned ch
               pp.d_i[lane][4] = clen;
               pp.d_i[lane][5] = static_cast<int>(c0 / rk);
               pp.d_i[lane][6] = __float_as_int(to_f32<T>(reinterpret_cast<const T*>(a.scales)[t.adapter]));
-              pp.d_i[lane][7] = static_cast<int>(c0);
+              pp.d_i[lane][7] = static_cast<int>(c0 - pr0 * S);  // chunk start inside its first pool row
               valid = 1;
             } else {
               set_status(a.status, SLORA_STATUS_BAD_TABLE);
@@ -961,7 +957,9 @@ __device__ __forceinline__ void expand_producer(const ExpandArgs& a, unsigned ch
     const uint32_t valid_mask = __ballot_sync(FULL_MASK, valid != 0);
     __syncwarp();
 
-    // one copy per lane: 0..15 pieces of the B chunk, 16..23 y segments, 24..31 delta rows
+    // one copy per lane: 0..15 pieces of the B chunk, 16..23 y segments, 24..31 delta rows.  Everything that does
+    // not depend on where the stage lands in the ring is worked out BEFORE the wait for ring space: what follows the
+    // wait is on the path from a consumer's release of a stage to the next copy's issue.
     for (uint32_t left = valid_mask; left != 0 && !r.dead; left &= left - 1) {
       const int k = __ffs(left) - 1;
       const int* di = pp.d_i[k];
@@ -972,6 +970,31 @@ __device__ __forceinline__ void expand_producer(const ExpandArgs& a, unsigned ch
       const uint32_t d_bytes = static_cast<uint32_t>(rk) * sizeof(T);
       const uint32_t total = b_bytes + static_cast<uint32_t>(n) * (y_bytes + d_bytes);
       const uint32_t sz = round128(total);
+      const int mytok = lane >= 16 ? di[8 + (lane & 7)] : 0;
+      uint32_t rel = 0, bytes = 0;  // this lane's copy: offset inside the stage, size
+      const T* src = w;
+      bool is_act = false;
+      if (lane < kMaxPieces) {
+        const int poff = lane * a.piece;
+        if (poff < clen) {
+          const int f = di[7] + poff;  // offset from the start of the chunk's first pool row
+          const int pr = f / static_cast<int>(S), col = f - pr * static_cast<int>(S);
+          src = w + pp.d_l[k][pr] * S + col;
+          rel = static_cast<uint32_t>(poff) * sizeof(T);
+          bytes = static_cast<uint32_t>(min(a.piece, clen - poff)) * sizeof(T);
+        }
+      } else if (lane < 16 + n) {
+        src = reinterpret_cast<const T*>(pick3(a.y, p)) + static_cast<int64_t>(mytok) * pick3(a.y_stride, p) + obase;
+        rel = b_bytes + static_cast<uint32_t>(lane - 16) * y_bytes;
+        bytes = y_bytes;
+        is_act = true;
+      } else if (lane >= 24 && lane < 24 + n) {
+        src = reinterpret_cast<const T*>(pick3(a.delta, p)) + static_cast<int64_t>(mytok) * a.delta_stride;
+        rel = b_bytes + static_cast<uint32_t>(n) * y_bytes + static_cast<uint32_t>(lane - 24) * d_bytes;
+        bytes = d_bytes;
+        is_act = true;
+      }
+      const int m_scale = di[6];
       const uint32_t off = ring_alloc(r, c, sz, lane);
       if (r.dead) break;
       const uint32_t slot = r.g % kSlots;
@@ -983,45 +1006,16 @@ __device__ __forceinline__ void expand_producer(const ExpandArgs& a, unsigned ch
         ring_issue(r, c, slot, 0, nullptr, 0u, false, lane);
         continue;
       }
-      const int mytok = lane >= 16 ? di[8 + (lane & 7)] : 0;
-      if (lane == 0) {
-        c.meta[slot][0] = 0;
-        c.meta[slot][1] = n;
-        c.meta[slot][2] = rk;
-        c.meta[slot][3] = p;
-        c.meta[slot][4] = clen;
-        c.meta[slot][5] = obase;
-        c.meta[slot][6] = di[6];
-        c.meta[slot][7] = static_cast<int>(off);
+      if (lane == 0) {  // the stage record in two 16-byte stores
+        int4* mrec = reinterpret_cast<int4*>(c.meta[slot]);
+        mrec[0] = make_int4(0, n, rk, p);
+        mrec[1] = make_int4(clen, obase, m_scale, static_cast<int>(off));
       } else if (lane >= 16 && lane < 24) {
         c.meta[slot][8 + lane - 16] = mytok;
       }
-      uint32_t dst = ring_base + off, bytes = 0;
-      const T* src = w;
-      bool is_act = false;
-      if (lane < kMaxPieces) {
-        const int poff = lane * a.piece;
-        if (poff < clen) {
-          const int64_t f = static_cast<int64_t>(di[7]) + poff;
-          const int64_t pr = f / S, col = f - pr * S;
-          src = w + pp.d_l[k][static_cast<int>(pr) - di[0]] * S + col;
-          dst += static_cast<uint32_t>(poff) * sizeof(T);
-          bytes = static_cast<uint32_t>(min(a.piece, clen - poff)) * sizeof(T);
-        }
-      } else if (lane < 16 + n) {
-        src = reinterpret_cast<const T*>(pick3(a.y, p)) + static_cast<int64_t>(mytok) * pick3(a.y_stride, p) + obase;
-        dst += b_bytes + static_cast<uint32_t>(lane - 16) * y_bytes;
-        bytes = y_bytes;
-        is_act = true;
-      } else if (lane >= 24 && lane < 24 + n) {
-        src = reinterpret_cast<const T*>(pick3(a.delta, p)) + static_cast<int64_t>(mytok) * a.delta_stride;
-        dst += b_bytes + static_cast<uint32_t>(n) * y_bytes + static_cast<uint32_t>(lane - 24) * d_bytes;
-        bytes = d_bytes;
-        is_act = true;
-      }
       __syncwarp();  // the arrive below publishes every lane's part of the stage record
       if (lane == 0) mbar_expect_tx(&c.full[slot], total);
-      ring_issue(r, c, slot, dst, src, bytes, is_act, lane);
+      ring_issue(r, c, slot, ring_base + off + rel, src, bytes, is_act, lane);
     }
     __syncwarp();
   }
