@@ -86,6 +86,10 @@ struct TpLink {
   int my_part, n_parts, half;
   int enabled;
   int inband;  // 1: no flags; the expand recognises delta values that have not arrived yet (see tp_has_empty)
+               // 2: the same, and the expand does not wait for the shrink's grid either: this GPU's own values are
+               //    recognised like the peers'.  The shrink then lets its dependents launch only after its own
+               //    grid-dependency wait, so what came before the shrink (the base projection that wrote y) is
+               //    complete before a CTA of the expand exists, and every CTA of the shrink is running by then.
 };
 
 struct ShrinkArgs {

@@ -510,7 +510,7 @@ int make_tmap(CUtensorMap* map, int dtype, const void* base, int64_t inner, int6
 // (Kernels with sizeable static shared memory pass static_bytes: the 48 KB default limit covers both kinds.)
 template <typename K>
 int ensure_dyn_smem(K kernel, int which, size_t smem, size_t static_bytes = 0) {
-  static int high_water[12][64];  // one row per kernel template (`which`)
+  static int high_water[16][64];  // one row per kernel template (`which`)
   if (smem + static_bytes <= 48 * 1024) return SLORA_OK;
   int dev = 0;
   cudaGetDevice(&dev);
@@ -813,6 +813,12 @@ int run_expand(const TileSrc& src, const Tables& tb, const void* w, const void* 
       const int rc2 = ensure_dyn_smem(k, which, smem);
       return rc2 ? rc2 : launch(k, grid, kPipeThreads, smem, flags, stream, a, "expand(pipelined)");
     };
+    if (tp && tp->inband) {  // the instantiation that checks whether the delta values have arrived
+      if (dtype == SLORA_F16)
+        return exact ? go(lora_expand_pipe_kernel<__half, true, true>, 12) : go(lora_expand_pipe_kernel<__half, false, true>, 10);
+      return exact ? go(lora_expand_pipe_kernel<__nv_bfloat16, true, true>, 13)
+                   : go(lora_expand_pipe_kernel<__nv_bfloat16, false, true>, 11);
+    }
     if (dtype == SLORA_F16) return exact ? go(lora_expand_pipe_kernel<__half, true>, 4) : go(lora_expand_pipe_kernel<__half, false>, 2);
     return exact ? go(lora_expand_pipe_kernel<__nv_bfloat16, true>, 5) : go(lora_expand_pipe_kernel<__nv_bfloat16, false>, 3);
   }
@@ -1187,7 +1193,7 @@ int slora_tp_shrink_push(const void* plan, const int64_t* ids, int nproj, const 
   tp.my_part = my_part;
   tp.n_parts = n_parts;
   tp.half = half;
-  tp.inband = inband ? 1 : 0;
+  tp.inband = inband == 2 ? 2 : (inband ? 1 : 0);
   TileSrc src;
   int32_t* status;
   int rc = make_src(plan, ids, T, n_adapters, 0, &src, &status);
@@ -1219,7 +1225,7 @@ int slora_tp_expand_wait(const void* plan, const int64_t* ids, int nproj, const 
   tp.my_part = my_part;
   tp.n_parts = n_parts;
   tp.half = half;
-  tp.inband = inband ? 1 : 0;
+  tp.inband = inband == 2 ? 2 : (inband ? 1 : 0);
   const int R = n_parts * part_width;
   const void* d[3];
   for (int p = 0; p < 3; ++p)

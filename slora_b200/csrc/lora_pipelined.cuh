@@ -122,6 +122,7 @@ struct Ring {
   uint32_t cap = kRingBytes;  // bytes of the ring
   const TpLink* tp = nullptr;  // expand under tensor parallelism: flags to wait for before activations are read
   int32_t* status = nullptr;
+  bool trigger_after_wait = false;  // shrink whose expand starts early: dependents may launch once this has waited
 };
 
 constexpr long long kTpLinkWaitCycles = 4000000000ll;  // about 2 s: ranks drift by host-side jitter, not more
@@ -191,8 +192,9 @@ __device__ __forceinline__ void tp_link_finish(const TpLink& tp, bool is_shrink)
 // before this rank has finished its next exchange on the other half, which starts after this kernel.
 constexpr uint32_t kTpEmpty2 = 0xffffffffu;  // two elements of the pattern 0xffff
 __device__ __forceinline__ bool tp_has_empty(const uint4& v) {
-  auto e = [](uint32_t w) { return (w & 0xffffu) == 0xffffu || (w >> 16) == 0xffffu; };
-  return e(v.x) || e(v.y) || e(v.z) || e(v.w);
+  // (bitwise ors: no short-circuit branches)
+  auto e = [](uint32_t w) { return ((w & 0xffffu) == 0xffffu) | ((w >> 16) == 0xffffu); };
+  return (e(v.x) | e(v.y) | e(v.z) | e(v.w)) != 0;
 }
 // Eight delta values from global memory, polled until none is the empty pattern; false when the wait ran out.
 __device__ __forceinline__ bool tp_poll_delta(const void* src, uint4& v, volatile int* gave_up) {
@@ -210,24 +212,32 @@ __device__ __forceinline__ bool tp_poll_delta(const void* src, uint4& v, volatil
     }
   }
 }
-// End of an expand with in-band signalling: the last CTA refills the consumed half with the empty pattern.
+// End of an expand with in-band signalling: the last CTA refills the consumed half with the empty pattern.  No fence
+// before the arrival: what has to precede the refill is the other CTAs' LOADS of the values, and a load has
+// returned its value before the code that follows it (the arrival) runs.
 __device__ __forceinline__ void tp_inband_finish(const TpLink& tp, void* half_base, int64_t bytes) {
   __shared__ int s_last;
   __syncthreads();
-  if (threadIdx.x == 0) {
-    __threadfence();
-    s_last = atomicAdd(tp.counter, 1) == static_cast<int>(gridDim.x) - 1;
-  }
+  if (threadIdx.x == 0) s_last = atomicAdd(tp.counter, 1) == static_cast<int>(gridDim.x) - 1;
   __syncthreads();
   if (!s_last) return;
   uint4* p = reinterpret_cast<uint4*>(half_base);
   const uint4 e = make_uint4(kTpEmpty2, kTpEmpty2, kTpEmpty2, kTpEmpty2);
-  for (int64_t i = threadIdx.x; i < bytes / 16; i += blockDim.x) p[i] = e;
+  const int64_t n16 = bytes / 16, nthr = blockDim.x;
+  int64_t i = threadIdx.x;
+  for (; i + 3 * nthr < n16; i += 4 * nthr) {  // four independent stores per thread and round
+    p[i] = e;
+    p[i + nthr] = e;
+    p[i + 2 * nthr] = e;
+    p[i + 3 * nthr] = e;
+  }
+  for (; i < n16; i += nthr) p[i] = e;
   if (threadIdx.x == 0) *tp.counter = 0;
 }
 
 __device__ __forceinline__ void ring_flush(Ring& r, PipeCtl& c, int lane) {
   pdl_wait();
+  if (r.trigger_after_wait) pdl_launch_dependents();
   if (r.tp != nullptr && !r.tp->inband && !tp_link_wait(*r.tp, lane)) {
     // the copies still go out (the consumers' barriers expect them); the result is flagged as not to be trusted
     if (lane == 0) set_status(r.status, SLORA_STATUS_TIMEOUT);
@@ -499,6 +509,7 @@ __device__ __forceinline__ void shrink_producer(const ShrinkArgs& a, unsigned ch
   PipeCtl::Prod& pp = c.prod[role];
   Ring r;
   r.role = role;
+  r.trigger_after_wait = a.tp.enabled && a.tp.inband == 2;
   constexpr int RMAX = EXACT ? kWideRows : kMaxRows;  // rows of the widest item = lane of the first token row
   const ItemMap map = EXACT ? build_item_map(a.src, a.nproj * a.max_rb, c, lane,
                                              [&](int rr, int) { return a.nproj * shrink_blocks_of(a, rr, false); })
@@ -689,6 +700,7 @@ template <typename T, bool EXACT>
 __device__ __forceinline__ void shrink_consumer(const ShrinkArgs& a, const unsigned char* ring_mem, PipeCtl& c,
                                                 ShrinkRed& red, int lane, int cw) {
   pdl_wait();
+  if (a.tp.enabled && a.tp.inband == 2) pdl_launch_dependents();
   float acc[kMaxRows][kTileTokens];
 #pragma unroll
   for (int j = 0; j < kMaxRows; ++j) {
@@ -830,7 +842,9 @@ __global__ void __launch_bounds__(kPipeThreads, kPipeCtasPerSm) lora_shrink_pipe
   if (segments_all_elsewhere(a.src, a.tb)) return;
   if (tid < kSlots) red.cnt[tid] = 0;
   pipe_init(ctl, tid);
-  pdl_launch_dependents();
+  // (a shrink whose expand starts early lets its dependents launch only after its own grid-dependency wait, thread
+  // by thread: see TpLink::inband)
+  if (!(a.tp.enabled && a.tp.inband == 2)) pdl_launch_dependents();
   if (EXACT) {
     fill_item_counts(a.src, a.tb, ctl, tid, [&](int rr, int n) { return shrink_items_of(a, rr, n); });
     __syncthreads();
@@ -881,6 +895,7 @@ __device__ __forceinline__ void expand_producer(const ExpandArgs& a, unsigned ch
   r.cap = EXACT ? kExpandRingBytes : kRingBytes;  // see kExpandRingBytes
   r.tp = a.tp.enabled ? &a.tp : nullptr;
   r.status = a.status;
+  if (a.tp.enabled && a.tp.inband == 2) r.pre = false;  // early start: nothing to wait for (see TpLink::inband)
   auto rank_ok = [&](int rk) { return expand_rank_ok(a, rk); };
   auto chunks_of = [&](int p, int rk) { return expand_chunks_of(a, p, rk); };
   const ItemMap map = EXACT ? build_item_map(a.src, total_chunks, c, lane, [&](int rr, int) { return expand_items_of(a, rr); })
@@ -1022,10 +1037,52 @@ __device__ __forceinline__ void expand_producer(const ExpandArgs& a, unsigned ch
   ring_finish(r, c, a.status, lane);
 }
 
+// Tensor parallelism with in-band signalling: before a warp uses a stage, it looks at the delta values the stage's
+// copy brought.  The common case - everything had landed - costs each lane one look at the vectors it is going to
+// use (the 16 bytes at its own k offset of each of the n rows) and the warp one vote.  Otherwise the warp settles the
+// whole delta block: lane l takes the vectors l, l + 32, ...; one that still holds the empty pattern is fetched again
+// from global memory until it has arrived (bounded) and put into the stage.  Every warp does this by itself (the
+// warps do not wait for one another; they write the same values), so the arithmetic that follows is the same
+// straight loop as without tensor parallelism.
+template <typename T>
+__device__ __noinline__ void expand_settle_slow(T* ds, const int* m, int r, const T* dglobal, int64_t dglobal_stride,
+                                                int32_t* status, volatile int* gave_up, int lane);
+
+template <typename T>
+__device__ __forceinline__ void expand_settle_delta(T* ds, const int* m, int r, const T* dglobal, int64_t dglobal_stride,
+                                                    int32_t* status, volatile int* gave_up, int lane) {
+  const int n = m[1];
+  const int kp = (lane & (r / 8 - 1)) * 8;  // r is a power of two (expand_rank_ok)
+  bool missing = false;
+  for (int tt = 0; tt < n; ++tt) missing |= tp_has_empty(*reinterpret_cast<const uint4*>(ds + tt * r + kp));
+  if (__any_sync(FULL_MASK, missing)) expand_settle_slow<T>(ds, m, r, dglobal, dglobal_stride, status, gave_up, lane);
+}
+
+// (kept out of line: it runs once in a long while and its polling loop would only bloat the consumers' hot loop)
+template <typename T>
+__device__ __noinline__ void expand_settle_slow(T* ds, const int* m, int r, const T* dglobal, int64_t dglobal_stride,
+                                                int32_t* status, volatile int* gave_up, int lane) {
+  const int n = m[1];
+  const int vec_per_row = r / 8;
+  for (int v = lane; v < n * vec_per_row; v += 32) {
+    const int tt = v / vec_per_row, k0 = (v - tt * vec_per_row) * 8;
+    uint4 dv = *reinterpret_cast<const uint4*>(ds + tt * r + k0);
+    if (tp_has_empty(dv)) {
+      if (!tp_poll_delta(dglobal + static_cast<int64_t>(m[8 + tt]) * dglobal_stride + k0, dv, gave_up)) {
+        set_status(status, SLORA_STATUS_TIMEOUT);
+        dv = make_uint4(0u, 0u, 0u, 0u);
+      }
+      *reinterpret_cast<uint4*>(ds + tt * r + k0) = dv;
+      fence_proxy_async();  // this store before the bulk copy that will reuse the stage's bytes
+    }
+  }
+  __syncwarp();
+}
+
 // One consumer warp's part of an expand stage.  LPO = lanes per output = r / 8.  The warp owns flat elements
 // [cw*2048, +2048) of the chunk as 8 loads of 256 elements; load m, lane l holds the 8 values of output
 // (cw*8 + m)*(32/LPO) + l/LPO for k in [(l % LPO)*8, +8).
-template <typename T, int LPO, bool FULL>
+template <typename T, int LPO, bool FULL, bool INBAND = false>
 __device__ __forceinline__ void expand_stage(const T* bs, const int* m, T* y, int64_t y_stride, int lane, int cw,
                                              const T* dglobal = nullptr, int64_t dglobal_stride = 0,
                                              int32_t* status = nullptr, volatile int* gave_up = nullptr) {
@@ -1045,6 +1102,9 @@ __device__ __forceinline__ void expand_stage(const T* bs, const int* m, T* y, in
     const int foff = cw * SPAN + mm * 256 + lane * 8;
     bv[mm] = (FULL || foff < clen) ? *reinterpret_cast<const uint4*>(bs + foff) : make_uint4(0u, 0u, 0u, 0u);
   }
+  // in-band signalling: have this stage's delta values all arrived?  (after the B loads have been issued, so that the
+  // look costs no latency of its own)
+  if (INBAND) expand_settle_delta<T>(const_cast<T*>(ds), m, R, dglobal, dglobal_stride, status, gave_up, lane);
   const int kp = (lane & (LPO - 1)) * 8;
   const int g = lane / LPO;
   const int m_base = expand_m_base<LPO>(lane);
@@ -1054,14 +1114,7 @@ __device__ __forceinline__ void expand_stage(const T* bs, const int* m, T* y, in
   for (int i = 0; i < NV; ++i) o_loc[i] = (cw * 8 + m_base + i) * OPL + g;  // output index inside the chunk
 
   for (int tt = 0; tt < n; ++tt) {
-    uint4 dv = *reinterpret_cast<const uint4*>(ds + tt * R + kp);
-    if (dglobal != nullptr && tp_has_empty(dv)) {
-      // tensor parallelism, in-band signalling: another rank's columns had not landed when the stage was copied
-      if (!tp_poll_delta(dglobal + static_cast<int64_t>(m[8 + tt]) * dglobal_stride + kp, dv, gave_up)) {
-        set_status(status, SLORA_STATUS_TIMEOUT);
-        dv = make_uint4(0u, 0u, 0u, 0u);
-      }
-    }
+    const uint4 dv = *reinterpret_cast<const uint4*>(ds + tt * R + kp);
     float yv[NV];
 #pragma unroll
     for (int i = 0; i < NV; ++i) {
@@ -1082,10 +1135,10 @@ __device__ __forceinline__ void expand_stage(const T* bs, const int* m, T* y, in
   }
 }
 
-template <typename T>
+template <typename T, bool INBAND>
 __device__ __forceinline__ void expand_consumer(const ExpandArgs& a, const unsigned char* ring_mem, PipeCtl& c,
                                                 int lane, int cw) {
-  pdl_wait();
+  if (!(a.tp.enabled && a.tp.inband == 2)) pdl_wait();
   for (uint32_t g = 0;; ++g) {
     const uint32_t slot = g % kSlots;
     if (!mbar_wait_timed(&c.full[slot], (g / kSlots) & 1)) {
@@ -1098,23 +1151,23 @@ __device__ __forceinline__ void expand_consumer(const ExpandArgs& a, const unsig
     const int p = m[3];
     T* y = reinterpret_cast<T*>(pick3(a.y, p));
     const int64_t ystr = pick3(a.y_stride, p);
-    const T* dg = (a.tp.enabled && a.tp.inband) ? reinterpret_cast<const T*>(pick3(a.delta, p)) : nullptr;
+    const T* dg = INBAND ? reinterpret_cast<const T*>(pick3(a.delta, p)) : nullptr;
     const int64_t dgs = a.delta_stride;
     if (m[4] == kPipeChunk) {  // complete chunk: no bounds checks
       switch (m[2]) {
-        case 8: expand_stage<T, 1, true>(bs, m, y, ystr, lane, cw, dg, dgs, a.status, &c.tp_gave_up); break;
-        case 16: expand_stage<T, 2, true>(bs, m, y, ystr, lane, cw, dg, dgs, a.status, &c.tp_gave_up); break;
-        case 32: expand_stage<T, 4, true>(bs, m, y, ystr, lane, cw, dg, dgs, a.status, &c.tp_gave_up); break;
-        case 64: expand_stage<T, 8, true>(bs, m, y, ystr, lane, cw, dg, dgs, a.status, &c.tp_gave_up); break;
-        default: expand_stage<T, 16, true>(bs, m, y, ystr, lane, cw, dg, dgs, a.status, &c.tp_gave_up); break;
+        case 8: expand_stage<T, 1, true, INBAND>(bs, m, y, ystr, lane, cw, dg, dgs, a.status, &c.tp_gave_up); break;
+        case 16: expand_stage<T, 2, true, INBAND>(bs, m, y, ystr, lane, cw, dg, dgs, a.status, &c.tp_gave_up); break;
+        case 32: expand_stage<T, 4, true, INBAND>(bs, m, y, ystr, lane, cw, dg, dgs, a.status, &c.tp_gave_up); break;
+        case 64: expand_stage<T, 8, true, INBAND>(bs, m, y, ystr, lane, cw, dg, dgs, a.status, &c.tp_gave_up); break;
+        default: expand_stage<T, 16, true, INBAND>(bs, m, y, ystr, lane, cw, dg, dgs, a.status, &c.tp_gave_up); break;
       }
     } else {
       switch (m[2]) {
-        case 8: expand_stage<T, 1, false>(bs, m, y, ystr, lane, cw, dg, dgs, a.status, &c.tp_gave_up); break;
-        case 16: expand_stage<T, 2, false>(bs, m, y, ystr, lane, cw, dg, dgs, a.status, &c.tp_gave_up); break;
-        case 32: expand_stage<T, 4, false>(bs, m, y, ystr, lane, cw, dg, dgs, a.status, &c.tp_gave_up); break;
-        case 64: expand_stage<T, 8, false>(bs, m, y, ystr, lane, cw, dg, dgs, a.status, &c.tp_gave_up); break;
-        default: expand_stage<T, 16, false>(bs, m, y, ystr, lane, cw, dg, dgs, a.status, &c.tp_gave_up); break;
+        case 8: expand_stage<T, 1, false, INBAND>(bs, m, y, ystr, lane, cw, dg, dgs, a.status, &c.tp_gave_up); break;
+        case 16: expand_stage<T, 2, false, INBAND>(bs, m, y, ystr, lane, cw, dg, dgs, a.status, &c.tp_gave_up); break;
+        case 32: expand_stage<T, 4, false, INBAND>(bs, m, y, ystr, lane, cw, dg, dgs, a.status, &c.tp_gave_up); break;
+        case 64: expand_stage<T, 8, false, INBAND>(bs, m, y, ystr, lane, cw, dg, dgs, a.status, &c.tp_gave_up); break;
+        default: expand_stage<T, 16, false, INBAND>(bs, m, y, ystr, lane, cw, dg, dgs, a.status, &c.tp_gave_up); break;
       }
     }
     __syncwarp();
@@ -1122,8 +1175,10 @@ __device__ __forceinline__ void expand_consumer(const ExpandArgs& a, const unsig
   }
 }
 
-template <typename T, bool EXACT>
-__global__ void __launch_bounds__(kPipeThreads) lora_expand_pipe_kernel(const ExpandArgs a) {
+// INBAND: the instantiation for tensor parallelism with in-band signalling (TpLink::inband); the plain one carries
+// none of its checks.
+template <typename T, bool EXACT, bool INBAND = false>
+__global__ void __launch_bounds__(kPipeThreads, kPipeCtasPerSm) lora_expand_pipe_kernel(const ExpandArgs a) {
   extern __shared__ __align__(128) unsigned char ring_mem[];
   __shared__ __align__(16) PipeCtl ctl;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -1137,13 +1192,14 @@ __global__ void __launch_bounds__(kPipeThreads) lora_expand_pipe_kernel(const Ex
   if (warp < kProducerWarps) {
     expand_producer<T, EXACT>(a, ring_mem, ctl, lane, warp);
   } else {
-    expand_consumer<T>(a, ring_mem, ctl, lane, warp - kProducerWarps);
+    expand_consumer<T, INBAND>(a, ring_mem, ctl, lane, warp - kProducerWarps);
   }
   if (a.tp.enabled) {
-    if (a.tp.inband) {
-      // the half of the delta buffer this exchange used: [3][full_tokens][delta_stride] elements from delta[0] on
+    if (INBAND) {
+      // what this exchange used of its half of the delta buffer: [nproj][full_tokens][delta_stride] elements from
+      // delta[0] on
       tp_inband_finish(a.tp, const_cast<void*>(a.delta[0]),
-                       3 * a.tp.full_tokens * a.delta_stride * static_cast<int64_t>(sizeof(T)));
+                       a.nproj * a.tp.full_tokens * a.delta_stride * static_cast<int64_t>(sizeof(T)));
     } else {
       tp_link_finish(a.tp, false);
     }

@@ -191,7 +191,7 @@ class _EmulatedPeers:
         return px
 
 
-@pytest.mark.parametrize("inband", [True, False])
+@pytest.mark.parametrize("inband", [2, True, False])
 @pytest.mark.parametrize("T", [40, 200])
 def test_fused_exchange_emulated_on_one_gpu(T, inband):
     """slora_tp_shrink_push / slora_tp_expand_wait, four ranks emulated on one GPU: every rank's shrink stores its rows
@@ -221,7 +221,8 @@ def test_fused_exchange_emulated_on_one_gpu(T, inband):
         shards.append((t, pa.to(DEV), pb.to(DEV)))
     peers = _EmulatedPeers(N, T, R, inband)
     pxs = [peers.rank(r) for r in range(N)]
-    be = tp.CudaBackend()
+    # (inband == 2: the expand does not wait for its own GPU's shrink either; chained as programmatic dependents)
+    be = tp.CudaBackend(use_pdl=inband == 2)
     xd, idd = x.to(DEV), ids.to(DEV)
     plans = [be.make_plan(idd, t) for t, _, _ in shards]
     want = [torch.stack([(x[i].float() @ ads[int(ids[i])][0][p].half().float().T)

@@ -22,7 +22,7 @@ RANKS = [8, 16, 8]
 class OracleBackend:
     """Same contract as tp.CudaBackend, computed with the CPU oracle (test infrastructure)."""
 
-    def make_plan(self, ids, t):
+    def make_plan(self, ids, t, local_width=None):
         return None
 
     def shrink(self, plan, ids, qkvo, deltas, x, pool_a, t, rank_mult=1):
