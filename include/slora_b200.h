@@ -73,6 +73,13 @@ extern "C" {
                                   group that the tensor-core kernels serve (slora_plan_header: no small tiles, every big
                                   group's rank a power of two that divides pool_stride and fits the delta buffers), so
                                   the call's CUDA-core launch would find nothing and is left out. */
+/* The plan was built by slora_plan_build_ex with this max_rank (resolved tiles: token ids, scale and pool rows of
+ * every tile at an address that follows from the tile index, so a launch fetches them in one round trip instead of
+ * chasing perm and the loc table).  Passing the flag for a plan built without them, or with another max_rank, is
+ * harmless when the workspace is at least slora_plan_workspace_bytes_ex(T, n_adapters, max_rank) bytes: the
+ * kernels check the plan's header and fall back to the tables. */
+#define SLORA_FLAG_RESOLVED(max_rank) (((((unsigned)(max_rank) + 7u) >> 3) & 0x1fu) << 8)
+#define SLORA_FLAG_RESOLVED_MASK (0x1fu << 8)
 /* With SLORA_FLAG_BIG_GROUPS: the plan's count of 128-token tiles of big groups (slora_plan_header word 6), when the
    caller has read it, in bits 16..31 of flags.  The tensor-core launches then enumerate exactly those tiles (and
    size their K split for them) instead of the most a batch of T tokens could have.  0 = not known. */
@@ -152,6 +159,13 @@ int slora_sgmv_expand(void* y, const void* delta, const void* w, const int64_t* 
  * slora_plan_status copies the plan's status word back (synchronises the stream).
  */
 size_t slora_plan_workspace_bytes(int64_t T, int64_t n_adapters);
+/* The same with resolved tiles for adapters of rank <= max_rank (see SLORA_FLAG_RESOLVED): loc is the adapters' loc
+ * table and scales their scale table (16-bit values; may be NULL), both read when the plan is built, so the plan
+ * must be rebuilt when they change.  max_rank = 0 or loc = NULL: no resolved tiles. */
+size_t slora_plan_workspace_bytes_ex(int64_t T, int64_t n_adapters, int max_rank);
+int slora_plan_build_ex(void* workspace, size_t workspace_bytes, const int64_t* ids, int64_t T, const int64_t* start,
+                        const int64_t* ranks4, const int64_t* loc, const void* scales, int64_t n_adapters,
+                        int64_t loc_len, int max_rank, void* stream);
 int slora_plan_build(void* workspace, size_t workspace_bytes, const int64_t* ids, int64_t T, const int64_t* start,
                      const int64_t* ranks4, int64_t n_adapters, int64_t loc_len, void* stream);
 /*

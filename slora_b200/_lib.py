@@ -19,6 +19,11 @@ FLAG_BIG_GROUPS = 2
 FLAG_EXACT_ITEMS = 4
 FLAG_ONLY_BIG = 16
 
+
+def flag_resolved(max_rank: int) -> int:
+    """``SLORA_FLAG_RESOLVED(max_rank)``: the plan holds resolved tiles for adapters of rank up to ``max_rank``."""
+    return (((int(max_rank) + 7) >> 3) & 0x1f) << 8 if 0 < max_rank <= 128 else 0
+
 STATUS_BITS = {1: "bad adapter id", 2: "bad table entry", 4: "unsupported rank", 8: "bulk-copy wait timed out"}
 
 
@@ -50,6 +55,8 @@ _SIGS = {
                                   c_int64, c_int, c_int64, c_int64, c_int64, c_int64, c_int64, c_int, _P]),
     "slora_plan_workspace_bytes": (c_size_t, [c_int64, c_int64]),
     "slora_plan_build": (c_int, [_P, c_size_t, _P, c_int64, _P, _P, c_int64, c_int64, _P]),
+    "slora_plan_workspace_bytes_ex": (c_size_t, [c_int64, c_int64, c_int]),
+    "slora_plan_build_ex": (c_int, [_P, c_size_t, _P, c_int64, _P, _P, _P, _P, c_int64, c_int64, c_int, _P]),
     "slora_plan_status": (c_int, [_P, POINTER(c_int), POINTER(c_int), _P]),
     "slora_lora_shrink_multi": (c_int, [_P, _P, c_int, POINTER(c_int), POINTER(c_void_p), c_int64, c_int, _P,
                                         c_int64, c_int, _P, c_int64, c_int64, _P, _P, _P, c_int64, c_int64, c_int64,

@@ -11,6 +11,7 @@ embedding stay with the caller, exactly where the reference has them.
 from __future__ import annotations
 
 import ctypes
+import os
 
 import torch
 
@@ -25,22 +26,39 @@ class BatchPlan:
     """
 
     def __init__(self, token_adapter_ids: torch.Tensor, a_start: torch.Tensor, a_len: torch.Tensor, loc_len: int,
-                 workspace: torch.Tensor | None = None):
+                 workspace: torch.Tensor | None = None, a_loc: torch.Tensor | None = None,
+                 a_scaling: torch.Tensor | None = None, max_rank: int = 0):
+        """``a_loc`` (and ``a_scaling``) with ``max_rank`` > 0: the plan also holds resolved tiles for adapters of
+        rank up to ``max_rank`` (token ids, scale and pool rows of every tile where a launch finds them in one round
+        trip; C entry ``slora_plan_build_ex``).  ``self.flags`` then carries ``SLORA_FLAG_RESOLVED(max_rank)`` for the
+        calls that use the plan; the plan must be rebuilt when the tables change."""
         _lib.require_cuda(token_adapter_ids, a_start, a_len)
         if token_adapter_ids.dtype != torch.int64 or token_adapter_ids.dim() != 1:
             raise RuntimeError("token_adapter_ids must be a 1-D int64 tensor")
         self.ids = token_adapter_ids.contiguous()
         self.T = self.ids.numel()
         self.n_adapters = a_start.numel()
-        need = _lib.lib.slora_plan_workspace_bytes(self.T, self.n_adapters)
+        cap = 0
+        if a_loc is not None and 0 < max_rank <= 128 and os.environ.get("SLORA_RESOLVED_TILES", "1") != "0":
+            _lib.require_cuda(a_loc)
+            if a_loc.dtype != torch.int64 or not a_loc.is_contiguous() or a_loc.numel() != int(loc_len):
+                raise RuntimeError("a_loc must be the contiguous int64 loc table of loc_len entries")
+            if a_scaling is not None and (a_scaling.element_size() != 2 or not a_scaling.is_contiguous()
+                                          or a_scaling.numel() != self.n_adapters):
+                raise RuntimeError("a_scaling must hold one 16-bit value per adapter")
+            cap = int(max_rank)
+        self.flags = _lib.flag_resolved(cap)
+        need = _lib.lib.slora_plan_workspace_bytes_ex(self.T, self.n_adapters, cap)
         if workspace is None:
             workspace = torch.empty((need + 3) // 4, dtype=torch.int32, device=self.ids.device)
         elif workspace.numel() * workspace.element_size() < need:
             raise RuntimeError(f"plan workspace too small: {workspace.numel() * workspace.element_size()} < {need}")
         self.workspace = workspace
-        _lib.check(_lib.lib.slora_plan_build(workspace.data_ptr(), workspace.numel() * workspace.element_size(),
-                                             self.ids.data_ptr(), self.T, a_start.data_ptr(), a_len.data_ptr(),
-                                             self.n_adapters, int(loc_len), _lib.current_stream_ptr()))
+        _lib.check(_lib.lib.slora_plan_build_ex(
+            workspace.data_ptr(), workspace.numel() * workspace.element_size(), self.ids.data_ptr(), self.T,
+            a_start.data_ptr(), a_len.data_ptr(), a_loc.data_ptr() if cap else 0,
+            a_scaling.data_ptr() if cap and a_scaling is not None else 0, self.n_adapters, int(loc_len), cap,
+            _lib.current_stream_ptr()))
 
     @property
     def ptr(self) -> int:
@@ -72,7 +90,8 @@ class BatchPlan:
         buf = (ctypes.c_int32 * 16)()
         _lib.check(_lib.lib.slora_plan_header(self.ptr, buf, _lib.current_stream_ptr()))
         return {"tiles": buf[1], "status": buf[2], "tokens": buf[4], "adapters": buf[5], "big_tiles": buf[6],
-                "uniform_rank": buf[9], "small_tiles": buf[10], "big_rank_max": buf[11], "big_ranks_pow2": bool(buf[12])}
+                "uniform_rank": buf[9], "small_tiles": buf[10], "big_rank_max": buf[11], "big_ranks_pow2": bool(buf[12]),
+                "resolved_cap": buf[14] if buf[13] > 0 else 0}
 
     def check(self):
         st, _ = self.status()
@@ -125,8 +144,9 @@ class LoraBatchOps:
         T = self.ids.numel()
         dtype = self.key_buffer[0].dtype
         self.delta = [torch.zeros((T, self.max_lora_dim), dtype=dtype, device=self.ids.device) for _ in range(3)]
-        self.plan = BatchPlan(self.ids, self.a_start, self.a_len, self.a_loc.numel()) if use_plan else None
-        self.flags = self.base_flags
+        self.plan = BatchPlan(self.ids, self.a_start, self.a_len, self.a_loc.numel(), a_loc=self.a_loc,
+                              a_scaling=self.a_scaling, max_rank=self.max_lora_dim) if use_plan else None
+        self.flags = self.base_flags | (self.plan.flags if self.plan is not None else 0)
         only_big, n_big_tiles = False, 0
         if self.plan is not None and T >= 128 and (big_groups is None or mixed_ranks is None):
             h = self.plan.header()

@@ -28,6 +28,16 @@ constexpr int PH_MAGIC = 0, PH_NTILES = 1, PH_STATUS = 2, PH_MAXTILES = 3, PH_T 
 // PH_NSMALL: 8-token tiles of groups that are not big (the CUDA-core kernels' share when big groups go to the tensor
 // cores); PH_BIG_RMAX: widest rank among the big groups; PH_BIG_POW2: 1 when every big group's rank is a power of two
 constexpr int PH_NSMALL = 10, PH_BIG_RMAX = 11, PH_BIG_POW2 = 12;
+// Resolved tiles (optional; a plan built with the adapters' loc table and a rank cap): after the big-tile records,
+// one entry of kXtHead + 4 * cap words per tile slot: {token ids of the tile [8]; the adapter's scale (its 16 bits as
+// stored in the table), 0, 0, 0; pool rows of projection 0 [cap], of projection 1 [cap], 2, 3} - everything a launch
+// would otherwise chase through perm, the scale table and the loc table, at an
+// address that follows from the tile index alone, so a producer can fetch the record and what hangs off it in one
+// round trip.  PH_XOFF = word offset of the entries (0: none), PH_XRCAP = cap; tile record word 6 = 1 when the
+// tile's entry is filled (rank <= cap).  A pool row that does not fit 31 bits is stored as -1 (the range check
+// that follows every lookup refuses it).
+constexpr int PH_XOFF = 13, PH_XRCAP = 14;
+constexpr int kXtHead = 12;
 constexpr int kBigGroupTokens = 128;  // planned batches: same-adapter groups at least this long go to the tensor cores
 constexpr int kBigSegmentTokens = 32;  // segment calls: segments at least this long do
 constexpr int kBigTileTokens = 128;
@@ -51,6 +61,7 @@ struct TileSrc {
   int big_slots;          // PLAN: big-tile slots the tensor-core launch enumerates
   int big_exact;          // PLAN: big_slots is the plan's own count (host side), not an upper bound
   int mma_max_rows;       // adapters with more slot rows than this (the call's delta width) stay on the CUDA cores
+  int xoff, xrcap;        // PLAN: where the host expects resolved tiles and their rank cap (0: do not look for them)
   int64_t T;
 };
 
@@ -72,6 +83,12 @@ struct TileInfo {
   int r;      // slot rows (= LoRA rank of the adapter as stored in the tables)
   int64_t loc_base;
   const int32_t* perm;  // PLAN only
+  // PLAN with resolved tiles (TileSrc::xoff > 0): xt = this tile's entry, fetched without waiting for the header or
+  // the record (the address follows from the tile index); xok = header and record confirm that the entry is there
+  const int32_t* xt;
+  int xrcap;
+  bool xok;
+  int tok[kTileTokens];  // the entry's token ids (valid when xok)
 };
 
 // Tensor-parallel link of a pipelined shrink (writes its result into every rank's delta buffer and signals) or expand
@@ -282,22 +299,38 @@ __device__ __forceinline__ bool lookup_tile(const TileSrc& s, const Tables& tb, 
                                             int32_t* status) {
   if (s.mode == MODE_PLAN) {
     const int32_t* hdr = s.plan;
-    if (tile_idx >= hdr[PH_NTILES]) return false;
+    // resolved tiles: the entry's token ids are fetched together with the header and the record
+    t.xrcap = s.xrcap;
+    t.xt = s.xoff > 0 ? s.plan + s.xoff + static_cast<int64_t>(tile_idx) * (kXtHead + 4 * s.xrcap) : nullptr;
+    int4 k0 = make_int4(0, 0, 0, 0), k1 = k0;
+    if (t.xt != nullptr) {
+      k0 = reinterpret_cast<const int4*>(t.xt)[0];
+      k1 = reinterpret_cast<const int4*>(t.xt)[1];
+    }
+    t.tok[0] = k0.x, t.tok[1] = k0.y, t.tok[2] = k0.z, t.tok[3] = k0.w;
+    t.tok[4] = k1.x, t.tok[5] = k1.y, t.tok[6] = k1.z, t.tok[7] = k1.w;
+    const int n_tiles = hdr[PH_NTILES], h_xoff = hdr[PH_XOFF], h_xrcap = hdr[PH_XRCAP];
     const int4* rec = reinterpret_cast<const int4*>(s.plan + PH_WORDS + kTileWords * tile_idx);
     const int4 r0 = rec[0];
     const int4 r1 = rec[1];
+    if (tile_idx >= n_tiles) return false;
     t.adapter = r0.x;
     t.first = r0.y;
     t.n = r0.z;
     t.r = r0.w;
     t.loc_base = r1.x;
     t.perm = s.plan + PH_WORDS + kTileWords * hdr[PH_MAXTILES];
+    // the entry counts when the plan holds resolved tiles where this launch expects them (same offset, same cap)
+    t.xok = t.xt != nullptr && h_xoff == s.xoff && h_xrcap == s.xrcap && r1.z != 0;
     // big groups an eligible layout lets the tensor-core kernels serve are theirs (same predicate as mma_serves)
     if (s.seg_split > 0 && r1.y != 0 && tb.pool_stride % t.r == 0 && t.r <= s.mma_max_rows) return false;
     return t.n > 0 && t.r > 0;
   }
   int64_t adapter;
   t.perm = nullptr;
+  t.xt = nullptr;
+  t.xrcap = 0;
+  t.xok = false;
   if (s.mode == MODE_TOKEN) {
     if (tile_idx >= s.T) return false;
     adapter = s.ids[tile_idx];
@@ -339,8 +372,20 @@ __device__ __forceinline__ bool lookup_tile(const TileSrc& s, const Tables& tb, 
   return t.r > 0;
 }
 
+// (callers that may see resolved tiles index with constants - unrolled loops - so that tok[] stays in registers)
 __device__ __forceinline__ int tile_token(const TileInfo& t, int i) {
+  if (t.xok) return t.tok[i];
   return t.perm ? t.perm[t.first + i] : t.first + i;
+}
+// Pool row of slot row `pr` (< the cap when there are resolved tiles) of projection `qkvo` of the tile's adapter, not
+// range-checked.  With resolved tiles the entry is read whether or not it turns out to count: the load does not
+// wait for the header and the record, and the table is only chased when the entry does not count.
+__device__ __forceinline__ int64_t tile_loc(const TileInfo& t, const Tables& tb, int qkvo, int64_t pr) {
+  if (t.xt != nullptr) {
+    const int v = t.xt[kXtHead + qkvo * t.xrcap + static_cast<int>(min(pr, static_cast<int64_t>(t.xrcap - 1)))];
+    if (t.xok) return v;
+  }
+  return tb.loc[t.loc_base + static_cast<int64_t>(t.r) * qkvo + pr];
 }
 
 // Sum V per-lane values across the warp; lane l returns the total of logical index (l >> (5 - log2 V)).

@@ -285,13 +285,29 @@ struct PlanLayout {
   int max_tiles;
   int max_big;
   size_t words;
+  int xoff;  // word offset of the resolved tiles (0: none)
 };
-PlanLayout plan_layout(int64_t T, int64_t n_adapters) {
+// Rank cap of a plan's resolved tiles for a caller's max_rank: a multiple of 8 up to 128 (0: none).
+int resolved_cap(int max_rank) {
+  if (max_rank <= 0) return 0;
+  const int cap = (max_rank + 7) & ~7;
+  return cap > 128 ? 0 : cap;
+}
+
+PlanLayout plan_layout(int64_t T, int64_t n_adapters, int xrcap = 0) {
   PlanLayout l;
   l.max_tiles = max_tiles_for(T, n_adapters);
   l.max_big = max_big_for(T);
   l.words = static_cast<size_t>(PH_WORDS) + static_cast<size_t>(kTileWords) * l.max_tiles + 2u * static_cast<size_t>(T) +
             static_cast<size_t>(n_adapters) + 4 + static_cast<size_t>(kTileWords) * l.max_big;
+  l.xoff = 0;
+  if (xrcap > 0) {
+    l.words = (l.words + 3) & ~static_cast<size_t>(3);
+    if (l.words + static_cast<size_t>(l.max_tiles) * (kXtHead + 4 * xrcap) < 0x7fffffffu) {
+      l.xoff = static_cast<int>(l.words);
+      l.words += static_cast<size_t>(l.max_tiles) * (kXtHead + 4 * xrcap);
+    }
+  }
   return l;
 }
 
@@ -550,6 +566,7 @@ int run_shrink(const TileSrc& src, const Tables& tb, const void* w, const void* 
   ShrinkArgs a;
   memset(&a, 0, sizeof(a));
   a.src = src;
+  a.src.xoff = a.src.xrcap = 0;  // resolved tiles are the pipelined kernels' (set where those are launched)
   a.tb = tb;
   a.w = w;
   a.x = x;
@@ -649,6 +666,8 @@ int run_shrink(const TileSrc& src, const Tables& tb, const void* w, const void* 
   if (tp && choice == CHOOSE_SIMPLE) return fail(SLORA_ERR_SHAPE, "No suitable kernel. the linked shrink is pipelined only");
   if (can_pipe && choice != CHOOSE_SIMPLE) {
     a.rows_per_cta = kMaxRows;
+    a.src.xoff = src.xoff;
+    a.src.xrcap = src.xrcap;
     a.max_rb = (delta_width + kMaxRows - 1) / kMaxRows;
     const int64_t items = static_cast<int64_t>(src.slots) * nproj * a.max_rb;
     const int64_t grid = items < sm_count() * kPipeCtasPerSm ? items : sm_count() * kPipeCtasPerSm;
@@ -704,6 +723,7 @@ int run_expand(const TileSrc& src, const Tables& tb, const void* w, const void* 
   ExpandArgs a;
   memset(&a, 0, sizeof(a));
   a.src = src;
+  a.src.xoff = a.src.xrcap = 0;  // resolved tiles are the pipelined kernels' (set where those are launched)
   a.tb = tb;
   a.w = w;
   a.scales = scales;
@@ -795,6 +815,8 @@ int run_expand(const TileSrc& src, const Tables& tb, const void* w, const void* 
   if (tp && choice == CHOOSE_SIMPLE) return fail(SLORA_ERR_SHAPE, "No suitable kernel. the linked expand is pipelined only");
   if (can_pipe && choice != CHOOSE_SIMPLE) {
     a.piece = pipe_piece;
+    a.src.xoff = src.xoff;
+    a.src.xrcap = src.xrcap;
     set_chunks(kPipeChunk);
     const int64_t items = static_cast<int64_t>(src.slots) * a.chunk_begin[nproj];
     const int64_t grid = items < sm_count() * kPipeCtasPerSm ? items : sm_count() * kPipeCtasPerSm;
@@ -849,6 +871,12 @@ int make_src(const void* plan, const int64_t* ids, int64_t T, int64_t n_adapters
       src->big_exact = 1;
     }
     src->seg_split = ((flags & SLORA_FLAG_BIG_GROUPS) && T >= kBigGroupTokens) ? kBigGroupTokens : 0;
+    // the caller says the plan was built with resolved tiles (SLORA_FLAG_RESOLVED): where the launch will look
+    const int cap = static_cast<int>((flags >> 8) & 0x1fu) * 8;
+    if (cap > 0 && cap <= 128) {
+      src->xoff = plan_layout(T, n_adapters, cap).xoff;
+      src->xrcap = src->xoff > 0 ? cap : 0;
+    }
     *status = const_cast<int32_t*>(src->plan) + PH_STATUS;
   } else {
     if (!ids && T > 0) return fail(SLORA_ERR_NULL, "neither plan nor ids given");
@@ -989,25 +1017,36 @@ int slora_sgmv_expand(void* y, const void* delta, const void* w, const int64_t* 
                     static_cast<cudaStream_t>(stream));
 }
 
-size_t slora_plan_workspace_bytes(int64_t T, int64_t n_adapters) {
+size_t slora_plan_workspace_bytes(int64_t T, int64_t n_adapters) { return slora_plan_workspace_bytes_ex(T, n_adapters, 0); }
+
+size_t slora_plan_workspace_bytes_ex(int64_t T, int64_t n_adapters, int max_rank) {
   if (T < 0 || n_adapters < 0) return 0;
-  return plan_layout(T, n_adapters).words * sizeof(int32_t);
+  return plan_layout(T, n_adapters, resolved_cap(max_rank)).words * sizeof(int32_t);
 }
 
 int slora_plan_build(void* workspace, size_t workspace_bytes, const int64_t* ids, int64_t T, const int64_t* start,
                      const int64_t* ranks4, int64_t n_adapters, int64_t loc_len, void* stream) {
+  return slora_plan_build_ex(workspace, workspace_bytes, ids, T, start, ranks4, nullptr, nullptr, n_adapters, loc_len, 0,
+                             stream);
+}
+
+int slora_plan_build_ex(void* workspace, size_t workspace_bytes, const int64_t* ids, int64_t T, const int64_t* start,
+                        const int64_t* ranks4, const int64_t* loc, const void* scales, int64_t n_adapters,
+                        int64_t loc_len, int max_rank, void* stream) {
   if (!workspace || (!ids && T > 0)) return fail(SLORA_ERR_NULL, "workspace or ids is null");
   if (!start || !ranks4) return fail(SLORA_ERR_NULL, "start or ranks4 is null");
   if (!aligned16(workspace)) return fail(SLORA_ERR_ALIGN, "plan workspace is not 16-byte aligned");
   if (T < 0 || T > 0x3fffffff || n_adapters < 0 || n_adapters > 0x3fffffff)
     return fail(SLORA_ERR_SHAPE, "T=%lld or n_adapters=%lld out of range", (long long)T, (long long)n_adapters);
-  const PlanLayout l = plan_layout(T, n_adapters);
+  const int cap = loc ? resolved_cap(max_rank) : 0;
+  const PlanLayout l = plan_layout(T, n_adapters, cap);
   if (workspace_bytes < l.words * sizeof(int32_t))
     return fail(SLORA_ERR_WORKSPACE, "plan workspace has %zu bytes, needs %zu", workspace_bytes,
                 l.words * sizeof(int32_t));
   plan_build_kernel<<<1, 1024, 0, static_cast<cudaStream_t>(stream)>>>(
       reinterpret_cast<int32_t*>(workspace), ids, start, ranks4, loc_len, static_cast<int>(T),
-      static_cast<int>(n_adapters), l.max_tiles, l.max_big);
+      static_cast<int>(n_adapters), l.max_tiles, l.max_big, loc, static_cast<const unsigned short*>(scales), l.xoff,
+      cap);
   plan_fence_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>();
   return check_launch("plan_build", 2);
 }
@@ -1196,7 +1235,7 @@ int slora_tp_shrink_push(const void* plan, const int64_t* ids, int nproj, const 
   tp.inband = inband == 2 ? 2 : (inband ? 1 : 0);
   TileSrc src;
   int32_t* status;
-  int rc = make_src(plan, ids, T, n_adapters, 0, &src, &status);
+  int rc = make_src(plan, ids, T, n_adapters, flags & SLORA_FLAG_RESOLVED_MASK, &src, &status);
   if (rc) return rc;
   if (T == 0) return SLORA_OK;  // every rank sees the same empty batch and skips the exchange
   void* d[3] = {peer_full[my_part], peer_full[my_part], peer_full[my_part]};  // unused: results go to every rank
@@ -1232,7 +1271,7 @@ int slora_tp_expand_wait(const void* plan, const int64_t* ids, int nproj, const 
     d[p] = static_cast<const char*>(my_full) + ((static_cast<int64_t>(half) * 3 + p) * full_tokens) * R * 2;
   TileSrc src;
   int32_t* status;
-  int rc = make_src(plan, ids, T, n_adapters, 0, &src, &status);
+  int rc = make_src(plan, ids, T, n_adapters, flags & SLORA_FLAG_RESOLVED_MASK, &src, &status);
   if (rc) return rc;
   if (T == 0) return SLORA_OK;
   const Tables tb = make_tables(start, ranks4, loc, n_adapters, loc_len, pool_rows, pool_stride);
@@ -1455,7 +1494,7 @@ int slora_batch_lora_o_noalloc(const int64_t* ids, void* o, int64_t o_stride, in
   // Routing big same-adapter groups to the tensor-core kernels may fork to a library-owned side stream, which is
   // created (stream and events) at first use: not in a call that promises to allocate nothing.  The bit is dropped;
   // such groups run on the CUDA-core kernels here.
-  flags &= ~static_cast<unsigned>(SLORA_FLAG_BIG_GROUPS);
+  flags &= ~static_cast<unsigned>(SLORA_FLAG_BIG_GROUPS | SLORA_FLAG_RESOLVED_MASK);  // its plan has no resolved tiles
   // the plan kernel clears its own counters; the intermediate needs no clearing (only columns < r are written and read)
   rc = slora_plan_build(scratch, kNoAllocPlanBytes, ids, T, start, ranks4, n_adapters, loc_len, stream);
   if (rc) return rc;

@@ -448,13 +448,18 @@ __device__ __forceinline__ ItemMap build_item_map(const TileSrc& src, int padded
   return m;
 }
 
-// The padded enumeration alone: nothing but the tile count is read from the plan.
+// The padded enumeration alone.  Nothing is read from the plan here: the first batch of items is bounded by the tile
+// slots the workspace has (tile_lookup tells which of them hold tiles), so that its loads do not queue behind a
+// load of the tile count; later batches use the count (padded_item_count), which has arrived by then.
 __device__ __forceinline__ ItemMap padded_item_map(const TileSrc& src, int padded_per_tile) {
   ItemMap m;
   m.per_tile = padded_per_tile;
-  m.n_tiles = tile_count(src);
+  m.n_tiles = src.slots;
   m.n_items = static_cast<int64_t>(m.n_tiles) * padded_per_tile;
   return m;
+}
+__device__ __forceinline__ int64_t padded_item_count(const TileSrc& src, int padded_per_tile) {
+  return static_cast<int64_t>(tile_count(src)) * padded_per_tile;
 }
 
 // Item q -> its tile and its index among that tile's items.
@@ -515,7 +520,8 @@ __device__ __forceinline__ void shrink_producer(const ShrinkArgs& a, unsigned ch
                                              [&](int rr, int) { return a.nproj * shrink_blocks_of(a, rr, false); })
                             : padded_item_map(a.src, a.nproj * a.max_rb);
   const int mode = EXACT ? map.mode : 0;
-  const int64_t n_items = map.n_items;
+  int64_t n_items = map.n_items;
+  const int rows_per_pool_row = static_cast<int>(S / h_in);  // the pipelined shrink is given S % h_in == 0
 
   for (int64_t batch0 = blockIdx.x; batch0 < n_items && !r.dead; batch0 += 32 * G) {
     // ---- 32 items resolved in parallel, one per lane; d_i[lane] = {valid, n, nrows, j0, p, -, -, -, tok[8]} ----
@@ -526,6 +532,21 @@ __device__ __forceinline__ void shrink_producer(const ShrinkArgs& a, unsigned ch
       item_to_tile(map, c, item, tile, rem);
       // projection and row block: known before the tile record arrives unless ranks are mixed
       int nb = mode == 0 ? a.max_rb : shrink_blocks_of(a, map.uniform, false);
+      // resolved tiles: where projection and row block follow from the item index alone, the pool rows of the
+      // item are fetched now, together with the header and the record that will say whether they count
+      int spec_row[kMaxRows];
+      bool spec = false;
+      if (a.src.mode == MODE_PLAN && a.src.xoff > 0 && mode != 2) {
+        const int p_s = min(rem / nb, a.nproj - 1), rb_s = rem - (rem / nb) * nb;
+        const int32_t* xt = a.src.plan + a.src.xoff + static_cast<int64_t>(tile) * (kXtHead + 4 * a.src.xrcap);
+        const int qk_s = pick3(a.qkvo, p_s);
+#pragma unroll
+        for (int j = 0; j < kMaxRows; ++j) {
+          const int pr = (rb_s * kMaxRows + j) / rows_per_pool_row;
+          spec_row[j] = xt[kXtHead + qk_s * a.src.xrcap + min(pr, a.src.xrcap - 1)];
+        }
+        spec = true;
+      }
       TileInfo t;
       if (lookup_tile(a.src, a.tb, tile, t, a.status)) {
         const bool wide = mode == 2 && t.n <= kWideTokens;
@@ -536,14 +557,15 @@ __device__ __forceinline__ void shrink_producer(const ShrinkArgs& a, unsigned ch
         const int rows_total = shrink_rows_of(a, t.r);  // A rows of the projection (rows may be shorter than a pool row)
         if (p < a.nproj && j0 < rows_total) {
           const int nrows = min(per, rows_total - j0);
-          const int64_t base = t.loc_base + static_cast<int64_t>(t.r) * pick3(a.qkvo, p);
+          const int qk = pick3(a.qkvo, p);
           bool ok = true;
 #pragma unroll
           for (int j = 0; j < RMAX; ++j) {
             if (j < nrows) {
               const int64_t f = static_cast<int64_t>(j0 + j) * h_in;
               const int64_t pr = f / S, col = f - pr * S;
-              const int64_t e = pr < t.r ? a.tb.loc[base + pr] : -1;
+              int64_t e = -1;
+              if (pr < t.r) e = (spec && t.xok && j < kMaxRows) ? spec_row[j < kMaxRows ? j : 0] : tile_loc(t, a.tb, qk, pr);
               if (e < 0 || e >= a.tb.pool_rows) ok = false;
               pp.d_l[lane][j] = e * S + col;
             }
@@ -611,6 +633,7 @@ __device__ __forceinline__ void shrink_producer(const ShrinkArgs& a, unsigned ch
       }
     }
     __syncwarp();
+    if (!EXACT && a.src.mode == MODE_PLAN) n_items = padded_item_count(a.src, a.nproj * a.max_rb);
   }
   ring_finish(r, c, a.status, lane);
 }
@@ -901,7 +924,7 @@ __device__ __forceinline__ void expand_producer(const ExpandArgs& a, unsigned ch
   const ItemMap map = EXACT ? build_item_map(a.src, total_chunks, c, lane, [&](int rr, int) { return expand_items_of(a, rr); })
                             : padded_item_map(a.src, total_chunks);
   const int mode = EXACT ? map.mode : 0;
-  const int64_t n_items = map.n_items;
+  int64_t n_items = map.n_items;
 
   for (int64_t batch0 = blockIdx.x; batch0 < n_items && !r.dead; batch0 += 32 * G) {
     // d_i[lane] = {pr0, n, r, p, clen, first output, scale bits, chunk start inside pool row pr0, tok[8]},
@@ -925,6 +948,20 @@ __device__ __forceinline__ void expand_producer(const ExpandArgs& a, unsigned ch
       } else if (mode == 1 && rank_ok(map.uniform * a.rank_mult)) {
         split(map.uniform * a.rank_mult);
       }
+      // resolved tiles: where projection and chunk follow from the item index alone, the chunk's pool rows and the
+      // adapter's scale are fetched now, together with the header and the record that will say whether they count
+      int spec_row[kSpanRows], spec_scale = 0;
+      bool spec = false;
+      if (a.src.mode == MODE_PLAN && a.src.xoff > 0 && mode != 2) {
+        const int32_t* xt = a.src.plan + a.src.xoff + static_cast<int64_t>(tile) * (kXtHead + 4 * a.src.xrcap);
+        const int qk_s = pick3(a.qkvo, p);
+        const int pr_s = static_cast<int>(static_cast<int64_t>(ch) * kPipeChunk / S);
+        spec_scale = xt[8];
+#pragma unroll
+        for (int j = 0; j < kSpanRows; ++j)
+          spec_row[j] = xt[kXtHead + qk_s * a.src.xrcap + min(pr_s + j, a.src.xrcap - 1)];
+        spec = true;
+      }
       TileInfo t;
       if (lookup_tile(a.src, a.tb, tile, t, a.status)) {
         const int rk = t.r * a.rank_mult;
@@ -937,14 +974,14 @@ __device__ __forceinline__ void expand_producer(const ExpandArgs& a, unsigned ch
             set_status(a.status, SLORA_STATUS_BAD_RANK);
           } else {
             const int clen = static_cast<int>(min(static_cast<int64_t>(kPipeChunk), flat_total - c0));
-            const int64_t base = t.loc_base + static_cast<int64_t>(t.r) * pick3(a.qkvo, p);
+            const int qk = pick3(a.qkvo, p);
             const int64_t pr0 = c0 / S, pr1 = (c0 + clen - 1) / S;
             bool ok = pr1 - pr0 < kSpanRows && pr1 < t.r;
             if (ok) {
 #pragma unroll
               for (int j = 0; j < kSpanRows; ++j) {
                 if (pr0 + j <= pr1) {
-                  const int64_t e = a.tb.loc[base + pr0 + j];
+                  const int64_t e = (spec && t.xok) ? spec_row[j] : tile_loc(t, a.tb, qk, pr0 + j);
                   if (e < 0 || e >= a.tb.pool_rows) ok = false;
                   pp.d_l[lane][j] = e;
                 }
@@ -959,7 +996,17 @@ __device__ __forceinline__ void expand_producer(const ExpandArgs& a, unsigned ch
               pp.d_i[lane][3] = p;
               pp.d_i[lane][4] = clen;
               pp.d_i[lane][5] = static_cast<int>(c0 / rk);
-              pp.d_i[lane][6] = __float_as_int(to_f32<T>(reinterpret_cast<const T*>(a.scales)[t.adapter]));
+              {
+                // the scale's 16 bits: from the resolved tile when it counts and carries one, else from the table
+                T sc;
+                if (spec && t.xok && (spec_scale & 0x10000)) {
+                  const unsigned short bits = static_cast<unsigned short>(spec_scale & 0xffff);
+                  sc = *reinterpret_cast<const T*>(&bits);
+                } else {
+                  sc = reinterpret_cast<const T*>(a.scales)[t.adapter];
+                }
+                pp.d_i[lane][6] = __float_as_int(to_f32<T>(sc));
+              }
               pp.d_i[lane][7] = static_cast<int>(c0 - pr0 * S);  // chunk start inside its first pool row
               valid = 1;
             } else {
@@ -1033,6 +1080,7 @@ __device__ __forceinline__ void expand_producer(const ExpandArgs& a, unsigned ch
       ring_issue(r, c, slot, ring_base + off + rel, src, bytes, is_act, lane);
     }
     __syncwarp();
+    if (!EXACT && a.src.mode == MODE_PLAN) n_items = padded_item_count(a.src, total_chunks);
   }
   ring_finish(r, c, a.status, lane);
 }

@@ -6,14 +6,17 @@
 namespace slora {
 
 // workspace words: [header PH_WORDS][tile records kTileWords * max_tiles][perm T][pos T][cnt n_adapters]
-//                  [big-tile records kTileWords * max_big]
+//                  [big-tile records kTileWords * max_big][resolved tiles (kXtHead + 4 * xrcap) * max_tiles, optional]
 // Counting sort by adapter id: histogram, exclusive scan over adapters (tokens and tiles at once), scatter.
 // Tokens whose id is outside [0, n_adapters) are left out and SLORA_STATUS_BAD_ID is recorded; adapters whose
 // table entries are out of range get tiles of zero tokens and SLORA_STATUS_BAD_TABLE.
 __global__ void __launch_bounds__(1024) plan_build_kernel(int32_t* ws, const int64_t* __restrict__ ids,
                                                           const int64_t* __restrict__ start,
                                                           const int64_t* __restrict__ ranks4, int64_t loc_len, int T,
-                                                          int n_adapters, int max_tiles, int max_big) {
+                                                          int n_adapters, int max_tiles, int max_big,
+                                                          const int64_t* __restrict__ loc,
+                                                          const unsigned short* __restrict__ scales16, int xoff,
+                                                          int xrcap) {
   int32_t* hdr = ws;
   int32_t* tiles = ws + PH_WORDS;
   int32_t* perm = tiles + kTileWords * max_tiles;
@@ -153,7 +156,39 @@ __global__ void __launch_bounds__(1024) plan_build_kernel(int32_t* ws, const int
     const int p = pos[t];
     if (p >= 0) perm[cnt[ids[t]] + p] = t;
   }
+  // resolved tiles (see PH_XOFF): token ids, scale and pool rows of every tile whose rank the entries hold
+  if (xoff > 0 && loc != nullptr) {
+    __syncthreads();  // tile records and perm are complete
+    const int ntiles = hdr[PH_NTILES];
+    const int ew = kXtHead + 4 * xrcap;
+    for (int tile = tid; tile < ntiles; tile += nthr) {
+      int32_t* rec = tiles + kTileWords * tile;
+      const int a = rec[0], first = rec[1], n = rec[2], r = rec[3];
+      const bool filled = n > 0 && r > 0 && r <= xrcap;
+      rec[6] = filled ? 1 : 0;
+      if (filled) {
+        int32_t* e = ws + xoff + static_cast<int64_t>(tile) * ew;
+        for (int i = 0; i < kTileTokens; ++i) e[i] = i < n ? perm[first + i] : 0;
+        e[8] = scales16 != nullptr ? (0x10000 | scales16[a]) : 0;
+        e[9] = e[10] = e[11] = 0;
+      }
+    }
+    const int per_tile = 4 * xrcap;
+    for (int64_t idx = tid; idx < static_cast<int64_t>(ntiles) * per_tile; idx += nthr) {
+      const int tile = static_cast<int>(idx / per_tile), q = static_cast<int>(idx - static_cast<int64_t>(tile) * per_tile);
+      const int p = q / xrcap, j = q - p * xrcap;
+      const int32_t* rec = tiles + kTileWords * tile;
+      const int n = rec[2], r = rec[3], st = rec[4];
+      if (n > 0 && r > 0 && r <= xrcap && j < r) {
+        const int64_t v = loc[static_cast<int64_t>(st) + static_cast<int64_t>(r) * p + j];
+        ws[xoff + static_cast<int64_t>(tile) * ew + kXtHead + p * xrcap + j] =
+            (v >= 0 && v < 0x7fffffffLL) ? static_cast<int32_t>(v) : -1;
+      }
+    }
+  }
   if (tid == 0) {
+    hdr[PH_XOFF] = (xoff > 0 && loc != nullptr) ? xoff : 0;
+    hdr[PH_XRCAP] = (xoff > 0 && loc != nullptr) ? xrcap : 0;
     hdr[PH_MAGIC] = kPlanMagic;
     hdr[PH_STATUS] = s_status;
     hdr[PH_MAXTILES] = max_tiles;

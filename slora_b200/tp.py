@@ -260,8 +260,9 @@ class CudaBackend:
         13B-shaped batch per layer: 52.3 against 57.7 us at N = 8, but 86.5 against 77.4 at N = 4)."""
         from . import _lib
         from .batch_infer import BatchPlan
-        plan = BatchPlan(ids, t.a_start, t.a_len, t.a_loc.numel())
-        self.flags = self.base_flags
+        plan = BatchPlan(ids, t.a_start, t.a_len, t.a_loc.numel(), a_loc=t.a_loc, a_scaling=t.a_scaling,
+                         max_rank=int(local_width or 0))
+        self.flags = self.base_flags | plan.flags
         if ids.numel() >= 128 and (local_width is None or local_width > 8) and plan.info()[2] == 0:
             self.flags |= _lib.FLAG_EXACT_ITEMS
         return plan

@@ -40,6 +40,12 @@ def test_version_and_workspace_size():
     # header + tiles + perm + pos + counters
     assert small >= 4 * (16 + 8 * (32 + 256) + 2 * 256 + 1000)
     assert _lib.lib.slora_plan_workspace_bytes(-1, 5) == 0
+    # resolved tiles: 12 + 4 * cap words per tile slot on top, cap = max_rank rounded up to a multiple of 8
+    assert _lib.lib.slora_plan_workspace_bytes_ex(256, 1000, 0) == small
+    with_tiles = _lib.lib.slora_plan_workspace_bytes_ex(256, 1000, 12)
+    assert with_tiles >= small + 4 * (32 + 256) * (12 + 4 * 16) and with_tiles - small < 4 * (32 + 256) * (12 + 4 * 16) + 64
+    assert _lib.lib.slora_plan_workspace_bytes_ex(256, 1000, 129) == small      # beyond the cap: none
+    assert _lib.flag_resolved(12) == 2 << 8 and _lib.flag_resolved(0) == 0 and _lib.flag_resolved(128) == 16 << 8
 
 
 def test_argument_validation_needs_no_device():

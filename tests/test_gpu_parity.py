@@ -390,3 +390,56 @@ def test_against_outputs_of_the_reference_kernels(case):
         assert (deltas[p].float().cpu() - ref_d).abs().max() <= 2e-3 * ref_d.abs().max()
         assert_parity(outs[p][:, mod.cols_of(wl.spec.hidden)], g[f"{case}_y_p{p}"].astype(np.float32), what=f"ref kernels {case} p{p}")
 
+
+
+@pytest.mark.parametrize("case", ["same_rank", "mixed_ranks", "cap_below_some_ranks", "flag_without_tiles", "bf16_gqa"])
+def test_resolved_tiles_give_the_same_bits_as_the_table_chase(case):
+    """A plan built with the loc table (slora_plan_build_ex) holds every tile's token ids, scale and pool rows where a
+    launch fetches them in one round trip; the kernels fall back to perm and the tables per tile (rank above the
+    plan's cap) or altogether (the flag says resolved tiles, the plan has none).  Same bits every way."""
+    from slora_b200 import _lib
+    dt = torch.float16
+    if case == "same_rank":
+        wl = build_workload(2, pool_rows=16384, n_adapters=300)
+    elif case == "bf16_gqa":
+        dt = torch.bfloat16
+        wl = build_workload(5, dtype=dt, pool_rows=8192, n_adapters=40, decode_tokens=200, hidden=4096, h_kv=1024,
+                            rank_choices=(8, 32, 64))
+    else:
+        wl = build_workload(3, pool_rows=16384, n_adapters=60, decode_tokens=150, prefill=("seqs", 3, 5, 40), hidden=4096)
+    w = wl.to(DEV)
+    R = w.max_rank
+    mask = 0x1f << 8
+
+    def run(plan_kw, flag_rank, exact):
+        ops = sl.LoraBatchOps(w.a_start, w.a_len, w.a_loc, w.a_scaling, w.pools_a, w.pools_b, R)
+        ops.prepare(w.ids, mixed_ranks=exact, big_groups=False)
+        ops.plan = sl.BatchPlan(w.ids, w.a_start, w.a_len, w.a_loc.numel(), **plan_kw)
+        ops.flags = (ops.flags & ~mask) | _lib.flag_resolved(flag_rank)
+        H, K = w.spec.hidden, w.spec.h_kv
+        out = [torch.zeros((w.T, n), dtype=dt, device=DEV) for n in (H, K, K, H)]
+        ops.lora_get_qkv(0, w.x_qkv[0], out[0], out[1], out[2])
+        ops.lora_get_o(0, w.x_o[0], out[3])
+        torch.cuda.synchronize()
+        ops.plan.check()
+        return out, ops.plan.header()
+
+    tables = dict(a_loc=w.a_loc, a_scaling=w.a_scaling)
+    for exact in (False, True):
+        chase, _ = run({}, 0, exact)
+        if case == "cap_below_some_ranks":
+            got, hdr = run(dict(max_rank=16, **tables), 16, exact)
+            assert hdr["resolved_cap"] == 16 and max(wl.ranks) > 16
+        elif case == "flag_without_tiles":
+            n = _lib.lib.slora_plan_workspace_bytes_ex(w.T, w.a_start.numel(), R)
+            ws = torch.empty(n // 4 + 1, dtype=torch.int32, device=DEV)
+            got, hdr = run(dict(workspace=ws), R, exact)
+            assert hdr["resolved_cap"] == 0
+        else:
+            got, hdr = run(dict(max_rank=R, **tables), R, exact)
+            assert hdr["resolved_cap"] == R
+        for p in range(4):
+            assert torch.equal(chase[p], got[p]), f"{case} exact={exact} proj {p}"
+    ref = oracle_layer(wl)
+    for p in range(4):
+        assert_parity(got[p], ref[p], dt, what=f"resolved tiles {case} proj {p}")
