@@ -173,16 +173,32 @@ __global__ void __launch_bounds__(1024) plan_build_kernel(int32_t* ws, const int
         e[9] = e[10] = e[11] = 0;
       }
     }
+    // pool rows: one (tile, projection, row) per thread and step, four steps in flight (32-bit index arithmetic; the
+    // table loads of a round are issued before any of them is used)
     const int per_tile = 4 * xrcap;
-    for (int64_t idx = tid; idx < static_cast<int64_t>(ntiles) * per_tile; idx += nthr) {
-      const int tile = static_cast<int>(idx / per_tile), q = static_cast<int>(idx - static_cast<int64_t>(tile) * per_tile);
-      const int p = q / xrcap, j = q - p * xrcap;
-      const int32_t* rec = tiles + kTileWords * tile;
-      const int n = rec[2], r = rec[3], st = rec[4];
-      if (n > 0 && r > 0 && r <= xrcap && j < r) {
-        const int64_t v = loc[static_cast<int64_t>(st) + static_cast<int64_t>(r) * p + j];
-        ws[xoff + static_cast<int64_t>(tile) * ew + kXtHead + p * xrcap + j] =
-            (v >= 0 && v < 0x7fffffffLL) ? static_cast<int32_t>(v) : -1;
+    const int total = ntiles * per_tile;  // at most a few hundred thousand
+    for (int idx0 = tid; idx0 < total; idx0 += 4 * nthr) {
+      int64_t v[4];
+      int dst[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int idx = idx0 + u * nthr;
+        dst[u] = -1;
+        v[u] = -1;
+        if (idx < total) {
+          const int tile = idx / per_tile, q = idx - tile * per_tile;
+          const int p = q / xrcap, j = q - p * xrcap;
+          const int4 rec0 = *reinterpret_cast<const int4*>(tiles + kTileWords * tile);
+          const int st = tiles[kTileWords * tile + 4];
+          if (rec0.z > 0 && rec0.w > 0 && rec0.w <= xrcap && j < rec0.w) {
+            v[u] = loc[static_cast<int64_t>(st) + static_cast<int64_t>(rec0.w) * p + j];
+            dst[u] = xoff + tile * ew + kXtHead + p * xrcap + j;
+          }
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        if (dst[u] >= 0) ws[dst[u]] = (v[u] >= 0 && v[u] < 0x7fffffffLL) ? static_cast<int32_t>(v[u]) : -1;
       }
     }
   }
