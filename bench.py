@@ -92,6 +92,10 @@ def parse_args(argv=None):
     ap.add_argument("--rope", action="store_true",
                     help="secondary line: rotary embedding and KV-pool scatter in the q/k/v expand's epilogue against "
                          "the same two steps as a pass of their own (configuration 2)")
+    ap.add_argument("--warm-outputs", action="store_true",
+                    help="secondary line: the step with the outputs written just before every call (as the base "
+                         "projection's epilogue leaves them, in L2) against the step on cold outputs: what writing "
+                         "y = xW + delta from one kernel could save at most")
     ap.add_argument("--scheduler", action="store_true",
                     help="secondary line: what the adapter-clustering request queue is worth on the LoRA path "
                          "(bench_sched.py)")
@@ -810,6 +814,52 @@ def rope_bench(args, device, peak):
     return line
 
 
+def warm_outputs_bench(args, device, peak):
+    """Upper bound of what a fused base projection + delta kernel would save: in the reference's layer the base
+    torch.mm writes y right before the LoRA calls read it, so y is in the 126 MB L2, not in HBM.  Per layer: the LoRA
+    step on outputs nobody touched since the previous pass over the physical layers (the main benchmark's setting:
+    y read from HBM); the same step with a fill of q, k, v (and o) issued before each call, minus the fills alone."""
+    import slora_b200 as sl
+    from slora_b200.workloads import build_workload
+    cfg = args.config if args.config in (2, 4) else 2
+    P = phys_layers_for(args, cfg)
+    wl = build_workload(cfg, device=device, phys_layers=P, pool_rows=args.pool_rows)
+    L, T, H, K = args.layers or wl.spec.layers, wl.T, wl.spec.hidden, wl.spec.h_kv
+    dt = wl.dtype
+    ops = sl.LoraBatchOps(wl.a_start, wl.a_len, wl.a_loc, wl.a_scaling, wl.pools_a, wl.pools_b, wl.max_rank,
+                          use_pdl=not args.no_pdl)
+    ops.prepare(wl.ids)
+    q = [torch.zeros((T, H), dtype=dt, device=device) for _ in range(P)]
+    k = [torch.zeros((T, K), dtype=dt, device=device) for _ in range(P)]
+    v = [torch.zeros((T, K), dtype=dt, device=device) for _ in range(P)]
+    o = [torch.zeros((T, H), dtype=dt, device=device) for _ in range(P)]
+
+    # A kernel of another library between the calls (here a fill, in the reference's layer the base projection and
+    # the attention) also ends the chain of programmatic dependent launches, so both settings get one: a fill of the
+    # whole output ("warm": y is in L2 when the call reads it) or of one element of it ("cold").
+    def step(lora, whole):
+        for l in range(L):
+            p = l % P
+            for t in (q[p], k[p], v[p]):
+                (t if whole else t[:1, :8]).fill_(0.5)
+            if lora:
+                ops.lora_get_qkv(p, wl.x_qkv[p], q[p], k[p], v[p])
+            (o[p] if whole else o[p][:1, :8]).fill_(0.5)
+            if lora:
+                ops.lora_get_o(p, wl.x_o[p], o[p])
+
+    cold = _graph_time(lambda: step(True, False), L) - _graph_time(lambda: step(False, False), L)
+    both = _graph_time(lambda: step(True, True), L)
+    fills = _graph_time(lambda: step(False, True), L)
+    y_bytes = T * (2 * H + 2 * K) * 2
+    return {"metric": "lora_step_with_outputs_in_l2", "unit": "us per layer", "workload": wl.spec.name, "layers": L,
+            "tokens": T, "cold_outputs_us": cold, "fills_then_lora_us": both, "fills_alone_us": fills,
+            "warm_outputs_us": both - fills, "value": cold - (both - fills),
+            "value_is": "us per layer that reading y from L2 instead of HBM saves: the most a fused base projection "
+                        "+ delta kernel could add on top of what the L2 already gives",
+            "y_bytes_per_layer": y_bytes, "y_read_at_measured_hbm_peak_us": y_bytes / peak[0] / 1e3}
+
+
 def main():
     args = parse_args()
     if args.impl == "reference":
@@ -841,6 +891,10 @@ def main():
     if args.rope:
         if rank == 0:
             print(json.dumps(rope_bench(args, device, peak)), flush=True)
+        return
+    if args.warm_outputs:
+        if rank == 0:
+            print(json.dumps(warm_outputs_bench(args, device, peak)), flush=True)
         return
     if args.scheduler:
         import bench_sched
