@@ -93,7 +93,9 @@ def tp_parity(ops, wl, world, rank, dist, q, k, v, o, o_rule):
         be.shrink_push(ops.px, ops.plan, ops.ids, [0, 1, 2], wl.x_qkv[0], wl.pools_a[0], t, Rl, 0)
         torch.cuda.synchronize()
         dist.barrier()
-        full = ops.px.full[0][:, :T].clone()          # [3, T, R] as this rank's expand is about to read it
+        # (rotating thirds: the shrink left the exchange's number, which picks the part, for its expand)
+        part = int(ops.px.inband_seq[1].item()) % 3 if ops.px.inband == 3 else 0
+        full = ops.px.full[part][:, :T].clone()       # [3, T, R] as this rank's expand is about to read it
         be.expand_wait(ops.px, ops.plan, ops.ids, [0, 1, 2], [q, k, v], wl.pools_b[0], t, Rl, 0)
     else:
         ops.lora_qkv(0, wl.x_qkv[0], q, k, v)

@@ -107,6 +107,15 @@ struct TpLink {
                //    recognised like the peers'.  The shrink then lets its dependents launch only after its own
                //    grid-dependency wait, so what came before the shrink (the base projection that wrote y) is
                //    complete before a CTA of the expand exists, and every CTA of the shrink is running by then.
+               // 3: early start over rotating thirds.  The buffers hold three parts instead of two halves; exchange
+               //    number e (kept on the device: seq_state[0] is read by a shrink after its grid-dependency wait,
+               //    seq_state[1] is left by that shrink for its expand, which writes e + 1 back for the next
+               //    shrink) works in part e % 3, and its SHRINK refills - spread over all CTAs, on this GPU's own
+               //    buffer - the part that exchange e - 1 used, whose expand on this GPU is complete by then.  No
+               //    arrival counter and no refill at the end of an expand.  A peer writes into that part again in
+               //    exchange e + 2, i.e. after it has received all of this GPU's values of exchange e + 1, whose
+               //    shrink starts writing after this GPU's expand e, which follows shrink e in stream order: the
+               //    refill is a whole kernel ahead of the next write.  `half` is not used.
 };
 
 struct ShrinkArgs {

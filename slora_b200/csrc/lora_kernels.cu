@@ -1232,7 +1232,7 @@ int slora_tp_shrink_push(const void* plan, const int64_t* ids, int nproj, const 
   tp.my_part = my_part;
   tp.n_parts = n_parts;
   tp.half = half;
-  tp.inband = inband == 2 ? 2 : (inband ? 1 : 0);
+  tp.inband = (inband == 2 || inband == 3) ? inband : (inband ? 1 : 0);
   TileSrc src;
   int32_t* status;
   int rc = make_src(plan, ids, T, n_adapters, flags & SLORA_FLAG_RESOLVED_MASK, &src, &status);
@@ -1264,11 +1264,12 @@ int slora_tp_expand_wait(const void* plan, const int64_t* ids, int nproj, const 
   tp.my_part = my_part;
   tp.n_parts = n_parts;
   tp.half = half;
-  tp.inband = inband == 2 ? 2 : (inband ? 1 : 0);
+  tp.inband = (inband == 2 || inband == 3) ? inband : (inband ? 1 : 0);
   const int R = n_parts * part_width;
   const void* d[3];
+  const int first = inband == 3 ? 0 : half;  // rotating thirds: the kernel adds the exchange's part itself
   for (int p = 0; p < 3; ++p)
-    d[p] = static_cast<const char*>(my_full) + ((static_cast<int64_t>(half) * 3 + p) * full_tokens) * R * 2;
+    d[p] = static_cast<const char*>(my_full) + ((static_cast<int64_t>(first) * 3 + p) * full_tokens) * R * 2;
   TileSrc src;
   int32_t* status;
   int rc = make_src(plan, ids, T, n_adapters, flags & SLORA_FLAG_RESOLVED_MASK, &src, &status);

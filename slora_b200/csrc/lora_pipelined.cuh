@@ -514,7 +514,7 @@ __device__ __forceinline__ void shrink_producer(const ShrinkArgs& a, unsigned ch
   PipeCtl::Prod& pp = c.prod[role];
   Ring r;
   r.role = role;
-  r.trigger_after_wait = a.tp.enabled && a.tp.inband == 2;
+  r.trigger_after_wait = a.tp.enabled && a.tp.inband >= 2;
   constexpr int RMAX = EXACT ? kWideRows : kMaxRows;  // rows of the widest item = lane of the first token row
   const ItemMap map = EXACT ? build_item_map(a.src, a.nproj * a.max_rb, c, lane,
                                              [&](int rr, int) { return a.nproj * shrink_blocks_of(a, rr, false); })
@@ -723,7 +723,27 @@ template <typename T, bool EXACT>
 __device__ __forceinline__ void shrink_consumer(const ShrinkArgs& a, const unsigned char* ring_mem, PipeCtl& c,
                                                 ShrinkRed& red, int lane, int cw) {
   pdl_wait();
-  if (a.tp.enabled && a.tp.inband == 2) pdl_launch_dependents();
+  int tp_slot = a.tp.half;  // which part of every rank's delta buffer this exchange writes
+  if (a.tp.enabled && a.tp.inband == 3) {
+    // rotating thirds (see TpLink::inband): the exchange's number picks the third; this CTA's share of the third
+    // the PREVIOUS exchange used - whose expand on this GPU is complete: it is what the wait above waited for - goes
+    // back to the empty pattern; one thread tells this exchange's expand its number
+    const int e = *reinterpret_cast<volatile const int32_t*>(a.tp.seq_state);
+    tp_slot = e % 3;
+    const int64_t third = 3 * a.tp.full_tokens * static_cast<int64_t>(a.tp.n_parts) * a.delta_width;  // elements
+    uint4* prev = reinterpret_cast<uint4*>(reinterpret_cast<T*>(a.tp.full[a.tp.my_part]) + ((e + 2) % 3) * third);
+    const int64_t n16 = third * static_cast<int64_t>(sizeof(T)) / 16;
+    const uint4 ev = make_uint4(kTpEmpty2, kTpEmpty2, kTpEmpty2, kTpEmpty2);
+    for (int64_t i = static_cast<int64_t>(blockIdx.x) * (kConsumerWarps * 32) + cw * 32 + lane; i < n16;
+         i += static_cast<int64_t>(gridDim.x) * (kConsumerWarps * 32))
+      prev[i] = ev;
+    if (blockIdx.x == 0 && cw == 0 && lane == 0) {
+      a.tp.seq_state[1] = e;
+      __threadfence();  // before this thread lets dependents launch
+    }
+    __syncwarp();
+  }
+  if (a.tp.enabled && a.tp.inband >= 2) pdl_launch_dependents();
   float acc[kMaxRows][kTileTokens];
 #pragma unroll
   for (int j = 0; j < kMaxRows; ++j) {
@@ -814,7 +834,7 @@ __device__ __forceinline__ void shrink_consumer(const ShrinkArgs& a, const unsig
             if (a.tp.enabled) {
               // tensor parallelism: this rank's rows go straight into every rank's delta buffer (NVLink stores)
               const int64_t R = static_cast<int64_t>(a.tp.n_parts) * a.delta_width;
-              const int64_t at = ((static_cast<int64_t>(a.tp.half) * 3 + m[4]) * a.tp.full_tokens + m[8 + i]) * R +
+              const int64_t at = ((static_cast<int64_t>(tp_slot) * 3 + m[4]) * a.tp.full_tokens + m[8 + i]) * R +
                                  static_cast<int64_t>(a.tp.my_part) * m[7] + m[3] + j;
               const T v = from_f32<T>(sum);
               for (int g = 0; g < a.tp.n_parts; ++g) reinterpret_cast<T*>(a.tp.full[g])[at] = v;
@@ -867,7 +887,7 @@ __global__ void __launch_bounds__(kPipeThreads, kPipeCtasPerSm) lora_shrink_pipe
   pipe_init(ctl, tid);
   // (a shrink whose expand starts early lets its dependents launch only after its own grid-dependency wait, thread
   // by thread: see TpLink::inband)
-  if (!(a.tp.enabled && a.tp.inband == 2)) pdl_launch_dependents();
+  if (!(a.tp.enabled && a.tp.inband >= 2)) pdl_launch_dependents();
   if (EXACT) {
     fill_item_counts(a.src, a.tb, ctl, tid, [&](int rr, int n) { return shrink_items_of(a, rr, n); });
     __syncthreads();
@@ -918,7 +938,13 @@ __device__ __forceinline__ void expand_producer(const ExpandArgs& a, unsigned ch
   r.cap = EXACT ? kExpandRingBytes : kRingBytes;  // see kExpandRingBytes
   r.tp = a.tp.enabled ? &a.tp : nullptr;
   r.status = a.status;
-  if (a.tp.enabled && a.tp.inband == 2) r.pre = false;  // early start: nothing to wait for (see TpLink::inband)
+  if (a.tp.enabled && a.tp.inband >= 2) r.pre = false;  // early start: nothing to wait for (see TpLink::inband)
+  int64_t delta_off = 0;  // rotating thirds: elements from the first third to this exchange's
+  if (a.tp.enabled && a.tp.inband == 3) {
+    const int e = *reinterpret_cast<volatile const int32_t*>(a.tp.seq_state + 1);  // left by this exchange's shrink
+    delta_off = (e % 3) * 3 * a.tp.full_tokens * a.delta_stride;
+    if (blockIdx.x == 0 && lane == 0) a.tp.seq_state[0] = e + 1;  // the next shrink reads it after its own wait
+  }
   auto rank_ok = [&](int rk) { return expand_rank_ok(a, rk); };
   auto chunks_of = [&](int p, int rk) { return expand_chunks_of(a, p, rk); };
   const ItemMap map = EXACT ? build_item_map(a.src, total_chunks, c, lane, [&](int rr, int) { return expand_items_of(a, rr); })
@@ -1051,7 +1077,7 @@ __device__ __forceinline__ void expand_producer(const ExpandArgs& a, unsigned ch
         bytes = y_bytes;
         is_act = true;
       } else if (lane >= 24 && lane < 24 + n) {
-        src = reinterpret_cast<const T*>(pick3(a.delta, p)) + static_cast<int64_t>(mytok) * a.delta_stride;
+        src = reinterpret_cast<const T*>(pick3(a.delta, p)) + delta_off + static_cast<int64_t>(mytok) * a.delta_stride;
         rel = b_bytes + static_cast<uint32_t>(n) * y_bytes + static_cast<uint32_t>(lane - 24) * d_bytes;
         bytes = d_bytes;
         is_act = true;
@@ -1186,7 +1212,11 @@ __device__ __forceinline__ void expand_stage(const T* bs, const int* m, T* y, in
 template <typename T, bool INBAND>
 __device__ __forceinline__ void expand_consumer(const ExpandArgs& a, const unsigned char* ring_mem, PipeCtl& c,
                                                 int lane, int cw) {
-  if (!(a.tp.enabled && a.tp.inband == 2)) pdl_wait();
+  if (!(a.tp.enabled && a.tp.inband >= 2)) pdl_wait();
+  int64_t delta_off = 0;
+  if (INBAND && a.tp.inband == 3)
+    delta_off = (*reinterpret_cast<volatile const int32_t*>(a.tp.seq_state + 1) % 3) * 3 * a.tp.full_tokens *
+                a.delta_stride;
   for (uint32_t g = 0;; ++g) {
     const uint32_t slot = g % kSlots;
     if (!mbar_wait_timed(&c.full[slot], (g / kSlots) & 1)) {
@@ -1199,7 +1229,7 @@ __device__ __forceinline__ void expand_consumer(const ExpandArgs& a, const unsig
     const int p = m[3];
     T* y = reinterpret_cast<T*>(pick3(a.y, p));
     const int64_t ystr = pick3(a.y_stride, p);
-    const T* dg = INBAND ? reinterpret_cast<const T*>(pick3(a.delta, p)) : nullptr;
+    const T* dg = INBAND ? reinterpret_cast<const T*>(pick3(a.delta, p)) + delta_off : nullptr;
     const int64_t dgs = a.delta_stride;
     if (m[4] == kPipeChunk) {  // complete chunk: no bounds checks
       switch (m[2]) {
@@ -1242,7 +1272,7 @@ __global__ void __launch_bounds__(kPipeThreads, kPipeCtasPerSm) lora_expand_pipe
   } else {
     expand_consumer<T, INBAND>(a, ring_mem, ctl, lane, warp - kProducerWarps);
   }
-  if (a.tp.enabled) {
+  if (a.tp.enabled && a.tp.inband != 3) {  // (rotating thirds: nothing to do at the end of an expand)
     if (INBAND) {
       // what this exchange used of its half of the delta buffer: [nproj][full_tokens][delta_stride] elements from
       // delta[0] on

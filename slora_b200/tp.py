@@ -89,7 +89,8 @@ class PeerExchange:
         import torch.distributed._symmetric_memory as symm_mem
         group = group or dist.group.WORLD
         self.world, self.rank = world, rank
-        self.full = symm_mem.empty((2, 3, max(T, 1), R), dtype=dtype, device=device)
+        # two halves (q,k,v calls / o calls), or three parts that rotate with the exchange's number (inband == 3)
+        self.full = symm_mem.empty((3 if inband == 3 else 2, 3, max(T, 1), R), dtype=dtype, device=device)
         self.flags = symm_mem.empty((2, world), dtype=torch.int32, device=device)
         self.parts = symm_mem.empty((world, max(T, 1), R), dtype=dtype, device=device)  # partial sums of the o shrink
         # in-band signalling of the fused exchange: an element that has not arrived yet is the bit pattern 0xffff
@@ -109,6 +110,8 @@ class PeerExchange:
         self._handles = (h_full, h_flags, h_parts)
         self.counter = torch.zeros(4, dtype=torch.int32, device=device)   # one arrival counter per entry point
         self.seq_state = torch.zeros(2, dtype=torch.int32, device=device)   # exchanges done per half (device-kept)
+        # rotating thirds: [0] the next exchange's number (read by its shrink), [1] left by a shrink for its expand
+        self.inband_seq = torch.zeros(2, dtype=torch.int32, device=device)
         torch.cuda.synchronize(device)
         dist.barrier(group=group)   # nobody signals before everybody's flags are zero
 
@@ -249,8 +252,9 @@ class CudaBackend:
         self.fused = fused   # with a PeerExchange: push from the shrink / wait in the expand, no exchange launch
         # fused exchange without flags: the expand recognises values that have not arrived (1); 2: and it does not
         # wait for this GPU's own shrink either (see TpLink::inband in csrc/lora_common.cuh)
-        if inband and use_pdl and os.environ.get("SLORA_TP_EARLY", "1") != "0":
-            inband = 2
+        # 3: early start over rotating thirds (no bookkeeping at the end of an expand)
+        if inband is True and use_pdl:
+            inband = {"0": 1, "2": 2}.get(os.environ.get("SLORA_TP_EARLY", "3"), 3)
         self.inband = int(inband)
 
     def make_plan(self, ids, t, local_width=None):
@@ -319,8 +323,9 @@ class CudaBackend:
             0 if plan is None else plan.ptr, ids.data_ptr(), n, (ctypes.c_int * n)(*qkvo), part_width, x.data_ptr(),
             x.stride(0), x.size(1), pool_a.data_ptr(), pool_a.size(0), pool_a.stride(0), t.a_start.data_ptr(),
             t.a_len.data_ptr(), t.a_loc.data_ptr(), t.a_start.numel(), t.a_loc.numel(), ids.numel(), px.full_ptrs,
-            px.flag_ptrs, px.counter.data_ptr(), px.seq_state.data_ptr(), px.rank, px.world, half, px.full.shape[2],
-            int(px.inband), _lib.dtype_code(x.dtype), self.flags, _lib.current_stream_ptr()))
+            px.flag_ptrs, px.counter.data_ptr(), self._seq(px).data_ptr(), px.rank, px.world,
+            0 if px.inband == 3 else half, px.full.shape[2], int(px.inband), _lib.dtype_code(x.dtype), self.flags,
+            _lib.current_stream_ptr()))
 
     def expand_wait(self, px, plan, ids, qkvo, ys, pool_b, t, part_width, half):
         """Expand that waits for every rank's flag, then reads this rank's buffer (``slora_tp_expand_wait``)."""
@@ -333,8 +338,13 @@ class CudaBackend:
             (ctypes.c_int * n)(*[y.size(1) for y in ys]), pool_b.data_ptr(), pool_b.size(0), pool_b.stride(0),
             t.a_start.data_ptr(), t.a_len.data_ptr(), t.a_loc.data_ptr(), t.a_scaling.data_ptr(), t.a_start.numel(),
             t.a_loc.numel(), ids.numel(), px.full.data_ptr(), px.flags.data_ptr(), px.counter.data_ptr() + 4,
-            px.seq_state.data_ptr(), px.rank, px.world, half, px.full.shape[2], part_width,
+            self._seq(px).data_ptr(), px.rank, px.world, 0 if px.inband == 3 else half, px.full.shape[2], part_width,
             int(px.inband), _lib.dtype_code(ys[0].dtype), self.flags, _lib.current_stream_ptr()))
+
+    @staticmethod
+    def _seq(px):
+        """The device-kept sequence words a fused exchange uses (rotating thirds have their own)."""
+        return px.inband_seq if px.inband == 3 else px.seq_state
 
     def expand(self, plan, ids, qkvo, ys, deltas, pool_b, t, **kw):
         from .batch_infer import expand_multi

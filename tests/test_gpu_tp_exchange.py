@@ -172,7 +172,8 @@ class _EmulatedPeers:
     """What CudaBackend reads of a PeerExchange, for N ranks that all live on one GPU (plain device tensors)."""
 
     def __init__(self, N, cap, R, inband):
-        self.fulls = [torch.zeros((2, 3, cap, R), dtype=torch.float16, device=DEV) for _ in range(N)]
+        self.fulls = [torch.zeros((3 if inband == 3 else 2, 3, cap, R), dtype=torch.float16, device=DEV)
+                      for _ in range(N)]
         if inband:
             for f in self.fulls:
                 f.view(torch.int16).fill_(-1)
@@ -187,17 +188,19 @@ class _EmulatedPeers:
         px.flag_ptrs = (ctypes.c_void_p * N)(*[f.data_ptr() for f in self.flagss])
         px.counter = torch.zeros(4, dtype=torch.int32, device=DEV)
         px.seq_state = torch.zeros(2, dtype=torch.int32, device=DEV)
+        px.inband_seq = torch.zeros(2, dtype=torch.int32, device=DEV)
         px.rank, px.world, px.inband = r, N, self.inband
         return px
 
 
-@pytest.mark.parametrize("inband", [2, True, False])
+@pytest.mark.parametrize("inband", [3, 2, True, False])
 @pytest.mark.parametrize("T", [40, 200])
 def test_fused_exchange_emulated_on_one_gpu(T, inband):
     """slora_tp_shrink_push / slora_tp_expand_wait, four ranks emulated on one GPU: every rank's shrink stores its rows
     into every rank's buffer; every rank's expand then finds them there (in-band signalling: none of the values it
-    uses is the empty pattern any more, and its last CTA refills the half; else: every rank's flag is up).  Three
-    exchanges (q,k,v; o; q,k,v again) against the formula."""
+    uses is the empty pattern any more, and its last CTA refills the half - or, with rotating thirds (3), the next
+    exchange's shrink refills the part; else: every rank's flag is up).  Five exchanges (q,k,v and o alternating, so
+    that the thirds wrap around) against the formula."""
     H, N = 4096, 4
     ranks = [8, 16, 32, 8]
     g = torch.Generator().manual_seed(23)
@@ -221,14 +224,14 @@ def test_fused_exchange_emulated_on_one_gpu(T, inband):
         shards.append((t, pa.to(DEV), pb.to(DEV)))
     peers = _EmulatedPeers(N, T, R, inband)
     pxs = [peers.rank(r) for r in range(N)]
-    # (inband == 2: the expand does not wait for its own GPU's shrink either; chained as programmatic dependents)
-    be = tp.CudaBackend(use_pdl=inband == 2)
+    # (inband >= 2: the expand does not wait for its own GPU's shrink either; chained as programmatic dependents)
+    be = tp.CudaBackend(use_pdl=inband in (2, 3), inband=inband)
     xd, idd = x.to(DEV), ids.to(DEV)
     plans = [be.make_plan(idd, t) for t, _, _ in shards]
     want = [torch.stack([(x[i].float() @ ads[int(ids[i])][0][p].half().float().T)
                          @ ads[int(ids[i])][1][p].half().float().T * (16.0 / ranks[int(ids[i])]) for i in range(T)])
             for p in range(4)]
-    for qkvo, half in (([0, 1, 2], 0), ([3], 1), ([0, 1, 2], 0)):
+    for n_done, (qkvo, half) in enumerate((([0, 1, 2], 0), ([3], 1), ([0, 1, 2], 0), ([3], 1), ([0, 1, 2], 0))):
         for rank, (t, pa, pb) in enumerate(shards):
             be.shrink_push(pxs[rank], plans[rank], idd, qkvo, xd, pa, t, Rl, half)
         ys = []
@@ -239,7 +242,11 @@ def test_fused_exchange_emulated_on_one_gpu(T, inband):
         torch.cuda.synchronize()
         for rank in range(N):
             plans[rank].check()
-            if inband:      # the consumed half is empty again
+            if inband == 3:    # the sequence words moved on; the part of the exchange before this one is empty again
+                assert pxs[rank].inband_seq.tolist() == [n_done + 1, n_done]
+                if n_done > 0:
+                    assert bool((peers.fulls[rank][(n_done - 1) % 3].view(torch.int16) == -1).all())
+            elif inband:       # the consumed half is empty again
                 assert bool((peers.fulls[rank][half].view(torch.int16) == -1).all())
         for j, p in enumerate(qkvo):
             got = torch.cat([ys[rank][j] for rank in range(N)], dim=1)
@@ -323,11 +330,17 @@ def _worker(rank, world, port, result_dir):
                     torch.tensor([16.0 / r for r in ranks], dtype=torch.float16, device=dev))
     outs = {}
     # peer memory from inside the shrink / expand kernels; one exchange kernel; NCCL all-gather + regroup
-    for kind, (peer, fused) in {"fused": (True, True), "kernel": (True, False), "nccl": (False, False)}.items():
-        ops = tp.TpLoraOps(t, [pa.to(dev)], [pb.to(dev)], max(ranks), world, rank, tp.CudaBackend(fused=fused),
+    # ("fused_early": chained as programmatic dependents, the expand starts without waiting for this GPU's shrink
+    # and the delta buffers rotate through three parts - what the benchmark runs)
+    kinds = {"fused": (True, True, False), "fused_early": (True, True, True), "kernel": (True, False, False),
+             "nccl": (False, False, False)}
+    for kind, (peer, fused, pdl) in kinds.items():
+        be = tp.CudaBackend(use_pdl=pdl, fused=fused)
+        assert be.inband == (3 if pdl else 1)
+        ops = tp.TpLoraOps(t, [pa.to(dev)], [pb.to(dev)], max(ranks), world, rank, be,
                            peer_exchange=peer).prepare(ids.to(dev))
         before = sl.launch_counts()
-        for rep in range(3):                    # several layers' worth of exchanges on both buffer halves
+        for rep in range(4):                    # several layers' worth of exchanges on every part of the buffers
             q, k, v, o = (torch.zeros((T, H // world), dtype=torch.float16, device=dev) for _ in range(4))
             ops.lora_qkv(0, x.to(dev), q, k, v)
             ops.lora_o(0, x.to(dev), o)
@@ -335,10 +348,11 @@ def _worker(rank, world, port, result_dir):
         ops.plan.check()
         outs[kind] = torch.stack([q, k, v, o]).cpu()
         after = sl.launch_counts()
-        if kind == "fused":                     # two launches per call and nothing else: no exchange kernel, no fallback
-            assert after["pipelined"] - before["pipelined"] == 3 * 4 and after["simple"] == before["simple"]
+        if kind.startswith("fused"):            # two launches per call and nothing else: no exchange kernel, no fallback
+            assert after["pipelined"] - before["pipelined"] == 4 * 4 and after["simple"] == before["simple"]
             assert after["plan"] == before["plan"]
     assert torch.equal(outs["fused"], outs["nccl"]) and torch.equal(outs["kernel"], outs["nccl"])
+    assert torch.equal(outs["fused_early"], outs["nccl"])
     np.save(os.path.join(result_dir, f"rank{rank}.npy"), outs["fused"].float().numpy())
 
     # the o projection with a head-sharded input: partial shrinks summed over peer memory, and by NCCL all_reduce
