@@ -377,6 +377,16 @@ int slora_tp_allsum(const void* local, void* const* peer_parts, int32_t* const* 
  * until the other rank's store has landed (bounded, ~2 s, then SLORA_STATUS_TIMEOUT and zeros).  The expand's last
  * CTA refills the half it consumed with the pattern.  Only the pipelined kernels do this: a layout they do not take
  * is an error in this mode.
+ * inband == 2: the same, and the expand does not wait for this rank's own shrink grid either (its values are
+ * recognised like the peers'): the two calls of an exchange must follow each other on one stream, and with
+ * SLORA_FLAG_PDL the expand's CTAs start as the shrink's retire (the shrink lets dependents launch only after its own
+ * grid-dependency wait, so what preceded the shrink is complete before the expand reads y).
+ * inband == 3: the early start over buffers of THREE parts, [3][3][full_tokens][R] (all 0xffff at the start), that
+ * rotate with the exchange's number.  seq_state is then two words of this rank's device memory, zeroed once and the
+ * kernels' to keep: word 0 is read by a shrink (after its grid-dependency wait) as its exchange's number e, word 1 is
+ * left by that shrink for its expand, which writes e + 1 back to word 0.  The exchange works in part e % 3 on every
+ * rank, and the shrink refills - spread over its CTAs, on this rank's own buffer - the part exchange e - 1 used.
+ * Nothing is done at the end of an expand; `half` is ignored; every rank must make the same sequence of calls.
  */
 int slora_tp_shrink_push(const void* plan, const int64_t* ids, int nproj, const int* qkvo, int part_width,
                          const void* x, int64_t x_stride, int h_in, const void* pool_a, int64_t pool_rows,
