@@ -3,7 +3,7 @@ tensor parallelism for the adapter path.
 
 Each rank holds its shard of every adapter (A: r/N rank rows, B: h_out/N output rows) for a few physical layers and
 runs the model's layer count over them; q/k/v see replicated activations, their rank-r intermediates are exchanged
-over NVLink from inside the kernels (peer-memory stores and flags; ``--tp-exchange p2p|nccl`` select the one-kernel
+over NVLink from inside the kernels (peer-memory stores, signalled in band; ``--tp-exchange p2p|nccl`` select the one-kernel
 exchange or NCCL all-gather + regroup).  The o projection runs by either rule: input replicated (the q/k/v rule), or
 input head-sharded ``[T, H/N]`` with the partial intermediates summed over the ranks, which is what a tensor-parallel
 base model hands over (the rule of the reference's figure for a row-parallel projection, ``figures/slora_tp.png``);
@@ -287,7 +287,10 @@ def run(args, dist, rank, world, device, peak):
     per_rank_bytes = (w_bytes + act) * L
     sec = head["ms_per_step"] * 1e-3
     if rank == 0:
-        how = ("peer memory from inside the shrink / expand kernels (NVLink stores + flags)"
+        signalling = {3: "in-band signalling, early start, buffers of three rotating parts",
+                      2: "in-band signalling, early start", 1: "in-band signalling",
+                      0: "flags"}.get(int(getattr(ops.px, "inband", 0)), "flags") if ops.px is not None else ""
+        how = ("peer memory from inside the shrink / expand kernels (NVLink stores; %s)" % signalling
                if ops.px is not None and args.tp_exchange == "fused" else
                "one kernel over peer memory (NVLink stores + flags)" if ops.px is not None else
                "NCCL all-gather + regroup")
