@@ -253,6 +253,72 @@ def test_fused_exchange_emulated_on_one_gpu(T, inband):
             assert_parity(got, want[p].numpy(), what=f"fused exchange proj {p}")
 
 
+def test_rotating_thirds_keep_their_place_across_graph_replays():
+    """One exchange per CUDA graph (an odd number, so a replay cannot start where the capture did): the part of the
+    buffers an exchange works in comes from the sequence words on the device, so replays rotate on through the three
+    parts.  Two ranks emulated on one GPU; five exchanges accumulate into the same outputs, against the same five
+    exchanges on the flag path."""
+    H, N, T = 4096, 2, 48
+    ranks = [16, 32, 16]
+    g = torch.Generator().manual_seed(29)
+    ads = [([torch.randn((r, H), generator=g) / 64 for _ in range(4)],
+            [torch.randn((H, r), generator=g) * 0.02 for _ in range(4)]) for r in ranks]
+    x = torch.randn((T, H), generator=g).to(torch.float16).to(DEV)
+    ids = torch.randint(0, len(ranks), (T,), generator=g).to(DEV)
+    R, Rl = max(ranks), max(ranks) // N
+    shards = []
+    for rank in range(N):
+        a_start, a_len, a_loc = make_tables([r // N for r in ranks], 512, 400 + rank, True)
+        pa = torch.zeros((512, H), dtype=torch.float16)
+        pb = torch.zeros((512, H), dtype=torch.float16)
+        for i, (A, B) in enumerate(ads):
+            ra, rb = tp.shard_adapter(A, B, rank, N, H)
+            loc = a_loc[a_start[i]: a_start[i] + a_len[i]]
+            pa[loc] = ra.to(torch.float16)
+            pb[loc] = rb.to(torch.float16)
+        t = tp.TpTables(a_start.to(DEV), a_len.to(DEV), a_loc.to(DEV),
+                        torch.tensor([16.0 / r for r in ranks], dtype=torch.float16, device=DEV))
+        shards.append((t, pa.to(DEV), pb.to(DEV)))
+
+    def run(inband, use_graph):
+        peers = _EmulatedPeers(N, T, R, inband)
+        pxs = [peers.rank(r) for r in range(N)]
+        be = tp.CudaBackend(use_pdl=inband == 3, inband=inband)
+        plans = [be.make_plan(ids, t) for t, _, _ in shards]
+        ys = [[torch.zeros((T, H // N), dtype=torch.float16, device=DEV) for _ in range(3)] for _ in range(N)]
+
+        def exchange():
+            for rank, (t, pa, pb) in enumerate(shards):
+                be.shrink_push(pxs[rank], plans[rank], ids, [0, 1, 2], x, pa, t, Rl, 0)
+            for rank, (t, pa, pb) in enumerate(shards):
+                be.expand_wait(pxs[rank], plans[rank], ids, [0, 1, 2], ys[rank], pb, t, Rl, 0)
+
+        s = torch.cuda.Stream()
+        s.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(s):
+            exchange()
+            if use_graph:
+                graph = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(graph, stream=s):
+                    exchange()
+                for _ in range(4):
+                    graph.replay()
+            else:
+                for _ in range(4):
+                    exchange()
+        s.synchronize()
+        for plan in plans:
+            plan.check()
+        return ys, pxs
+
+    want, _ = run(False, False)
+    got, pxs = run(3, True)
+    for rank in range(N):
+        assert pxs[rank].inband_seq.tolist() == [5, 4]
+        for j in range(3):
+            assert torch.equal(got[rank][j], want[rank][j]), f"rank {rank} proj {j}"
+
+
 def test_in_band_wait_runs_out_without_hanging():
     """An expand whose delta rows nobody writes (no rank has pushed): the consumers' bounded re-reads give up, the
     status word says so, the launch ends and the context stays usable."""
