@@ -541,6 +541,28 @@ int ensure_dyn_smem(K kernel, int which, size_t smem, size_t static_bytes = 0) {
   return SLORA_OK;
 }
 
+// Grid of a pipelined launch: two CTAs per SM, or one per item when there are fewer.  Under the padded enumeration
+// (slot i belongs to CTA i mod grid, `per_tile` slots per tile) the grid is made coprime to per_tile: with a common
+// factor a CTA only ever sees some of a tile's slot kinds, and where low-rank adapters leave the same kinds empty
+// every time (the second row block of a projection, say) the CTAs that see those would idle while the others do all
+// the work - e.g. 296 CTAs and 6 slots per tile: the odd CTAs would only get second row blocks.
+int64_t pipe_grid(int64_t items, int per_tile, bool exact) {
+  int64_t grid = static_cast<int64_t>(sm_count()) * kPipeCtasPerSm;
+  if (items < grid) return items;
+  if (!exact && per_tile > 1) {
+    auto gcd = [](int64_t a, int64_t b) {
+      while (b) {
+        const int64_t t = a % b;
+        a = b;
+        b = t;
+      }
+      return a;
+    };
+    while (grid > 1 && gcd(grid, per_tile) != 1) --grid;
+  }
+  return grid;
+}
+
 int run_shrink(const TileSrc& src, const Tables& tb, const void* w, const void* x, int64_t x_stride, int h_in,
                int nproj, const int* qkvo, void* const* delta, int64_t delta_stride, int delta_width, int dtype,
                unsigned flags, int32_t* status, cudaStream_t stream, const TpLink* tp = nullptr, int rank_mult = 1) {
@@ -670,9 +692,9 @@ int run_shrink(const TileSrc& src, const Tables& tb, const void* w, const void* 
     a.src.xrcap = src.xrcap;
     a.max_rb = (delta_width + kMaxRows - 1) / kMaxRows;
     const int64_t items = static_cast<int64_t>(src.slots) * nproj * a.max_rb;
-    const int64_t grid = items < sm_count() * kPipeCtasPerSm ? items : sm_count() * kPipeCtasPerSm;
-    const size_t smem = kRingBytes;
     const bool exact = (flags & SLORA_FLAG_EXACT_ITEMS) != 0 && src.mode == MODE_PLAN;
+    const int64_t grid = pipe_grid(items, nproj * a.max_rb, exact);
+    const size_t smem = kRingBytes;
     auto go = [&](auto k, int which) {
       const int rc2 = ensure_dyn_smem(k, which, smem);
       return rc2 ? rc2 : launch(k, grid, kPipeThreads, smem, flags, stream, a, "shrink(pipelined)");
@@ -819,8 +841,8 @@ int run_expand(const TileSrc& src, const Tables& tb, const void* w, const void* 
     a.src.xrcap = src.xrcap;
     set_chunks(kPipeChunk);
     const int64_t items = static_cast<int64_t>(src.slots) * a.chunk_begin[nproj];
-    const int64_t grid = items < sm_count() * kPipeCtasPerSm ? items : sm_count() * kPipeCtasPerSm;
     const bool exact = (flags & SLORA_FLAG_EXACT_ITEMS) != 0 && src.mode == MODE_PLAN;
+    const int64_t grid = pipe_grid(items, a.chunk_begin[nproj], exact);
     const size_t smem = exact ? kExpandRingBytes : kRingBytes;
     if (epi) {
       // the expand with rotary embedding / KV-pool scatter in its epilogue (lora_rope.cuh)
