@@ -546,10 +546,16 @@ int ensure_dyn_smem(K kernel, int which, size_t smem, size_t static_bytes = 0) {
 // factor a CTA only ever sees some of a tile's slot kinds, and where low-rank adapters leave the same kinds empty
 // every time (the second row block of a projection, say) the CTAs that see those would idle while the others do all
 // the work - e.g. 296 CTAs and 6 slots per tile: the odd CTAs would only get second row blocks.
+// Off unless SLORA_COPRIME_GRID=1: measured on one GPU only (a rank's kernels of the 13B-shaped batch under 8-way
+// tensor parallelism, emulated: 54.1 -> 51.6 us per layer; same-rank decode batches unchanged).
 int64_t pipe_grid(int64_t items, int per_tile, bool exact) {
+  static const bool coprime = [] {
+    const char* e = getenv("SLORA_COPRIME_GRID");
+    return e && strcmp(e, "1") == 0;
+  }();
   int64_t grid = static_cast<int64_t>(sm_count()) * kPipeCtasPerSm;
   if (items < grid) return items;
-  if (!exact && per_tile > 1) {
+  if (coprime && !exact && per_tile > 1) {
     auto gcd = [](int64_t a, int64_t b) {
       while (b) {
         const int64_t t = a % b;
