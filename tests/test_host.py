@@ -138,3 +138,26 @@ def test_algorithmic_bytes_of_the_s1_decode_batch():
     assert w.algorithmic_bytes_per_layer() == want
     assert 100 <= distinct <= 170     # Zipf(1.0) over 1000 adapters, 256 draws
     assert w.gathered_bytes_per_layer() > w.algorithmic_bytes_per_layer()
+
+
+def test_reference_arm_of_the_benchmark_runs_without_the_product_library(tmp_path):
+    """``bench.py --impl reference`` times the CPU restatement of the reference's per-token formula and must not need
+    the CUDA library: it is run here with the library path pointing nowhere (importing the package would fail).  Its
+    line carries the keys the benchmark contract asks of the reference arm."""
+    import json
+    import os
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    env = dict(os.environ, SLORA_B200_LIB=str(tmp_path / "no_such_library.so"))
+    out = subprocess.run([sys.executable, os.path.join(root, "bench.py"), "--impl", "reference", "--config", "1",
+                          "--steps", "1", "--warmup", "1"], env=env, capture_output=True, text=True, timeout=600)
+    assert out.returncode == 0, out.stderr[-2000:]
+    line = json.loads(out.stdout.strip().splitlines()[-1])
+    assert line["impl"] == "reference" and line["metric"] == "lora_delta_tokens_per_s" and line["value"] > 0
+    assert line["gpu_launches"] == 0 and line["vs_baseline"] is None
+    assert line["e2e"] == {"value": line["value"], "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}
+    cb = line["cpu_baseline"]
+    assert cb["kind"] == "port" and cb["cores"] >= 1 and cb["value"] == line["value"] and "sample" in cb
+    assert str(cb["cores"]) in cb["thread_sweep_s_per_layer"]
+    assert line["config"]["workload"].startswith("cfg1") and line["config"]["tokens"] == 32
